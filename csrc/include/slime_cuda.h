@@ -1,0 +1,69 @@
+// C API of libslime_cuda.so: every sm_100a kernel launcher and the CUDA-side
+// memory plumbing (symmetric heap, IPC import, status pages). All functions
+// return 0 on success and a negative value on error; slime_last_error() gives
+// the message for the calling thread. `stream` is a cudaStream_t passed as
+// void*; `status` is a device (or mapped host) pointer to a 32-byte status page
+// or NULL.
+#pragma once
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* slime_last_error(void);
+int         slime_cuda_version(void);
+
+// ---- status pages and small utilities (runtime.cu) -------------------------
+// A status page is 32 bytes of mapped pinned host memory: the kernel writes it,
+// the host reads it without a copy. *dev_ptr is the address kernels receive.
+int slime_status_alloc(void** host_ptr, void** dev_ptr);
+int slime_status_free(void* host_ptr);
+// Mapped pinned host words usable as flags that a kernel can wait on or set.
+int slime_host_flags_alloc(unsigned long long n_words, void** host_ptr, void** dev_ptr);
+int slime_host_flags_free(void* host_ptr);
+// Test helper: launches one thread that waits (bounded by limit_ns) for *flag >= target.
+int slime_wait_flag_kernel(const void* flag, unsigned long long target, unsigned long long limit_ns, void* status,
+                           void* stream);
+// Writes `value` to the 64-bit word at `flag` with release semantics at system scope, in stream order.
+int slime_signal_flag_kernel(void* flag, unsigned long long value, int add, void* stream);
+
+// ---- symmetric heap (symm_heap.cu) ----------------------------------------
+// cudaMalloc-backed region with a CUDA IPC handle (64 bytes) that other
+// processes on the node can map. Returns the device pointer in *ptr.
+int slime_symm_alloc(unsigned long long bytes, void** ptr, unsigned char* ipc_handle_out64);
+int slime_symm_free(void* ptr);
+int slime_ipc_get_handle(const void* ptr, unsigned char* ipc_handle_out64, unsigned long long* offset_out,
+                         unsigned long long* alloc_size_out);
+int slime_ipc_open(const unsigned char* ipc_handle64, void** ptr_out);
+int slime_ipc_close(void* ptr);
+int slime_enable_peer_access(int peer_device);
+int slime_memset_async(void* ptr, int value, unsigned long long bytes, void* stream);
+
+// ---- fp8 block-scaled quantisation (fp8_quant.cu) ---------------------------
+int slime_fp8_quant_1x128(const void* x, void* q, float* scales, long long rows, int cols, long long ldx,
+                          long long ldq, void* stream);
+int slime_fp8_dequant_1x128(const void* q, const float* scales, void* y, long long rows, int cols, long long ldq,
+                            long long ldy, void* stream);
+int slime_fp8_quant_128x128(const void* w, void* q, float* scales, int rows, int cols, long long ldw, long long ldq,
+                            void* stream);
+
+// ---- tcgen05 GEMMs (gemm.cu) -----------------------------------------------
+// C[M,N] = A[M,K] * B[N,K]^T, bf16 in, fp32 accumulate, bf16 out.
+int slime_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                    long long ldc, void* status, void* stream);
+// Same, but a tile of A rows is read only after its arrival flag reached the target
+// (a_ready[row / a_ready_rows] >= a_ready_target); m tiles start at m_tile_rotate.
+int slime_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                          long long ldc, const void* a_ready, int a_ready_rows, unsigned long long a_ready_target,
+                          int m_tile_rotate, void* status, void* stream);
+// Rows of A are split into num_groups consecutive groups by the device array
+// group_offsets[num_groups+1]; group g multiplies B rows [g*rowsB, (g+1)*rowsB).
+// epilogue 0: store; 1: SwiGLU (B holds N gate rows then N up rows per group, C is [M,N]);
+// 2: scatter row r, scaled by row_scale[r], to the address row_dst[r] (0 = skip).
+int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                            int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                            const void* row_dst, const float* row_scale, void* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,372 @@
+// Persistent, warp-specialised bf16 GEMM main loop on the 5th-generation tensor
+// cores: TMA (128-byte swizzle) -> shared memory ring -> tcgen05.mma (one issuing
+// thread) -> fp32 accumulators in TMEM (double buffered) -> tcgen05.ld epilogue.
+//
+//   C[g] (rows of group g, N) = A[g] (rows of group g, K) * B[g] (N, K)^T
+//
+// A is one row-major [M_total, K] matrix whose rows are partitioned into groups
+// by a device-side prefix array; B is row-major [groups * rowsB, K] ("K-major",
+// the nn.Linear layout). Tiles are 128 x BN x 64. A tile that crosses the end of
+// its group computes garbage rows that the epilogue never stores, so groups need
+// no row padding.
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner and MMA
+// issuer, warps 2..5 = epilogue (each owns the 32 TMEM lanes of its quadrant).
+// Every wait is bounded; a timeout is recorded in the status page and the CTA
+// drains, frees its TMEM and returns.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace slime {
+namespace gemm {
+
+constexpr int kBM      = 128;
+constexpr int kBK      = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kThreads = 192;
+
+enum Epilogue : int {
+    kEpiStore  = 0,  // C = acc (bf16)
+    kEpiSwiGLU = 1,  // tile columns [0,BN/2) are gate, [BN/2,BN) are up: C = silu(gate) * up
+    kEpiScatterRows = 2,  // C row r goes to dst_ptr[row_map[r]] (may be peer memory), scaled by row_scale[r]
+};
+
+struct Args {
+    int M_total;  // rows in A (upper bound for every group end)
+    int N;        // output columns per group (for SwiGLU: the intermediate size)
+    int K;
+    int rowsB;  // rows of B per group (N, or 2N for SwiGLU where gate rows precede up rows)
+    int num_groups;
+    const int* group_offsets;  // [num_groups + 1] device prefix of rows, or nullptr for one group [0, M_total)
+    __nv_bfloat16* C;
+    long long      ldc;
+    // kEpiScatterRows: destination row pointers and per-row weights
+    const unsigned long long* row_dst;    // [M_total] absolute addresses of the destination rows (0 = drop)
+    const float*              row_scale;  // [M_total] or nullptr
+    // optional per-128-row A readiness flags (all-gather -> GEMM): tile rows [128*i, 128*i+128)
+    // may be read once a_ready[i / a_ready_div] >= a_ready_target
+    const unsigned long long* a_ready;
+    int                       a_ready_rows;  // rows covered by one flag
+    unsigned long long        a_ready_target;
+    int                       m_tile_rotate;  // start the m-tile order at this tile (own shard first)
+    KernelStatus*             status;
+    unsigned long long        wait_ns;
+};
+
+template<int BN, int STAGES>
+struct Smem {
+    static constexpr int kABytes     = kBM * kBK * 2;
+    static constexpr int kBBytes     = BN * kBK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarBytes   = (2 * STAGES + 4) * 8 + 16;
+    static constexpr int kTotal      = STAGES * kStageBytes + kBarBytes + 1024;  // + alignment slack
+};
+
+struct TileCoord {
+    int group;
+    int row0;     // first row of the tile in A / C
+    int row_end;  // one past the last valid row of the group
+    int nt;       // n-tile index inside the group
+};
+
+// Walks the persistent tile sequence blockIdx.x, blockIdx.x + gridDim.x, ...
+// Order inside a group: m fastest, so CTAs running at the same time share B tiles in L2.
+struct TileWalker {
+    const Args& a;
+    int         ntiles_n;
+    int         t;          // next linear tile for this CTA
+    int         g;          // current group
+    int         cum;        // tiles before group g
+    int         g_begin, g_end, g_mtiles;
+
+    __device__ TileWalker(const Args& args, int bn_out): a(args)
+    {
+        ntiles_n = (a.N + bn_out - 1) / bn_out;
+        t        = blockIdx.x;
+        g        = -1;
+        cum      = 0;
+        g_begin = g_end = g_mtiles = 0;
+        advance_group();
+    }
+    __device__ void advance_group()
+    {
+        ++g;
+        if (g < a.num_groups) {
+            g_begin  = a.group_offsets ? a.group_offsets[g] : 0;
+            g_end    = a.group_offsets ? a.group_offsets[g + 1] : a.M_total;
+            if (g_end > a.M_total) g_end = a.M_total;
+            if (g_begin > g_end) g_begin = g_end;
+            g_mtiles = (g_end - g_begin + kBM - 1) / kBM;
+        }
+    }
+    __device__ bool next(TileCoord& c)
+    {
+        while (g < a.num_groups) {
+            const int tiles_g = g_mtiles * ntiles_n;
+            if (t < cum + tiles_g) {
+                const int local = t - cum;
+                int       mt    = local % g_mtiles;
+                if (a.m_tile_rotate) mt = (mt + a.m_tile_rotate) % g_mtiles;
+                c.group   = g;
+                c.row0    = g_begin + mt * kBM;
+                c.row_end = g_end;
+                c.nt      = local / g_mtiles;
+                t += gridDim.x;
+                return true;
+            }
+            cum += tiles_g;
+            advance_group();
+        }
+        return false;
+    }
+};
+
+__device__ __forceinline__ float silu(float x)
+{
+    return x / (1.0f + __expf(-x));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
+{
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template<int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args args)
+{
+    using S = Smem<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    uint64_t* full_bar   = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
+    uint64_t* empty_bar  = full_bar + STAGES;
+    uint64_t* tfull_bar  = empty_bar + STAGES;  // [2] accumulator ready
+    uint64_t* tempty_bar = tfull_bar + 2;       // [2] accumulator drained
+    uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+    volatile uint32_t* fail_slot = tmem_slot + 1;  // set by any role whose wait ran out
+
+    const int          warp    = threadIdx.x >> 5;
+    const int          lane    = threadIdx.x & 31;
+    const int          kblocks = (args.K + kBK - 1) / kBK;
+    KernelStatus*      st      = args.status;
+    const unsigned long long lim = args.wait_ns ? args.wait_ns : kDefaultWaitNs;
+    constexpr int      kTmemCols = 2 * BN;  // double-buffered accumulator (power of two >= 32)
+    constexpr int      kBNOut    = (EPI == kEpiSwiGLU) ? BN / 2 : BN;
+
+    if (threadIdx.x == 0) {
+        *fail_slot = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tfull_bar[s], 1);
+            mbar_init(&tempty_bar[s], 128);
+        }
+        fence_mbar_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            TileWalker walk(args, kBNOut);
+            TileCoord  tc;
+            int        stage = 0;
+            uint32_t   phase = 0;
+            bool       ok    = true;
+            while (ok && walk.next(tc)) {
+                if (args.a_ready) {
+                    // rows [row0, row0+128) must have arrived in local memory
+                    const int f0 = tc.row0 / args.a_ready_rows;
+                    int       last_row = tc.row0 + kBM - 1;
+                    if (last_row >= tc.row_end) last_row = tc.row_end - 1;
+                    const int f1 = last_row / args.a_ready_rows;
+                    for (int f = f0; f <= f1 && ok; ++f)
+                        ok = wait_flag_ge(args.a_ready + f, args.a_ready_target, st, 10, f, lim);
+                    if (!ok) break;
+                    fence_proxy_async();
+                }
+                int yb0, yb1;
+                if (EPI == kEpiSwiGLU) {
+                    yb0 = tc.group * args.rowsB + tc.nt * (BN / 2);
+                    yb1 = yb0 + args.N;
+                }
+                else {
+                    yb0 = tc.group * args.rowsB + tc.nt * BN;
+                    yb1 = yb0 + BN / 2;
+                }
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, st, 1, stage, lim)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem + stage * S::kStageBytes;
+                    uint8_t* sb = sa + S::kABytes;
+                    mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
+                    tma_load_2d(sa, &tmA, &full_bar[stage], kb * kBK, tc.row0);
+                    tma_load_2d(sb, &tmB, &full_bar[stage], kb * kBK, yb0);
+                    tma_load_2d(sb + S::kBBytes / 2, &tmB, &full_bar[stage], kb * kBK, yb1);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok) *fail_slot = 1;
+        }
+    }
+    else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            TileWalker walk(args, kBNOut);
+            TileCoord  tc;
+            int        stage = 0;
+            uint32_t   phase = 0;
+            int        acc = 0;
+            uint32_t   acc_phase = 0;
+            bool       ok = true;
+            constexpr uint32_t idesc = make_idesc(kFmtBF16, kFmtBF16, kBM, BN);
+            while (ok && walk.next(tc)) {
+                if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, st, 2, acc, lim)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, st, 3, stage, lim)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
+                    const uint32_t sb = sa + S::kABytes;
+                    const uint64_t da = make_kmajor_sw128_desc(sa);
+                    const uint64_t db = make_kmajor_sw128_desc(sb);
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        // advance 16 bf16 = 32 bytes along K inside the swizzle row: +2 in the >>4 address field
+                        umma_f16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(&empty_bar[stage]);  // frees the smem slot when these MMAs retire
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(&tfull_bar[acc]);
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+            if (!ok) *fail_slot = 1;
+        }
+    }
+    else {
+        // ------------------------------ epilogue ----------------------------------
+        const int  quad = warp & 3;  // TMEM lane quadrant this warp may access
+        TileWalker walk(args, kBNOut);
+        TileCoord  tc;
+        int        acc = 0;
+        uint32_t   acc_phase = 0;
+        while (walk.next(tc)) {
+            if (!mbar_wait(&tfull_bar[acc], acc_phase, st, 4, acc, lim)) {
+                *fail_slot = 1;
+                break;
+            }
+            tc_fence_after_sync();
+            const int      row   = tc.row0 + quad * 32 + lane;
+            const bool     valid = row < tc.row_end;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+            const int      col0  = tc.nt * kBNOut;
+
+            if (EPI == kEpiSwiGLU) {
+                __nv_bfloat16* crow = args.C + static_cast<long long>(row) * args.ldc + col0;
+#pragma unroll 1
+                for (int c = 0; c < BN / 2; c += 16) {
+                    uint32_t g[16], u[16];
+                    tmem_ld_32x32b_x16(taddr + c, g);
+                    tmem_ld_32x32b_x16(taddr + BN / 2 + c, u);
+                    tmem_ld_wait();
+                    if (valid && col0 + c < args.N) {
+                        uint32_t o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float h0 = silu(__uint_as_float(g[2 * i])) * __uint_as_float(u[2 * i]);
+                            const float h1 = silu(__uint_as_float(g[2 * i + 1])) * __uint_as_float(u[2 * i + 1]);
+                            o[i]           = pack_bf16(h0, h1);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(crow + c);
+                        dst[0]     = make_uint4(o[0], o[1], o[2], o[3]);
+                        dst[1]     = make_uint4(o[4], o[5], o[6], o[7]);
+                    }
+                }
+            }
+            else {
+                __nv_bfloat16* crow;
+                float          scale = 1.0f;
+                bool           do_store = valid;
+                if (EPI == kEpiScatterRows) {
+                    unsigned long long d = valid ? args.row_dst[row] : 0ull;
+                    do_store             = d != 0ull;
+                    crow                 = reinterpret_cast<__nv_bfloat16*>(d) + col0;
+                    if (do_store && args.row_scale) scale = args.row_scale[row];
+                }
+                else {
+                    crow = args.C + static_cast<long long>(row) * args.ldc + col0;
+                }
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + c, v);
+                    tmem_ld_wait();
+                    if (do_store && col0 + c < args.N) {
+                        uint32_t o[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            o[i] = pack_bf16(__uint_as_float(v[2 * i]) * scale, __uint_as_float(v[2 * i + 1]) * scale);
+                        uint4* dst = reinterpret_cast<uint4*>(crow + c);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tempty_bar[acc]);
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1;
+            }
+        }
+    }
+
+    // teardown: everyone meets, then the allocating warp frees TMEM
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        if (*fail_slot != 0) {
+            // a wait ran out somewhere: give copies still in flight a bounded moment to land
+            const unsigned long long t0 = globaltimer_ns();
+            while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace gemm
+}  // namespace slime

@@ -1,0 +1,162 @@
+"""In-tree native build: nvcc for the sm_100a kernels, g++ for the host runtime.
+
+Two artefacts are produced next to the Python package so that they travel with a
+source snapshot and are visible as loaded in-tree libraries:
+
+* ``dlslime_b200/_C/libslime_cuda.so`` -- every ``csrc/kernels/*.cu`` compiled
+  with ``-gencode arch=compute_100a,code=sm_100a``; a plain C API (ctypes).
+* ``dlslime_b200/_slime_c*.so`` -- the pybind11 host runtime (assignment model,
+  cache directory, counters, TCP endpoint, RPC session, control plane, ...).
+* ``dlslime_b200/_C/nanoctrl`` -- the stand-alone control-plane server binary.
+
+Objects are rebuilt only when a source or header is newer (mtime), and
+independent translation units compile in parallel.
+"""
+
+from __future__ import annotations
+
+import concurrent.futures as cf
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "csrc"
+PKG = ROOT / "dlslime_b200"
+OBJ = ROOT / "build" / "obj"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+    "-DSLIME_BUILDING_LIB",
+]
+CXX_FLAGS = ["-O2", "-g0", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread", "-Wall", "-Wno-unused-function"]
+
+
+def _nvcc() -> str:
+    cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(cand).exists():
+        raise RuntimeError("nvcc not found; the sm_100a kernels cannot be built")
+    return cand
+
+
+def _newest_header_mtime(dirs) -> float:
+    newest = 0.0
+    for d in dirs:
+        for p in Path(d).rglob("*"):
+            if p.suffix in (".h", ".hpp", ".cuh"):
+                newest = max(newest, p.stat().st_mtime)
+    return newest
+
+
+def _run(cmd, verbose):
+    if verbose:
+        print(" ".join(str(c) for c in cmd), flush=True)
+    res = subprocess.run([str(c) for c in cmd], capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"build command failed:\n{' '.join(str(c) for c in cmd)}\n{res.stdout}\n{res.stderr}")
+    if verbose and (res.stdout.strip() or res.stderr.strip()):
+        print(res.stdout, res.stderr, flush=True)
+    return res
+
+
+def _compile_many(jobs, verbose, workers):
+    """jobs: list of (src, obj, cmd). Runs the stale ones in parallel."""
+    stale = []
+    for src, obj, cmd, dep_mtime in jobs:
+        if (not obj.exists()) or obj.stat().st_mtime < max(src.stat().st_mtime, dep_mtime):
+            stale.append((src, obj, cmd))
+    if not stale:
+        return False
+    with cf.ThreadPoolExecutor(max_workers=workers) as ex:
+        futs = [ex.submit(_run, cmd, verbose) for _, _, cmd in stale]
+        for f in futs:
+            f.result()
+    return True
+
+
+def cuda_lib_path() -> Path:
+    return PKG / "_C" / "libslime_cuda.so"
+
+
+def host_ext_path() -> Path:
+    suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    return PKG / f"_slime_c{suffix}"
+
+
+def nanoctrl_bin_path() -> Path:
+    return PKG / "_C" / "nanoctrl"
+
+
+def build_cuda(verbose: bool = False, ptxas_info: bool = False, workers: int | None = None) -> Path:
+    nvcc = _nvcc()
+    kdir = CSRC / "kernels"
+    inc = [CSRC / "include", kdir]
+    dep = _newest_header_mtime([CSRC / "include", kdir])
+    (OBJ / "cuda").mkdir(parents=True, exist_ok=True)
+    (PKG / "_C").mkdir(parents=True, exist_ok=True)
+    jobs, objs = [], []
+    for src in sorted(kdir.glob("*.cu")):
+        obj = OBJ / "cuda" / (src.stem + ".o")
+        cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if ptxas_info else []), *sum((["-I", i] for i in inc), []), "-c", src, "-o", obj]
+        jobs.append((src, obj, cmd, dep))
+        objs.append(obj)
+    changed = _compile_many(jobs, verbose or ptxas_info, workers or min(8, os.cpu_count() or 4))
+    out = cuda_lib_path()
+    if changed or not out.exists():
+        _run([nvcc, "-shared", "-o", out, *objs, "-cudart", "static", "-Xlinker", "--no-undefined", "-lpthread", "-ldl", "-lrt"], verbose)
+    return out
+
+
+def build_host(verbose: bool = False, workers: int | None = None) -> Path:
+    import pybind11
+
+    hdir = CSRC / "host"
+    if not hdir.exists():
+        return host_ext_path()
+    inc = [CSRC / "include", hdir, Path(pybind11.get_include()), Path(sysconfig.get_paths()["include"])]
+    dep = _newest_header_mtime([CSRC / "include", hdir])
+    (OBJ / "host").mkdir(parents=True, exist_ok=True)
+    cxx = os.environ.get("CXX", "g++")
+    jobs, objs, main_objs = [], [], []
+    for src in sorted(hdir.rglob("*.cpp")):
+        rel = "_".join(src.relative_to(hdir).with_suffix("").parts)
+        obj = OBJ / "host" / (rel + ".o")
+        cmd = [cxx, *CXX_FLAGS, *sum((["-I", i] for i in inc), []), "-c", src, "-o", obj]
+        jobs.append((src, obj, cmd, dep))
+        if src.name == "nanoctrl_main.cpp":
+            main_objs.append(obj)
+        else:
+            objs.append(obj)
+    changed = _compile_many(jobs, verbose, workers or min(8, os.cpu_count() or 4))
+    out = host_ext_path()
+    if changed or not out.exists():
+        _run([cxx, "-shared", "-o", out, *objs, "-pthread", "-ldl", "-lrt"], verbose)
+    if main_objs:
+        exe = nanoctrl_bin_path()
+        if changed or not exe.exists():
+            (PKG / "_C").mkdir(parents=True, exist_ok=True)
+            core = [o for o in objs if not o.name.startswith("bind")]
+            _run([cxx, "-o", exe, *main_objs, *core, "-pthread", "-ldl", "-lrt"], verbose)
+    return out
+
+
+def build_all(verbose: bool = False) -> None:
+    build_cuda(verbose=verbose)
+    build_host(verbose=verbose)
+
+
+if __name__ == "__main__":
+    v = "-v" in sys.argv
+    if "--ptxas" in sys.argv:
+        build_cuda(verbose=True, ptxas_info=True)
+    elif "--cuda" in sys.argv:
+        build_cuda(verbose=v)
+    elif "--host" in sys.argv:
+        build_host(verbose=v)
+    else:
+        build_all(verbose=v)
+    print("built:", cuda_lib_path(), host_ext_path())

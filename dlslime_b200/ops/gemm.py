@@ -1,0 +1,53 @@
+"""bf16 GEMMs on the tcgen05 tensor cores (``csrc/kernels/gemm.cu``).
+
+Weights use the ``nn.Linear`` layout ``[N, K]`` (K contiguous), activations are
+``[M, K]``; accumulation is fp32 in tensor memory, outputs are bf16.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ._common import default_status, ptr, require_cuda, stream_ptr
+
+EPI_STORE, EPI_SWIGLU, EPI_SCATTER_ROWS = 0, 1, 2
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[M, N] = a[M, K] @ b[N, K].T``."""
+    require_cuda(a, b)
+    assert a.dtype == b.dtype == torch.bfloat16 and a.stride(1) == 1 and b.stride(1) == 1
+    m, k = a.shape
+    n, kb = b.shape
+    assert k == kb
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    _lib.call("slime_gemm_bf16", ptr(a), ptr(b), ptr(out), m, n, k, a.stride(0), b.stride(0), out.stride(0),
+              default_status().dev_ptr, stream_ptr())
+    return out
+
+
+def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor, out: torch.Tensor | None = None,
+                      epilogue: int = EPI_STORE, row_dst: torch.Tensor | None = None,
+                      row_scale: torch.Tensor | None = None) -> torch.Tensor | None:
+    """Grouped GEMM over consecutive row groups of ``a``.
+
+    ``a`` is ``[M_cap, K]``; ``group_offsets`` is an int32 device tensor of
+    ``G + 1`` row prefixes (rows past ``group_offsets[G]`` are ignored); ``b`` is
+    ``[G, N, K]`` (``[G, 2N, K]`` with gate rows before up rows for SwiGLU).
+    The group sizes never leave the device, so there is no host synchronisation.
+    """
+    require_cuda(a, b, group_offsets)
+    assert a.dtype == b.dtype == torch.bfloat16 and group_offsets.dtype == torch.int32
+    assert a.stride(1) == 1 and b.is_contiguous() and b.dim() == 3
+    g, rows_b, k = b.shape
+    m_cap = a.shape[0]
+    n = rows_b // 2 if epilogue == EPI_SWIGLU else rows_b
+    assert group_offsets.numel() == g + 1 and a.shape[1] == k
+    if epilogue != EPI_SCATTER_ROWS and out is None:
+        out = torch.empty((m_cap, n), dtype=torch.bfloat16, device=a.device)
+    ldc = out.stride(0) if out is not None else n
+    _lib.call("slime_grouped_gemm_bf16", ptr(a), ptr(b), ptr(out), ptr(group_offsets), g, m_cap, n, k, a.stride(0), k,
+              ldc, epilogue, ptr(row_dst), ptr(row_scale), default_status().dev_ptr, stream_ptr())
+    return out

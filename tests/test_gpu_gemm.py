@@ -1,0 +1,99 @@
+"""tcgen05 GEMM kernels against an fp32 PyTorch matmul of the same bf16 inputs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(out, ref, k):
+    # bf16 output of an fp32 accumulation: relative 2^-7 of the result magnitude plus a
+    # small absolute term for cancellation
+    err = (out.float() - ref).abs()
+    tol = ref.abs() * 2 ** -7 + 2 ** -7 * ref.abs().mean() + 1e-3
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{bad} of {out.numel()} elements off; max err {err.max().item():.4g}"
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 512), (256, 512, 4096), (1000, 4096, 4096), (77, 96, 136)])
+def test_gemm_bf16(m, n, k):
+    from dlslime_b200.ops import gemm
+    from dlslime_b200.ops._common import default_status
+
+    torch.manual_seed(m + n + k)
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16)
+    out = gemm.gemm_bf16(a, b)
+    torch.cuda.synchronize()
+    default_status().check()
+    ref = a.float() @ b.float().t()
+    _check(out, ref, k)
+
+
+def test_grouped_gemm_store_and_swiglu():
+    from dlslime_b200.ops import gemm
+    from dlslime_b200.ops._common import default_status
+
+    torch.manual_seed(5)
+    sizes = [0, 5, 128, 131, 300, 1, 0, 64]
+    g, k, n = len(sizes), 512, 256
+    offs = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device="cuda")
+    total = sum(sizes)
+    a = torch.randn(total + 50, k, device="cuda", dtype=torch.bfloat16)  # extra rows past the last group are ignored
+    w = (torch.randn(g, n, k, device="cuda") * 0.05).to(torch.bfloat16)
+    out = torch.full((total + 50, n), 7.0, device="cuda", dtype=torch.bfloat16)
+    gemm.grouped_gemm_bf16(a, w, offs, out=out)
+    torch.cuda.synchronize()
+    default_status().check()
+    start = 0
+    for gi, sz in enumerate(sizes):
+        if sz:
+            ref = a[start:start + sz].float() @ w[gi].float().t()
+            _check(out[start:start + sz], ref, k)
+        start += sz
+    assert (out[total:] == 7.0).all(), "rows outside every group must not be written"
+
+    # SwiGLU: weights hold N gate rows then N up rows per group
+    n_int = 128
+    w2 = (torch.randn(g, 2 * n_int, k, device="cuda") * 0.05).to(torch.bfloat16)
+    h = gemm.grouped_gemm_bf16(a, w2, offs, epilogue=gemm.EPI_SWIGLU)
+    torch.cuda.synchronize()
+    default_status().check()
+    start = 0
+    for gi, sz in enumerate(sizes):
+        if sz:
+            x = a[start:start + sz].float()
+            gate = x @ w2[gi, :n_int].float().t()
+            up = x @ w2[gi, n_int:].float().t()
+            _check(h[start:start + sz], torch.nn.functional.silu(gate) * up, k)
+        start += sz
+
+
+def test_grouped_gemm_scatter_rows():
+    from dlslime_b200.ops import gemm
+    from dlslime_b200.ops._common import default_status
+
+    torch.manual_seed(6)
+    sizes = [40, 0, 200]
+    g, k, n = len(sizes), 256, 512
+    total = sum(sizes)
+    offs = torch.tensor([0, 40, 40, 240], dtype=torch.int32, device="cuda")
+    a = torch.randn(total, k, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(g, n, k, device="cuda") * 0.05).to(torch.bfloat16)
+    dst = torch.zeros(total, n, device="cuda", dtype=torch.bfloat16)
+    perm = torch.randperm(total, device="cuda")
+    row_dst = dst.data_ptr() + perm.to(torch.int64) * (n * 2)
+    row_dst[3] = 0  # dropped row
+    scale = torch.rand(total, device="cuda") + 0.5
+    gemm.grouped_gemm_bf16(a, w, offs, epilogue=gemm.EPI_SCATTER_ROWS, row_dst=row_dst, row_scale=scale)
+    torch.cuda.synchronize()
+    default_status().check()
+    ref = torch.zeros(total, n, device="cuda")
+    start = 0
+    for gi, sz in enumerate(sizes):
+        if sz:
+            ref[start:start + sz] = (a[start:start + sz].float() @ w[gi].float().t()) * scale[start:start + sz, None]
+        start += sz
+    expect = torch.zeros_like(ref)
+    expect[perm] = ref
+    expect[perm[3]] = 0
+    _check(dst, expect, k)
