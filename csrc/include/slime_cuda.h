@@ -59,10 +59,31 @@ int slime_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, i
 // Rows of A are split into num_groups consecutive groups by the device array
 // group_offsets[num_groups+1]; group g multiplies B rows [g*rowsB, (g+1)*rowsB).
 // epilogue 0: store; 1: SwiGLU (B holds N gate rows then N up rows per group, C is [M,N]);
-// 2: scatter row r, scaled by row_scale[r], to the address row_dst[r] (0 = skip).
+// 2: scatter row r, scaled by row_scale[r], to scatter_bases8[info >> 48] + (info & 2^48-1) * scatter_row_bytes
+//    where info = row_info[r]; the regions may be peer memory; a region >= 8 or slot >= scatter_slots drops the row.
 int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
                             int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
-                            const void* row_dst, const float* row_scale, void* status, void* stream);
+                            const void* row_info, const unsigned long long* scatter_bases8,
+                            unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
+                            const float* row_scale, void* status, void* stream);
+
+// ---- expert-parallel dispatch / combine (ep.cu) ------------------------------
+// cfg_bytes points at a packed EpConfig (see dlslime_b200/ops/ep.py for the field order).
+int slime_ep_config_size(void);
+int slime_ep_route(const void* cfg_bytes, const float* logits, int T, int* topk_idx, float* topk_w, int* slot,
+                   unsigned int* send_count, unsigned int* block_counter, unsigned long long epoch, int renormalize,
+                   void* stream);
+int slime_ep_dispatch(const void* cfg_bytes, const void* x, long long ldx, int T, const int* topk_idx, const int* slot,
+                      int* group_offsets, unsigned int* block_counter, unsigned long long epoch, int max_blocks,
+                      void* status, void* stream);
+int slime_ep_recv_dequant(const void* cfg_bytes, const int* group_offsets, void* y, long long ldy, int expected_rows,
+                          unsigned long long epoch, void* status, void* stream);
+int slime_ep_combine_push(const void* cfg_bytes, const void* y, long long ldy, const int* group_offsets,
+                          int expected_rows, void* status, void* stream);
+int slime_ep_signal(const void* cfg_bytes, int which, unsigned long long epoch, void* stream);
+int slime_ep_combine_reduce(const void* cfg_bytes, int T, const int* topk_idx, const float* topk_w, void* out,
+                            long long ldo, unsigned long long epoch, int do_signal, void* status, void* stream);
+int slime_ep_barrier(const void* cfg_bytes, unsigned long long epoch, void* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -28,7 +28,7 @@ constexpr int kThreads = 192;
 enum Epilogue : int {
     kEpiStore  = 0,  // C = acc (bf16)
     kEpiSwiGLU = 1,  // tile columns [0,BN/2) are gate, [BN/2,BN) are up: C = silu(gate) * up
-    kEpiScatterRows = 2,  // C row r goes to dst_ptr[row_map[r]] (may be peer memory), scaled by row_scale[r]
+    kEpiScatterRows = 2,  // row r goes to scatter_base[info >> 48] + (info & 2^48-1) * scatter_row_bytes (peer memory allowed)
 };
 
 struct Args {
@@ -40,9 +40,12 @@ struct Args {
     const int* group_offsets;  // [num_groups + 1] device prefix of rows, or nullptr for one group [0, M_total)
     __nv_bfloat16* C;
     long long      ldc;
-    // kEpiScatterRows: destination row pointers and per-row weights
-    const unsigned long long* row_dst;    // [M_total] absolute addresses of the destination rows (0 = drop)
+    // kEpiScatterRows: per-row destination (region index << 48 | row slot inside that region) and optional weight
+    const unsigned long long* row_info;   // [M_total]; a region index >= 8 or a slot >= scatter_slots drops the row
     const float*              row_scale;  // [M_total] or nullptr
+    unsigned long long        scatter_base[8];  // base address of each destination region (0 = absent)
+    unsigned long long        scatter_row_bytes;
+    unsigned long long        scatter_slots;
     // optional per-128-row A readiness flags (all-gather -> GEMM): tile rows [128*i, 128*i+128)
     // may be read once a_ready[i / a_ready_div] >= a_ready_target
     const unsigned long long* a_ready;
@@ -321,9 +324,12 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 float          scale = 1.0f;
                 bool           do_store = valid;
                 if (EPI == kEpiScatterRows) {
-                    unsigned long long d = valid ? args.row_dst[row] : 0ull;
-                    do_store             = d != 0ull;
-                    crow                 = reinterpret_cast<__nv_bfloat16*>(d) + col0;
+                    const unsigned long long inf    = valid ? args.row_info[row] : ~0ull;
+                    const unsigned int       region = static_cast<unsigned int>(inf >> 48);
+                    const unsigned long long slot   = inf & 0xffffffffffffull;
+                    const unsigned long long base   = region < 8 ? args.scatter_base[region] : 0ull;
+                    do_store                        = valid && base != 0ull && slot < args.scatter_slots;
+                    crow = reinterpret_cast<__nv_bfloat16*>(base + slot * args.scatter_row_bytes) + col0;
                     if (do_store && args.row_scale) scale = args.row_scale[row];
                 }
                 else {

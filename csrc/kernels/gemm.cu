@@ -91,7 +91,9 @@ int slime_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, i
 
 int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
                             int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
-                            const void* row_dst, const float* row_scale, void* status, void* stream)
+                            const void* row_info, const unsigned long long* scatter_bases8,
+                            unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
+                            const float* row_scale, void* status, void* stream)
 {
     if (check_common(M_cap, N, K, lda, ldb)) return -1;
     if (num_groups <= 0 || group_offsets == nullptr) return fail("grouped gemm: need group offsets");
@@ -114,10 +116,14 @@ int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* gr
             a.rowsB = 2 * N;
             return launch<kEpiSwiGLU>(A, B, a, lda, ldb, 0, s);
         case kEpiScatterRows:
-            if (row_dst == nullptr) return fail("grouped gemm: scatter epilogue needs row_dst");
+            if (row_info == nullptr || scatter_bases8 == nullptr) return fail("grouped gemm: scatter epilogue needs row_info and bases");
+            if (scatter_row_bytes % 16 != 0) return fail("grouped gemm: scatter rows must be 16-byte aligned");
             a.rowsB     = N;
-            a.row_dst   = static_cast<const unsigned long long*>(row_dst);
+            a.row_info  = static_cast<const unsigned long long*>(row_info);
             a.row_scale = row_scale;
+            for (int i = 0; i < 8; ++i) a.scatter_base[i] = scatter_bases8[i];
+            a.scatter_row_bytes = scatter_row_bytes;
+            a.scatter_slots     = scatter_slots;
             return launch<kEpiScatterRows>(A, B, a, lda, ldb, 0, s);
         default:
             return fail("grouped gemm: unknown epilogue %d", epilogue);

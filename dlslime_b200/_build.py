@@ -30,8 +30,7 @@ OBJ = ROOT / "build" / "obj"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-    "-DSLIME_BUILDING_LIB",
+    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",
 ]
 CXX_FLAGS = ["-O2", "-g0", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread", "-Wall", "-Wno-unused-function"]
 

@@ -1,0 +1,154 @@
+"""DeepSeek-V3-shaped expert-parallel MoE layer built from the EP kernels.
+
+One forward step on every rank:
+
+    route -> dispatch (fp8 1x128 quantisation fused with the NVLink push)
+          -> receive + dequantise -> grouped gate/up GEMM with SwiGLU epilogue
+          -> grouped down GEMM whose epilogue stores rows into the token owners'
+             combine buffers over NVLink -> gate-weighted reduction.
+
+Expert weights are random N(0, 0.02) bf16 in the ``nn.Linear`` layout. The layer
+is the flagship workload of ``bench.py``; ``ref_moe_forward`` is its fp32 PyTorch
+oracle.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import gemm
+from ..ops.ep import EpBuffer
+from ..ops.quant import ref_dequant_1x128, ref_quant_1x128
+
+
+@dataclass
+class MoEConfig:
+    num_experts: int = 256
+    topk: int = 8
+    hidden: int = 7168
+    intermediate: int = 2048
+    renormalize: bool = False
+    init_std: float = 0.02
+
+
+def init_expert_weights(cfg: MoEConfig, experts: range, device, seed: int = 0):
+    """Weights of the given global experts: (w_gate_up [n, 2I, H], w_down [n, H, I]), bf16.
+
+    Expert ``e`` is drawn from its own generator seeded ``seed * 100003 + e`` so a rank's
+    shard equals the matching slice of the full set, whatever the world size.
+    """
+    n = len(experts)
+    w13 = torch.empty((n, 2 * cfg.intermediate, cfg.hidden), dtype=torch.bfloat16, device=device)
+    w2 = torch.empty((n, cfg.hidden, cfg.intermediate), dtype=torch.bfloat16, device=device)
+    gen = torch.Generator(device=device)
+    for i, e in enumerate(experts):
+        gen.manual_seed(seed * 100003 + e)
+        w13[i].copy_(torch.randn((2 * cfg.intermediate, cfg.hidden), generator=gen, device=device, dtype=torch.float32)
+                     .mul_(cfg.init_std))
+        w2[i].copy_(torch.randn((cfg.hidden, cfg.intermediate), generator=gen, device=device, dtype=torch.float32)
+                    .mul_(cfg.init_std))
+    return w13, w2
+
+
+class ExpertParallelMoE:
+    """One rank's shard of the MoE layer."""
+
+    def __init__(self, cfg: MoEConfig, max_tokens: int, *, group=None, seed: int = 0, buffer: EpBuffer | None = None,
+                 recv_cap: int | None = None):
+        self.cfg = cfg
+        self.buf = buffer or EpBuffer(cfg.num_experts, cfg.topk, cfg.hidden, max_tokens, group=group, recv_cap=recv_cap)
+        self.rank, self.world = self.buf.rank, self.buf.world
+        dev = self.buf.device
+        epr = self.buf.experts_per_rank
+        self.w_gate_up, self.w_down = init_expert_weights(cfg, range(self.rank * epr, (self.rank + 1) * epr), dev, seed)
+        cap = self.buf.recv_cap
+        self.xd = torch.empty((cap, cfg.hidden), dtype=torch.bfloat16, device=dev)
+        self.h = torch.empty((cap, cfg.intermediate), dtype=torch.bfloat16, device=dev)
+        self.max_tokens = max_tokens
+        self._bases = self.buf.scatter_bases()
+
+    # The steps are separate methods so that a single-GPU test can interleave ranks.
+    def step_route(self, logits, T, epoch):
+        self.buf.route(logits, T, epoch, self.cfg.renormalize)
+
+    def step_dispatch(self, x, epoch):
+        self.buf.dispatch(x, epoch)
+
+    def step_experts(self, T, epoch):
+        c = self.cfg
+        self.buf.recv_dequant(self.xd, epoch, expected_rows=min(self.buf.recv_cap, max(1, 2 * T * c.topk)))
+        gemm.grouped_gemm_bf16(self.xd, self.w_gate_up, self.buf.group_offsets, out=self.h, epilogue=gemm.EPI_SWIGLU)
+        gemm.grouped_gemm_bf16(self.h, self.w_down, self.buf.group_offsets, epilogue=gemm.EPI_SCATTER_ROWS,
+                               row_info=self.buf.recv_info, scatter_bases=self._bases,
+                               scatter_row_bytes=c.hidden * 2, scatter_slots=self.max_tokens * c.topk)
+
+    def step_combine(self, out, T, epoch, do_signal=True):
+        self.buf.combine_reduce(out, T, epoch, do_signal=do_signal)
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """x [T, hidden] bf16, router logits [T, num_experts] fp32 -> [T, hidden] bf16."""
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty_like(x)
+        e = self.buf.next_epoch()
+        self.step_route(logits, T, e)
+        self.step_dispatch(x, e)
+        self.step_experts(T, e)
+        self.step_combine(out, T, e)
+        return out
+
+    __call__ = forward
+
+
+def emulated_forward(layers: list[ExpertParallelMoE], xs, logits):
+    """Run one step of a whole emulated group on one GPU, phase by phase."""
+    outs = [torch.empty_like(x) for x in xs]
+    epochs = [layer.buf.next_epoch() for layer in layers]
+    for layer, x, lg, e in zip(layers, xs, logits, epochs):
+        layer.step_route(lg, x.shape[0], e)
+    for layer, x, e in zip(layers, xs, epochs):
+        layer.step_dispatch(x, e)
+    for layer, x, e in zip(layers, xs, epochs):
+        layer.step_experts(x.shape[0], e)
+    for layer, e in zip(layers, epochs):
+        layer.buf.signal(1, e)
+    for layer, x, out, e in zip(layers, xs, outs, epochs):
+        layer.step_combine(out, x.shape[0], e, do_signal=False)
+    return outs
+
+
+def ref_route(logits: torch.Tensor, topk: int, renormalize: bool = False):
+    probs = torch.softmax(logits.float(), dim=-1)
+    w, idx = torch.topk(probs, topk, dim=-1)
+    if renormalize:
+        w = w / w.sum(-1, keepdim=True)
+    return idx, w
+
+
+def ref_moe_forward(cfg: MoEConfig, x: torch.Tensor, logits: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor):
+    """fp32 restatement of the layer for ALL experts held in one place.
+
+    Mirrors the roundings of the kernels: fp8 1x128 quantisation of the token,
+    bf16 dequantised activations, bf16 intermediate and expert outputs, fp32
+    gate-weighted sum rounded once to bf16.
+    """
+    idx, w = ref_route(logits, cfg.topk, cfg.renormalize)
+    q, s = ref_quant_1x128(x)
+    xd = ref_dequant_1x128(q, s).to(torch.bfloat16).float()
+    out = torch.zeros_like(xd)
+    inter = cfg.intermediate
+    for e in range(cfg.num_experts):
+        sel = (idx == e)
+        tok = sel.any(-1).nonzero().flatten()
+        if tok.numel() == 0:
+            continue
+        xe = xd[tok]
+        g = xe @ w_gate_up[e, :inter].float().t()
+        u = xe @ w_gate_up[e, inter:].float().t()
+        h = (torch.nn.functional.silu(g) * u).to(torch.bfloat16).float()
+        y = (h @ w_down[e].float().t()).to(torch.bfloat16).float()
+        gate = (w[tok] * sel[tok]).sum(-1, keepdim=True)
+        out[tok] += gate * y
+    return out.to(torch.bfloat16), idx, w

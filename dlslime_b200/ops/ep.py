@@ -1,0 +1,219 @@
+"""Expert-parallel dispatch / combine buffers (``csrc/kernels/ep.cu``).
+
+``EpBuffer`` owns the symmetric memory one rank needs for a MoE layer: the count
+matrix, the packed fp8 receive buffers with scales and source info, the combine
+staging buffer and the flag words. The API follows the buffer pattern of the
+reference's removed all-to-all ops (``dlslime/csrc/python/bind.cpp:515-531``:
+construct, ``buffer_info()``, ``connect_full_mesh()``, then the low-latency op).
+"""
+
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass
+
+import torch
+
+from .. import _lib
+from ..parallel.symm import SymmetricHeap
+from ._common import default_status, ptr, stream_ptr
+
+_CFG_FMT = "<8i8Q8QQ"
+
+
+@dataclass
+class EpLayout:
+    off_counts: int
+    off_dispatch_done: int
+    off_combine_done: int
+    off_barrier: int
+    off_x: int
+    off_scale: int
+    off_info: int
+    off_combine: int
+    total: int
+
+
+def ep_layout(world: int, num_experts: int, topk: int, hidden: int, max_tokens: int, recv_cap: int) -> EpLayout:
+    cur = 0
+
+    def take(n):
+        nonlocal cur
+        off = (cur + 255) // 256 * 256
+        cur = off + n
+        return off
+
+    return EpLayout(
+        off_counts=take(8 * world * num_experts),
+        off_dispatch_done=take(8 * 8),
+        off_combine_done=take(8 * 8),
+        off_barrier=take(8 * 8),
+        off_x=take(recv_cap * hidden),
+        off_scale=take(recv_cap * (hidden // 128) * 4),
+        off_info=take(recv_cap * 8),
+        off_combine=take(max_tokens * topk * hidden * 2),
+        total=(cur + 255) // 256 * 256,
+    )
+
+
+class EpBuffer:
+    """Per-rank state of the dispatch/combine protocol.
+
+    Parameters
+    ----------
+    num_experts, topk, hidden : model shape (hidden must be a multiple of 512).
+    max_tokens : largest number of tokens this rank dispatches in one step.
+    recv_cap : rows of the packed receive buffer; defaults to the worst case
+        ``world * max_tokens * min(topk, experts_per_rank)`` so no step can overflow.
+    heap : an existing :class:`SymmetricHeap` to carve from (else one is created
+        over ``group``).
+    """
+
+    def __init__(self, num_experts: int, topk: int, hidden: int, max_tokens: int, *, group=None,
+                 recv_cap: int | None = None, heap: SymmetricHeap | None = None, rank: int | None = None,
+                 base_off: int | None = None, wait_ns: int = 0):
+        if heap is None:
+            import torch.distributed as dist
+
+            world = dist.get_world_size(group) if dist.is_initialized() else 1
+            epr = num_experts // world
+            cap = recv_cap or world * max_tokens * min(topk, epr)
+            lay = ep_layout(world, num_experts, topk, hidden, max_tokens, cap)
+            heap = SymmetricHeap(lay.total, group=group)
+            self._own_heap = True
+        else:
+            self._own_heap = False
+        self.heap = heap
+        self.world = heap.world
+        self.rank = heap.rank if rank is None else rank
+        self.num_experts, self.topk, self.hidden, self.max_tokens = num_experts, topk, hidden, max_tokens
+        assert num_experts % self.world == 0 and hidden % 512 == 0 and topk <= 8 and self.world <= 8
+        self.experts_per_rank = num_experts // self.world
+        self.recv_cap = recv_cap or self.world * max_tokens * min(topk, self.experts_per_rank)
+        self.layout = ep_layout(self.world, num_experts, topk, hidden, max_tokens, self.recv_cap)
+        self.base_off = heap.reserve(self.layout.total) if base_off is None else base_off
+        self.wait_ns = wait_ns
+        self.epoch = 0
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.device = dev
+        # rank-local scratch
+        self.topk_idx = torch.empty((max_tokens, topk), dtype=torch.int32, device=dev)
+        self.topk_w = torch.empty((max_tokens, topk), dtype=torch.float32, device=dev)
+        self.slot = torch.empty((max_tokens, topk), dtype=torch.int32, device=dev)
+        self.send_count = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self.block_counters = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.group_offsets = torch.zeros(self.experts_per_rank + 1, dtype=torch.int32, device=dev)
+        self._cfg = self._pack_cfg()
+        self.status = default_status()
+
+    # -- config ------------------------------------------------------------------
+    def _pack_cfg(self) -> bytes:
+        L, b = self.layout, self.base_off
+        peers = list(self.heap.peer_ptrs) + [0] * (8 - self.world)
+        return struct.pack(
+            _CFG_FMT, self.rank, self.world, self.num_experts, self.experts_per_rank, self.topk, self.hidden,
+            self.max_tokens, self.recv_cap,
+            b + L.off_counts, b + L.off_dispatch_done, b + L.off_combine_done, b + L.off_barrier,
+            b + L.off_x, b + L.off_scale, b + L.off_info, b + L.off_combine, *peers, self.wait_ns)
+
+    @classmethod
+    def emulated_group(cls, world: int, num_experts: int, topk: int, hidden: int, max_tokens: int,
+                       recv_cap: int | None = None, wait_ns: int = 0) -> list["EpBuffer"]:
+        """``world`` buffers on ONE device that address each other like ranks on separate GPUs.
+
+        Meant for single-GPU tests: run each protocol step for every rank before the next
+        step, so that every wait finds its flag already published.
+        """
+        epr = num_experts // world
+        cap = recv_cap or world * max_tokens * min(topk, epr)
+        lay = ep_layout(world, num_experts, topk, hidden, max_tokens, cap)
+        heap = SymmetricHeap.emulated(world, lay.total)
+        off = heap.reserve(lay.total)
+        return [cls(num_experts, topk, hidden, max_tokens, recv_cap=cap, heap=heap, rank=r, base_off=off, wait_ns=wait_ns)
+                for r in range(world)]
+
+    def buffer_info(self) -> dict:
+        return self.heap.export_info()
+
+    def connect_full_mesh(self, infos) -> None:
+        self.heap.connect(infos)
+        self._cfg = self._pack_cfg()
+
+    # -- views into this rank's region ----------------------------------------------
+    def _view(self, off, shape, dtype):
+        return self.heap.view(self.base_off + off, shape, dtype, rank=self.rank)
+
+    @property
+    def recv_x(self) -> torch.Tensor:
+        return self._view(self.layout.off_x, (self.recv_cap, self.hidden), torch.float8_e4m3fn)
+
+    @property
+    def recv_scale(self) -> torch.Tensor:
+        return self._view(self.layout.off_scale, (self.recv_cap, self.hidden // 128), torch.float32)
+
+    @property
+    def recv_info(self) -> torch.Tensor:
+        return self._view(self.layout.off_info, (self.recv_cap,), torch.int64)
+
+    @property
+    def combine_buf(self) -> torch.Tensor:
+        return self._view(self.layout.off_combine, (self.max_tokens * self.topk, self.hidden), torch.bfloat16)
+
+    def scatter_bases(self):
+        """Base address of every rank's combine buffer (for the GEMM scatter epilogue)."""
+        import ctypes
+
+        arr = (ctypes.c_ulonglong * 8)()
+        for r in range(self.world):
+            arr[r] = self.heap.peer_ptrs[r] + self.base_off + self.layout.off_combine
+        return arr
+
+    # -- protocol steps -----------------------------------------------------------------
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def route(self, logits: torch.Tensor | None, T: int, epoch: int, renormalize: bool = False) -> None:
+        """Top-k routing (or counting of caller-provided ``topk_idx``) and count broadcast."""
+        _lib.call("slime_ep_route", self._cfg, ptr(logits), T, ptr(self.topk_idx), ptr(self.topk_w), ptr(self.slot),
+                  ptr(self.send_count), self.block_counters[0:].data_ptr(), epoch, int(renormalize), stream_ptr())
+
+    def dispatch(self, x: torch.Tensor, epoch: int, max_blocks: int = 0) -> None:
+        """Quantise ``x`` [T, hidden] bf16 to fp8 and push every (token, expert) copy to its owner."""
+        T = x.shape[0]
+        assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.shape[1] == self.hidden
+        _lib.call("slime_ep_dispatch", self._cfg, ptr(x), x.stride(0), T, ptr(self.topk_idx), ptr(self.slot),
+                  ptr(self.group_offsets), self.block_counters[1:].data_ptr(), epoch, max_blocks,
+                  self.status.dev_ptr, stream_ptr())
+
+    def recv_dequant(self, out: torch.Tensor, epoch: int, expected_rows: int) -> None:
+        """Wait for every rank's rows, then expand the packed fp8 rows to bf16 ``out`` [recv_cap, hidden]."""
+        _lib.call("slime_ep_recv_dequant", self._cfg, ptr(self.group_offsets), ptr(out), out.stride(0), expected_rows,
+                  epoch, self.status.dev_ptr, stream_ptr())
+
+    def combine_push(self, y: torch.Tensor, expected_rows: int) -> None:
+        _lib.call("slime_ep_combine_push", self._cfg, ptr(y), y.stride(0), ptr(self.group_offsets), expected_rows,
+                  self.status.dev_ptr, stream_ptr())
+
+    def signal(self, which: int, epoch: int) -> None:
+        _lib.call("slime_ep_signal", self._cfg, which, epoch, stream_ptr())
+
+    def combine_reduce(self, out: torch.Tensor, T: int, epoch: int, do_signal: bool = True) -> None:
+        _lib.call("slime_ep_combine_reduce", self._cfg, T, ptr(self.topk_idx), ptr(self.topk_w), ptr(out), out.stride(0),
+                  epoch, int(do_signal), self.status.dev_ptr, stream_ptr())
+
+    def barrier(self, epoch: int) -> None:
+        _lib.call("slime_ep_barrier", self._cfg, epoch, self.status.dev_ptr, stream_ptr())
+
+
+_lib.declare("slime_ep_config_size", [])
+import ctypes as _ct  # noqa: E402
+
+_v, _i, _ll, _ull = _ct.c_void_p, _ct.c_int, _ct.c_longlong, _ct.c_ulonglong
+_lib.declare("slime_ep_route", [_ct.c_char_p, _v, _i, _v, _v, _v, _v, _v, _ull, _i, _v])
+_lib.declare("slime_ep_dispatch", [_ct.c_char_p, _v, _ll, _i, _v, _v, _v, _v, _ull, _i, _v, _v])
+_lib.declare("slime_ep_recv_dequant", [_ct.c_char_p, _v, _v, _ll, _i, _ull, _v, _v])
+_lib.declare("slime_ep_combine_push", [_ct.c_char_p, _v, _ll, _v, _i, _v, _v])
+_lib.declare("slime_ep_signal", [_ct.c_char_p, _i, _ull, _v])
+_lib.declare("slime_ep_combine_reduce", [_ct.c_char_p, _i, _v, _v, _v, _ll, _ull, _i, _v, _v])
+_lib.declare("slime_ep_barrier", [_ct.c_char_p, _ull, _v, _v])

@@ -29,7 +29,8 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None)
 
 
 def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor, out: torch.Tensor | None = None,
-                      epilogue: int = EPI_STORE, row_dst: torch.Tensor | None = None,
+                      epilogue: int = EPI_STORE, row_info: torch.Tensor | None = None, scatter_bases=None,
+                      scatter_row_bytes: int = 0, scatter_slots: int = 0,
                       row_scale: torch.Tensor | None = None) -> torch.Tensor | None:
     """Grouped GEMM over consecutive row groups of ``a``.
 
@@ -37,6 +38,10 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
     ``G + 1`` row prefixes (rows past ``group_offsets[G]`` are ignored); ``b`` is
     ``[G, N, K]`` (``[G, 2N, K]`` with gate rows before up rows for SwiGLU).
     The group sizes never leave the device, so there is no host synchronisation.
+
+    With ``EPI_SCATTER_ROWS`` nothing is written to ``out``: result row ``r`` is stored at
+    ``scatter_bases[info >> 48] + (info & (2**48 - 1)) * scatter_row_bytes`` with
+    ``info = row_info[r]`` (int64 device tensor); the regions may live on peer GPUs.
     """
     require_cuda(a, b, group_offsets)
     assert a.dtype == b.dtype == torch.bfloat16 and group_offsets.dtype == torch.int32
@@ -49,5 +54,6 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
         out = torch.empty((m_cap, n), dtype=torch.bfloat16, device=a.device)
     ldc = out.stride(0) if out is not None else n
     _lib.call("slime_grouped_gemm_bf16", ptr(a), ptr(b), ptr(out), ptr(group_offsets), g, m_cap, n, k, a.stride(0), k,
-              ldc, epilogue, ptr(row_dst), ptr(row_scale), default_status().dev_ptr, stream_ptr())
+              ldc, epilogue, ptr(row_info), scatter_bases, scatter_row_bytes, scatter_slots, ptr(row_scale),
+              default_status().dev_ptr, stream_ptr())
     return out

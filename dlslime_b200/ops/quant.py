@@ -59,7 +59,7 @@ def fp8_quant_128x128(w: torch.Tensor):
 def ref_quant_1x128(x: torch.Tensor):
     xf = x.float().reshape(x.shape[0], -1, 128)
     amax = xf.abs().amax(dim=-1).clamp_min(AMAX_FLOOR)
-    scale = amax / FP8_MAX
+    scale = amax / torch.full_like(amax, FP8_MAX)  # tensor / tensor: IEEE division, not a reciprocal multiply
     q = (xf / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     return q.reshape(x.shape), scale
 
@@ -76,6 +76,6 @@ def ref_quant_128x128(w: torch.Tensor):
     wf[:rows, :cols] = w.float()
     blocks = wf.reshape(pr // 128, 128, pc // 128, 128)
     amax = blocks.abs().amax(dim=(1, 3)).clamp_min(AMAX_FLOOR)
-    scale = amax / FP8_MAX
+    scale = amax / torch.full_like(amax, FP8_MAX)
     q = (blocks / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     return q.reshape(pr, pc)[:rows, :cols].contiguous(), scale

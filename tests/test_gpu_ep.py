@@ -1,0 +1,101 @@
+"""Expert-parallel dispatch / expert FFN / combine against the fp32 oracle.
+
+Multi-rank protocols are replayed on ONE GPU: every rank gets its own symmetric
+region on the same device and the steps run phase by phase.
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_group(world, tokens, cfg):
+    from dlslime_b200.models.moe import ExpertParallelMoE, emulated_forward, init_expert_weights, ref_moe_forward
+    from dlslime_b200.ops.ep import EpBuffer
+    from dlslime_b200.ops._common import default_status
+
+    max_tokens = max(max(tokens), 1)
+    bufs = EpBuffer.emulated_group(world, cfg.num_experts, cfg.topk, cfg.hidden, max_tokens)
+    layers = [ExpertParallelMoE(cfg, max_tokens, buffer=b, seed=3) for b in bufs]
+    w13, w2 = init_expert_weights(cfg, range(cfg.num_experts), "cuda", seed=3)
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    for step in range(2):  # two steps: flags and counters must be reusable
+        xs = [torch.randn((t, cfg.hidden), generator=gen, device="cuda").to(torch.bfloat16) for t in tokens]
+        lgs = [torch.randn((t, cfg.num_experts), generator=gen, device="cuda") for t in tokens]
+        outs = emulated_forward(layers, xs, lgs)
+        torch.cuda.synchronize()
+        default_status().check()
+        for r in range(world):
+            if tokens[r] == 0:
+                continue
+            ref, idx, w = ref_moe_forward(cfg, xs[r], lgs[r], w13, w2)
+            got_idx = layers[r].buf.topk_idx[:tokens[r]].long()
+            assert torch.equal(got_idx, idx), "top-k selection differs from torch.topk"
+            assert torch.allclose(layers[r].buf.topk_w[:tokens[r]], w, rtol=1e-5, atol=1e-7)
+            err = (outs[r].float() - ref.float()).abs()
+            tol = ref.float().abs() * 2 ** -6 + ref.float().abs().mean() * 2 ** -5
+            assert (err <= tol).all(), f"rank {r} step {step}: max err {err.max().item()} (ref mean {ref.float().abs().mean().item()})"
+        # packed rows: every rank received exactly the rows routed to its experts
+        total = sum(int(layers[r].buf.group_offsets[-1].item()) for r in range(world))
+        assert total == sum(tokens) * cfg.topk
+
+
+@pytest.mark.parametrize("world,tokens", [(1, [37]), (2, [17, 3]), (4, [1, 0, 64, 130]), (8, [5, 6, 7, 8, 9, 10, 11, 12])])
+def test_moe_layer_emulated_group(world, tokens):
+    from dlslime_b200.models.moe import MoEConfig
+
+    cfg = MoEConfig(num_experts=32, topk=4, hidden=1024, intermediate=256)
+    _run_group(world, tokens, cfg)
+
+
+def test_dispatch_payload_bit_exact():
+    """Rows that land in the owner's packed buffer carry exactly the reference fp8 bytes and scales."""
+    from dlslime_b200.models.moe import ref_route
+    from dlslime_b200.ops.ep import EpBuffer
+    from dlslime_b200.ops.quant import ref_quant_1x128
+    from dlslime_b200.ops._common import default_status
+
+    world, E, K, H, T = 2, 16, 2, 512, 50
+    bufs = EpBuffer.emulated_group(world, E, K, H, T)
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    xs = [torch.randn((T, H), generator=gen, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    lgs = [torch.randn((T, E), generator=gen, device="cuda") for _ in range(world)]
+    for b, lg in zip(bufs, lgs):
+        b.route(lg, T, 1)
+    for b, x in zip(bufs, xs):
+        b.dispatch(x, 1)
+    torch.cuda.synchronize()
+    default_status().check()
+    epr = E // world
+    for r, b in enumerate(bufs):
+        offs = b.group_offsets.tolist()
+        info = b.recv_info[:offs[-1]]
+        src, slot = (info >> 48).tolist(), (info & ((1 << 48) - 1)).tolist()
+        for j in range(epr):
+            for row in range(offs[j], offs[j + 1]):
+                s, t, k = src[row], slot[row] // K, slot[row] % K
+                idx, _ = ref_route(lgs[s], K)
+                assert idx[t, k].item() == r * epr + j
+                q, sc = ref_quant_1x128(xs[s][t:t + 1])
+                assert torch.equal(b.recv_x[row].view(torch.uint8), q[0].view(torch.uint8))
+                assert torch.equal(b.recv_scale[row], sc[0])
+        # rows of one expert are grouped by source rank in rank order
+        for j in range(epr):
+            seg = src[offs[j]:offs[j + 1]]
+            assert seg == sorted(seg)
+
+
+def test_wait_times_out_instead_of_hanging():
+    """A count row that never arrives makes dispatch give up after its limit and report TIME_OUT."""
+    from dlslime_b200.ops.ep import EpBuffer
+    from dlslime_b200.ops._common import KernelTimeout, default_status
+
+    bufs = EpBuffer.emulated_group(2, 16, 2, 512, 8, wait_ns=20_000_000)  # 20 ms limit
+    x = torch.randn((8, 512), device="cuda").to(torch.bfloat16)
+    lg = torch.randn((8, 16), device="cuda")
+    bufs[0].route(lg, 8, 1)  # rank 1 never publishes its counts
+    bufs[0].dispatch(x, 1)
+    torch.cuda.synchronize()
+    with pytest.raises(KernelTimeout):
+        default_status().check()
+    default_status().check()  # the page is cleared after reporting

@@ -81,10 +81,15 @@ def test_grouped_gemm_scatter_rows():
     w = (torch.randn(g, n, k, device="cuda") * 0.05).to(torch.bfloat16)
     dst = torch.zeros(total, n, device="cuda", dtype=torch.bfloat16)
     perm = torch.randperm(total, device="cuda")
-    row_dst = dst.data_ptr() + perm.to(torch.int64) * (n * 2)
-    row_dst[3] = 0  # dropped row
+    import ctypes
+
+    row_info = perm.to(torch.int64).clone()  # region 0, slot = destination row
+    row_info[3] = -1  # dropped row (region index out of range)
+    bases = (ctypes.c_ulonglong * 8)()
+    bases[0] = dst.data_ptr()
     scale = torch.rand(total, device="cuda") + 0.5
-    gemm.grouped_gemm_bf16(a, w, offs, epilogue=gemm.EPI_SCATTER_ROWS, row_dst=row_dst, row_scale=scale)
+    gemm.grouped_gemm_bf16(a, w, offs, epilogue=gemm.EPI_SCATTER_ROWS, row_info=row_info, scatter_bases=bases,
+                           scatter_row_bytes=n * 2, scatter_slots=total, row_scale=scale)
     torch.cuda.synchronize()
     default_status().check()
     ref = torch.zeros(total, n, device="cuda")
