@@ -1,0 +1,301 @@
+#!/usr/bin/env python
+"""Headline benchmark: DeepSeek-V3-shaped expert-parallel MoE dispatch + combine.
+
+    python bench.py --gpus N --steps K --warmup W [--mode ll|normal] [--impl ours|reference]
+
+One step is a full MoE layer forward on every rank: top-8 routing of T tokens
+over 256 experts, dispatch with fp8 e4m3 1x128 quantisation, the grouped SwiGLU
+expert FFN (hidden 7168, intermediate 2048, bf16 weights N(0, 0.02)) and the
+gate-weighted bf16 combine. ``--mode ll`` uses T = 128 tokens per rank (decode),
+``--mode normal`` T = 4096 (prefill). Inputs are synthetic and seeded, weights
+random-init. Timing is CUDA events on the launching stream, max over ranks,
+after warm-up, bracketed by a barrier and a device synchronise.
+
+The line printed by rank 0 reports the step latency in microseconds (the whole
+layer, nothing skipped), the end-to-end figure through the public API including
+the pinned host->device copy of the step's inputs and the device->host read of
+its output, aggregate tokens/s, the NVLink payload rate per rank, and the SM
+clocks sampled during the timed region.
+
+``--impl reference`` runs the same workload with the unmodified reference package
+installed under ``baseline/_ref``: its ``NVLinkEndpoint.read`` moves the token
+rows (the only NVLink path it has), NCCL carries the counts, and torch / cuBLAS do
+the quantisation, expert FFN and weighted sum, the way a user of the reference
+would compose them.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+E, TOPK, HIDDEN, INTER = 256, 8, 7168, 2048
+T_MODE = {"ll": 128, "normal": 4096}
+
+
+# ---------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------
+# distributed plumbing
+# ---------------------------------------------------------------------------------
+def init_dist(n_gpus: int):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != n_gpus:
+        if world == 1 and n_gpus > 1:
+            # re-launch under torchrun, one rank per GPU
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n_gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 2000), *sys.argv]
+            raise SystemExit(subprocess.call(cmd))
+        raise SystemExit(f"WORLD_SIZE={world} does not match --gpus {n_gpus}")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def max_over_ranks(value: float, world: int) -> float:
+    import torch
+    import torch.distributed as dist
+
+    if world == 1:
+        return value
+    t = torch.tensor([value], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sync_all(world: int):
+    import torch
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def make_inputs(T: int, rank: int, steps: int):
+    """Pinned host inputs for `steps` distinct steps (seeded per rank and step)."""
+    import torch
+
+    xs, lgs = [], []
+    for s in range(steps):
+        g = torch.Generator().manual_seed(1000 * rank + s)
+        xs.append(torch.randn((T, HIDDEN), generator=g).to(torch.bfloat16).pin_memory())
+        lgs.append(torch.randn((T, E), generator=g).pin_memory())
+    return xs, lgs
+
+
+# ---------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------
+def run_ours(args, rank, world, local):
+    import torch
+
+    from dlslime_b200.models.moe import ExpertParallelMoE, MoEConfig
+
+    T = T_MODE[args.mode]
+    cfg = MoEConfig(num_experts=E, topk=TOPK, hidden=HIDDEN, intermediate=INTER)
+    layer = ExpertParallelMoE(cfg, max_tokens=T, seed=0)
+    n_in = min(4, max(1, args.steps))
+    host_x, host_lg = make_inputs(T, rank, n_in)
+    dev_x = [h.cuda() for h in host_x]
+    dev_lg = [h.cuda() for h in host_lg]
+    out = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device="cuda")
+    host_out = torch.empty((T, HIDDEN), dtype=torch.bfloat16).pin_memory()
+    x_stage = torch.empty_like(dev_x[0])
+    lg_stage = torch.empty_like(dev_lg[0])
+
+    def step_device(i):
+        layer.forward(dev_x[i % n_in], dev_lg[i % n_in], out=out)
+
+    def step_e2e(i):
+        x_stage.copy_(host_x[i % n_in], non_blocking=True)
+        lg_stage.copy_(host_lg[i % n_in], non_blocking=True)
+        layer.forward(x_stage, lg_stage, out=out)
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result every step
+
+    def timed(fn):
+        for i in range(args.warmup):
+            fn(i)
+        sync_all(world)
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for i in range(args.steps):
+            fn(i)
+        ev1.record()
+        sync_all(world)
+        clocks = sampler.stop() if rank == 0 else None
+        ms = ev0.elapsed_time(ev1) / args.steps
+        layer.buf.status.check()
+        return max_over_ranks(ms, world), clocks
+
+    ms_dev, clocks = timed(step_device)
+    ms_e2e, _ = timed(step_e2e)
+
+    # phase breakdown (one extra instrumented pass; not part of the reported value)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+    sync_all(world)
+    e = layer.buf.next_epoch()
+    evs[0].record()
+    layer.step_route(dev_lg[0], T, e)
+    evs[1].record()
+    layer.step_dispatch(dev_x[0], e)
+    evs[2].record()
+    layer.step_experts(T, e)
+    evs[3].record()
+    layer.step_combine(out, T, e)
+    evs[4].record()
+    sync_all(world)
+    names = ["route", "dispatch", "experts_ffn_and_combine_push", "combine_reduce"]
+    breakdown = {n: round(max_over_ranks(evs[i].elapsed_time(evs[i + 1]) * 1e3, world), 1) for i, n in enumerate(names)}
+
+    weights_gb = (layer.w_gate_up.numel() + layer.w_down.numel()) * 2 / 1e9
+    remote_frac = (world - 1) / world
+    nvlink_bytes = T * TOPK * (HIDDEN + HIDDEN // 128 * 4 + 8) * remote_frac + T * TOPK * HIDDEN * 2 * remote_frac
+    return {
+        "ms_dev": ms_dev, "ms_e2e": ms_e2e, "clocks": clocks, "breakdown_us": breakdown, "T": T,
+        "h2d": host_x[0].numel() * 2 + host_lg[0].numel() * 4, "d2h": host_out.numel() * 2,
+        "launches": 6 * args.steps, "weights_gb": weights_gb, "nvlink_bytes_per_rank": nvlink_bytes,
+    }
+
+
+# ---------------------------------------------------------------------------------
+# reference arm
+# ---------------------------------------------------------------------------------
+def run_reference(args, rank, world, local):
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "dlslime")):
+        return {"unavailable": "baseline/_ref is not installed (pip install --target baseline/_ref of the reference has not been run)"}
+    from baseline.reference_arm import run as run_ref_arm
+
+    return run_ref_arm(args, rank, world, local, T_MODE[args.mode], make_inputs, sync_all, max_over_ranks, ClockSampler)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--mode", choices=["ll", "normal"], default="normal")
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device visible"}))
+        return 0
+    rank, world, local = init_dist(args.gpus)
+    res = run_ours(args, rank, world, local) if args.impl == "ours" else run_reference(args, rank, world, local)
+    if "unavailable" in res:
+        if rank == 0:
+            print(json.dumps({"impl": args.impl, "unavailable": res["unavailable"]}))
+        return 0
+    T = res["T"]
+    us = res["ms_dev"] * 1e3
+    line = {
+        "metric": "EP dispatch+combine latency (us) [full MoE layer step: dispatch+fp8 quant -> grouped SwiGLU FFN -> combine]",
+        "value": round(us, 2), "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(res["ms_dev"], 5), "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 (fp8 e4m3 1x128 on the wire)", "data": "synthetic", "impl": args.impl,
+        "tokens_per_s": round(world * T / (res["ms_dev"] * 1e-3), 1),
+        "nvlink_gbs_per_rank": round(res["nvlink_bytes_per_rank"] / (res["ms_dev"] * 1e-3) / 1e9, 2),
+        "config": {
+            "model": "DeepSeek-V3-shaped MoE layer: 256 experts, top-8, hidden 7168, intermediate 2048",
+            "mode": args.mode, "tokens_per_rank": T, "global_batch": world * T, "seq_len": 1,
+            "parallelism": f"ep{world}", "experts_per_rank": E // world,
+            "l2": f"inputs larger than L2: {res['weights_gb']:.1f} GB of expert weights per rank are streamed every step",
+        },
+        "e2e": {"value": round(res["ms_e2e"] * 1e3, 2), "unit": "us", "h2d_bytes_per_step": res["h2d"],
+                "d2h_bytes_per_step": res["d2h"],
+                "tokens_per_s": round(world * T / (res["ms_e2e"] * 1e-3), 1)},
+        "gpu_launches": res["launches"],
+        "clocks": res["clocks"],
+        "breakdown_us": res.get("breakdown_us"),
+    }
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

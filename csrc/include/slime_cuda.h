@@ -85,6 +85,28 @@ int slime_ep_combine_reduce(const void* cfg_bytes, int T, const int* topk_idx, c
                             long long ldo, unsigned long long epoch, int do_signal, void* status, void* stream);
 int slime_ep_barrier(const void* cfg_bytes, unsigned long long epoch, void* status, void* stream);
 
+// ---- NVLink endpoint (nvlink_endpoint.cu) -----------------------------------
+void* slime_nvlink_ep_create(void);
+int   slime_nvlink_ep_destroy(void* ep);
+int   slime_nvlink_ep_register(void* ep, unsigned long long addr, unsigned long long length, const char* name);
+int   slime_nvlink_ep_unregister(void* ep, int handle);
+int   slime_nvlink_ep_local_info(void* ep, int handle, unsigned char* ipc_out64, unsigned long long* offset,
+                                 unsigned long long* addr, unsigned long long* length);
+int   slime_nvlink_ep_register_remote(void* ep, const char* name, const unsigned char* ipc64, unsigned long long offset,
+                                      unsigned long long length, unsigned long long addr, int same_process);
+int   slime_nvlink_ep_handle(void* ep, const char* name, int remote);
+unsigned long long slime_nvlink_ep_remote_addr(void* ep, int handle);
+// tuples: n x {local_handle, remote_handle, remote_offset, local_offset, length} as u64.
+int slime_nvlink_ep_transfer(void* ep, const unsigned long long* tuples, int n, int is_write, void* signal,
+                             unsigned long long signal_value, int signal_add, int max_blocks, void* stream);
+
+// ---- low-latency all-gather (allgather.cu) -----------------------------------
+int slime_ag_config_size(void);
+int slime_ag_push(const void* cfg_bytes, const void* src, unsigned long long bytes, unsigned long long stride_bytes,
+                  unsigned long long step, unsigned int* block_counter, int do_wait, int max_blocks, void* status,
+                  void* stream);
+int slime_ag_wait(const void* cfg_bytes, unsigned long long step, void* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

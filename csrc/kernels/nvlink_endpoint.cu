@@ -1,0 +1,398 @@
+// NVLink endpoint: memory-region registry over CUDA IPC plus ONE kernel that moves
+// a whole batch of (local offset, remote offset, length) segments between this
+// GPU and peer GPUs. Counterpart of the reference's NVLinkEndpoint / NVLinkMemoryPool
+// (dlslime/csrc/engine/nvlink/nvlink_endpoint.h:22-47, memory_pool.cpp:19-153 in the
+// reference), which issues one cudaMemcpyAsync per segment and can only read. Here a
+// batch is one launch, both directions exist, and a completion word (local, remote
+// or mapped host memory) can be published when the last byte has landed, which is
+// what write_with_imm / imm_recv are built from.
+//
+// Work is cut into 64 KiB units over all segments; persistent CTAs walk the units.
+// Aligned units move as 16-byte vectors with eight loads in flight per thread;
+// ragged heads and tails fall back to bytes.
+#include <algorithm>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "common/host_utils.h"
+#include "common/ptx.cuh"
+#include "slime_cuda.h"
+
+using namespace slime;
+
+namespace {
+
+constexpr unsigned long long kUnitBytes  = 64ull << 10;
+constexpr int                kInlineSegs = 8;
+constexpr int                kThreads    = 256;
+
+struct Segment {
+    unsigned long long dst;
+    unsigned long long src;
+    unsigned long long len;
+    unsigned long long first_unit;  // index of this segment's first unit in the batch
+};
+
+struct InlineBatch {
+    Segment seg[kInlineSegs];
+};
+
+struct CopyArgs {
+    const Segment*      table;  // device table, or nullptr when `inl` is used
+    int                 n_seg;
+    unsigned long long  n_units;
+    unsigned long long* signal;  // optional completion word
+    unsigned long long  signal_value;
+    int                 signal_add;
+    unsigned int*       block_counter;
+};
+
+__device__ __forceinline__ void copy_unit(unsigned char* dst, const unsigned char* src, unsigned long long n)
+{
+    const unsigned long long mis = (reinterpret_cast<unsigned long long>(dst) | reinterpret_cast<unsigned long long>(src)) & 15;
+    if (mis == 0) {
+        const unsigned long long nv = n >> 4;
+        const uint4*             s  = reinterpret_cast<const uint4*>(src);
+        uint4*                   d  = reinterpret_cast<uint4*>(dst);
+        unsigned long long       i  = threadIdx.x;
+        for (; i + 7ull * kThreads < nv; i += 8ull * kThreads) {
+            uint4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = s[i + j * kThreads];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) d[i + j * kThreads] = v[j];
+        }
+        for (; i < nv; i += kThreads) d[i] = s[i];
+        for (unsigned long long b = (nv << 4) + threadIdx.x; b < n; b += kThreads) dst[b] = src[b];
+    }
+    else if (((reinterpret_cast<unsigned long long>(dst) ^ reinterpret_cast<unsigned long long>(src)) & 15) == 0) {
+        // same misalignment on both sides: byte head, vector body, byte tail
+        unsigned long long head = 16 - (reinterpret_cast<unsigned long long>(dst) & 15);
+        if (head > n) head = n;
+        for (unsigned long long b = threadIdx.x; b < head; b += kThreads) dst[b] = src[b];
+        const unsigned long long nv = (n - head) >> 4;
+        const uint4*             s  = reinterpret_cast<const uint4*>(src + head);
+        uint4*                   d  = reinterpret_cast<uint4*>(dst + head);
+        for (unsigned long long i = threadIdx.x; i < nv; i += kThreads) d[i] = s[i];
+        for (unsigned long long b = head + (nv << 4) + threadIdx.x; b < n; b += kThreads) dst[b] = src[b];
+    }
+    else {
+        for (unsigned long long b = threadIdx.x; b < n; b += kThreads) dst[b] = src[b];
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) p2p_scatter_gather_kernel(CopyArgs a, InlineBatch inl)
+{
+    __shared__ Segment s_seg;
+    for (unsigned long long u = blockIdx.x; u < a.n_units; u += gridDim.x) {
+        if (threadIdx.x == 0) {
+            // binary search for the segment that owns unit u
+            int lo = 0, hi = a.n_seg - 1;
+            while (lo < hi) {
+                const int                mid = (lo + hi + 1) >> 1;
+                const unsigned long long fu  = a.table ? a.table[mid].first_unit : inl.seg[mid].first_unit;
+                if (fu <= u)
+                    lo = mid;
+                else
+                    hi = mid - 1;
+            }
+            s_seg = a.table ? a.table[lo] : inl.seg[lo];
+        }
+        __syncthreads();
+        const unsigned long long off = (u - s_seg.first_unit) * kUnitBytes;
+        const unsigned long long n   = min(kUnitBytes, s_seg.len - off);
+        copy_unit(reinterpret_cast<unsigned char*>(s_seg.dst + off), reinterpret_cast<const unsigned char*>(s_seg.src + off), n);
+        __syncthreads();
+    }
+    if (a.signal != nullptr) {
+        __shared__ bool is_last;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            fence_acq_rel_sys();
+            is_last = atomicAdd(a.block_counter, 1u) == gridDim.x - 1;
+            if (is_last) {
+                fence_acq_rel_sys();
+                if (a.signal_add)
+                    red_add_release_sys(a.signal, a.signal_value);
+                else
+                    st_release_sys(a.signal, a.signal_value);
+                *a.block_counter = 0;
+            }
+        }
+    }
+}
+
+struct Region {
+    std::string        name;
+    unsigned long long addr   = 0;  // usable address in this process (already includes offset)
+    unsigned long long offset = 0;  // offset of addr inside its allocation (exported with the handle)
+    unsigned long long length = 0;
+    unsigned char      ipc[64];
+    void*              mapped_base = nullptr;  // remote only: what cudaIpcOpenMemHandle returned
+    bool               alive       = false;
+};
+
+struct StagingSlot {
+    Segment*    host = nullptr;
+    Segment*    dev  = nullptr;
+    cudaEvent_t done = nullptr;
+};
+
+constexpr int kStagingSlots   = 8;
+constexpr int kStagingEntries = 1 << 16;
+
+struct Endpoint {
+    std::mutex                 mu;
+    std::vector<Region>        local, remote;
+    std::map<std::string, int> local_by_name, remote_by_name;
+    std::map<std::string, void*> opened;  // ipc handle bytes -> mapped base (one open per allocation)
+    StagingSlot                slots[kStagingSlots];
+    int                        next_slot = 0;
+    unsigned int*              counters  = nullptr;  // one block counter per staging slot
+    int                        next_counter = 0;
+    int                        device = 0;
+};
+
+int ensure_staging(Endpoint* ep)
+{
+    if (ep->counters) return 0;
+    SLIME_CUDA_OK(cudaGetDevice(&ep->device));
+    SLIME_CUDA_OK(cudaMalloc(&ep->counters, sizeof(unsigned int) * 64));
+    SLIME_CUDA_OK(cudaMemset(ep->counters, 0, sizeof(unsigned int) * 64));
+    return 0;
+}
+
+int ensure_slot(StagingSlot& s)
+{
+    if (s.host) return 0;
+    SLIME_CUDA_OK(cudaHostAlloc(reinterpret_cast<void**>(&s.host), sizeof(Segment) * kStagingEntries, cudaHostAllocPortable));
+    SLIME_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&s.dev), sizeof(Segment) * kStagingEntries));
+    SLIME_CUDA_OK(cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+void* slime_nvlink_ep_create(void)
+{
+    return new Endpoint();
+}
+
+int slime_nvlink_ep_destroy(void* h)
+{
+    Endpoint* ep = static_cast<Endpoint*>(h);
+    if (!ep) return 0;
+    for (auto& kv : ep->opened) cudaIpcCloseMemHandle(kv.second);
+    for (auto& s : ep->slots) {
+        if (s.host) cudaFreeHost(s.host);
+        if (s.dev) cudaFree(s.dev);
+        if (s.done) cudaEventDestroy(s.done);
+    }
+    if (ep->counters) cudaFree(ep->counters);
+    delete ep;
+    return 0;
+}
+
+// Registers [addr, addr+length) as a local region. The IPC handle of the enclosing
+// allocation and the offset of addr inside it are recorded for export.
+// Returns the handle (>= 0). Registering the same name again replaces the entry.
+int slime_nvlink_ep_register(void* h, unsigned long long addr, unsigned long long length, const char* name)
+{
+    Endpoint* ep = static_cast<Endpoint*>(h);
+    Region    r;
+    r.addr   = addr;
+    r.length = length;
+    r.alive  = true;
+    unsigned long long off = 0;
+    if (slime_ipc_get_handle(reinterpret_cast<const void*>(addr), r.ipc, &off, nullptr)) {
+        // Memory that CUDA IPC cannot export (for example virtual-memory-managed pools) can still be
+        // used by endpoints of the same process; other processes will fail to open the zero handle.
+        memset(r.ipc, 0, 64);
+        off = 0;
+        cudaGetLastError();
+    }
+    r.offset = off;
+    std::lock_guard<std::mutex> g(ep->mu);
+    char                        auto_name[64];
+    if (name == nullptr || name[0] == 0) {
+        snprintf(auto_name, sizeof(auto_name), "auto_0x%llx", addr);
+        name = auto_name;
+    }
+    r.name  = name;
+    auto it = ep->local_by_name.find(r.name);
+    if (it != ep->local_by_name.end()) {
+        ep->local[it->second] = r;
+        return it->second;
+    }
+    ep->local.push_back(r);
+    ep->local_by_name[r.name] = static_cast<int>(ep->local.size()) - 1;
+    return static_cast<int>(ep->local.size()) - 1;
+}
+
+int slime_nvlink_ep_unregister(void* h, int handle)
+{
+    Endpoint*                   ep = static_cast<Endpoint*>(h);
+    std::lock_guard<std::mutex> g(ep->mu);
+    if (handle < 0 || handle >= static_cast<int>(ep->local.size()) || !ep->local[handle].alive)
+        return fail("nvlink endpoint: no local region with handle %d", handle);
+    ep->local_by_name.erase(ep->local[handle].name);
+    ep->local[handle].alive = false;
+    return 0;
+}
+
+// Fills `out` (64 bytes handle, then offset, addr, length as u64) for local handle.
+int slime_nvlink_ep_local_info(void* h, int handle, unsigned char* ipc_out64, unsigned long long* offset,
+                               unsigned long long* addr, unsigned long long* length)
+{
+    Endpoint*                   ep = static_cast<Endpoint*>(h);
+    std::lock_guard<std::mutex> g(ep->mu);
+    if (handle < 0 || handle >= static_cast<int>(ep->local.size()) || !ep->local[handle].alive)
+        return fail("nvlink endpoint: no local region with handle %d", handle);
+    const Region& r = ep->local[handle];
+    memcpy(ipc_out64, r.ipc, 64);
+    *offset = r.offset;
+    *addr   = r.addr;
+    *length = r.length;
+    return 0;
+}
+
+// Maps a peer's region. same_process != 0 means `addr` is directly usable (both
+// endpoints live in one process, where an IPC handle cannot be opened).
+int slime_nvlink_ep_register_remote(void* h, const char* name, const unsigned char* ipc64, unsigned long long offset,
+                                    unsigned long long length, unsigned long long addr, int same_process)
+{
+    Endpoint* ep = static_cast<Endpoint*>(h);
+    Region    r;
+    r.name   = name ? name : "";
+    r.offset = offset;
+    r.length = length;
+    r.alive  = true;
+    memcpy(r.ipc, ipc64, 64);
+    std::lock_guard<std::mutex> g(ep->mu);
+    if (same_process) {
+        r.addr = addr;
+    }
+    else {
+        const std::string key(reinterpret_cast<const char*>(ipc64), 64);
+        auto              it = ep->opened.find(key);
+        void*             base = nullptr;
+        if (it == ep->opened.end()) {
+            if (slime_ipc_open(ipc64, &base)) return -1;
+            ep->opened[key] = base;
+        }
+        else {
+            base = it->second;
+        }
+        r.mapped_base = base;
+        r.addr        = reinterpret_cast<unsigned long long>(base) + offset;
+    }
+    auto it = ep->remote_by_name.find(r.name);
+    if (!r.name.empty() && it != ep->remote_by_name.end()) {
+        ep->remote[it->second] = r;
+        return it->second;
+    }
+    ep->remote.push_back(r);
+    if (!r.name.empty()) ep->remote_by_name[r.name] = static_cast<int>(ep->remote.size()) - 1;
+    return static_cast<int>(ep->remote.size()) - 1;
+}
+
+int slime_nvlink_ep_handle(void* h, const char* name, int remote)
+{
+    Endpoint*                   ep = static_cast<Endpoint*>(h);
+    std::lock_guard<std::mutex> g(ep->mu);
+    auto&                       m  = remote ? ep->remote_by_name : ep->local_by_name;
+    auto                        it = m.find(name);
+    return it == m.end() ? -1 : it->second;
+}
+
+unsigned long long slime_nvlink_ep_remote_addr(void* h, int handle)
+{
+    Endpoint*                   ep = static_cast<Endpoint*>(h);
+    std::lock_guard<std::mutex> g(ep->mu);
+    if (handle < 0 || handle >= static_cast<int>(ep->remote.size())) return 0;
+    return ep->remote[handle].addr;
+}
+
+// One batched transfer. tuples = n x {local_handle, remote_handle, remote_offset, local_offset, length}
+// (the assignment tuple order of the endpoint API). is_write: local -> remote, else remote -> local.
+// signal (optional) receives signal_value (store, or add when signal_add) after the last byte.
+int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, int is_write, void* signal,
+                             unsigned long long signal_value, int signal_add, int max_blocks, void* stream_v)
+{
+    Endpoint*    ep     = static_cast<Endpoint*>(h);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (n < 0) return fail("nvlink endpoint: negative batch size");
+    if (ensure_staging(ep)) return -1;
+    int done = 0;
+    if (n == 0 && signal == nullptr) return 0;
+    do {
+        const int          batch = std::min(n - done, kStagingEntries);
+        InlineBatch        inl{};
+        Segment*           seg_out = nullptr;
+        StagingSlot*       slot    = nullptr;
+        if (batch <= kInlineSegs) {
+            seg_out = inl.seg;
+        }
+        else {
+            slot = &ep->slots[ep->next_slot];
+            ep->next_slot = (ep->next_slot + 1) % kStagingSlots;
+            if (ensure_slot(*slot)) return -1;
+            SLIME_CUDA_OK(cudaEventSynchronize(slot->done));  // previous user of this slot has been consumed
+            seg_out = slot->host;
+        }
+        unsigned long long units = 0;
+        {
+            std::lock_guard<std::mutex> g(ep->mu);
+            for (int i = 0; i < batch; ++i) {
+                const unsigned long long* t  = tuples + 5ull * (done + i);
+                const long long           lh = static_cast<long long>(t[0]), rh = static_cast<long long>(t[1]);
+                if (lh < 0 || lh >= static_cast<long long>(ep->local.size()) || !ep->local[lh].alive)
+                    return fail("nvlink endpoint: assignment %d names unknown local region %lld", done + i, lh);
+                if (rh < 0 || rh >= static_cast<long long>(ep->remote.size()) || !ep->remote[rh].alive)
+                    return fail("nvlink endpoint: assignment %d names unknown remote region %lld", done + i, rh);
+                const Region& L = ep->local[lh];
+                const Region& R = ep->remote[rh];
+                const unsigned long long roff = t[2], loff = t[3], len = t[4];
+                if (loff + len > L.length || roff + len > R.length)
+                    return fail("nvlink endpoint: assignment %d exceeds a region (local %llu+%llu of %llu, remote %llu+%llu of %llu)",
+                                done + i, loff, len, L.length, roff, len, R.length);
+                Segment& s   = seg_out[i];
+                s.dst        = is_write ? R.addr + roff : L.addr + loff;
+                s.src        = is_write ? L.addr + loff : R.addr + roff;
+                s.len        = len;
+                s.first_unit = units;
+                units += (len + kUnitBytes - 1) / kUnitBytes;
+                if (len == 0) units += 0;
+            }
+        }
+        CopyArgs a{};
+        a.n_seg   = batch;
+        a.n_units = units;
+        const bool last_batch = done + batch >= n;
+        if (last_batch && signal != nullptr) {
+            a.signal        = static_cast<unsigned long long*>(signal);
+            a.signal_value  = signal_value;
+            a.signal_add    = signal_add;
+            a.block_counter = ep->counters + ep->next_counter;
+            ep->next_counter = (ep->next_counter + 1) % 64;
+        }
+        if (slot) {
+            SLIME_CUDA_OK(cudaMemcpyAsync(slot->dev, slot->host, sizeof(Segment) * batch, cudaMemcpyHostToDevice, stream));
+            a.table = slot->dev;
+        }
+        long long grid = static_cast<long long>(std::min<unsigned long long>(units, static_cast<unsigned long long>(sm_count()) * 8));
+        if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
+        if (grid < 1) grid = 1;
+        p2p_scatter_gather_kernel<<<static_cast<int>(grid), kThreads, 0, stream>>>(a, inl);
+        SLIME_CUDA_OK(cudaGetLastError());
+        if (slot) SLIME_CUDA_OK(cudaEventRecord(slot->done, stream));  // the slot is free once the kernel has read its table
+        done += batch;
+    } while (done < n);
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,108 @@
+"""Low-latency all-gather buffer (``csrc/kernels/allgather.cu``).
+
+Follows the buffer pattern of the reference's removed ``AllGatherInterLLBuffer``
+(``dlslime/csrc/python/bind.cpp:533-541`` in the reference): the object owns a
+pre-registered symmetric buffer, ``buffer_info()`` is exchanged out of band,
+``connect_full_mesh(infos)`` maps the peers, ``all_gather_ll(x)`` gathers, and
+``all_gather_ll_hook(x)`` issues the transfer and returns a hook that completes it.
+Constructor arguments here: ``(max_bs, msg_size, dtype, world_size, rank)``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import struct
+
+import torch
+
+from .. import _lib
+from ..parallel.symm import SymmetricHeap
+from ._common import default_status, ptr, stream_ptr
+
+_v, _i, _ull = ctypes.c_void_p, ctypes.c_int, ctypes.c_ulonglong
+_lib.declare("slime_ag_push", [ctypes.c_char_p, _v, _ull, _ull, _ull, _v, _i, _i, _v, _v])
+_lib.declare("slime_ag_wait", [ctypes.c_char_p, _ull, _v, _v])
+_CFG_FMT = "<2i3Q8QQ"
+
+
+class AllGatherLLBuffer:
+    def __init__(self, max_bs: int, msg_size: int, dtype: torch.dtype, world_size: int | None = None,
+                 rank: int | None = None, *, group=None, heap: SymmetricHeap | None = None, base_off: int | None = None,
+                 wait_ns: int = 0):
+        self.dtype, self.msg_size, self.max_bs = dtype, msg_size, max_bs
+        self.itemsize = torch.empty((), dtype=dtype).element_size()
+        self.slot_bytes = (max_bs * msg_size * self.itemsize + 255) // 256 * 256
+        world = world_size if world_size is not None else (heap.world if heap else None)
+        if heap is None:
+            import torch.distributed as dist
+
+            world = dist.get_world_size(group) if dist.is_initialized() else 1
+            heap = SymmetricHeap(2 * world * self.slot_bytes + 4096, group=group)
+        self.heap, self.world = heap, heap.world
+        self.rank = heap.rank if rank is None else rank
+        assert world is None or world == self.world
+        total = 2 * self.world * self.slot_bytes + 4096
+        self.base_off = heap.reserve(total) if base_off is None else base_off
+        self.off_data = self.base_off
+        self.off_flags = self.base_off + 2 * self.world * self.slot_bytes
+        self.step = 0
+        self.wait_ns = wait_ns
+        self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self._counter_ptr = self.counter.data_ptr()
+        self.status = default_status()
+        self._cfg = self._pack()
+
+    def _pack(self) -> bytes:
+        peers = list(self.heap.peer_ptrs) + [0] * (8 - self.world)
+        return struct.pack(_CFG_FMT, self.rank, self.world, self.off_data, self.off_flags, self.slot_bytes, *peers, self.wait_ns)
+
+    @classmethod
+    def emulated_group(cls, world: int, max_bs: int, msg_size: int, dtype: torch.dtype, wait_ns: int = 0):
+        slot = (max_bs * msg_size * torch.empty((), dtype=dtype).element_size() + 255) // 256 * 256
+        heap = SymmetricHeap.emulated(world, 2 * world * slot + 4096)
+        off = heap.reserve(2 * world * slot + 4096)
+        return [cls(max_bs, msg_size, dtype, heap=heap, rank=r, base_off=off, wait_ns=wait_ns) for r in range(world)]
+
+    def buffer_info(self) -> dict:
+        return self.heap.export_info()
+
+    def connect_full_mesh(self, infos) -> None:
+        self.heap.connect(infos)
+        self._cfg = self._pack()
+
+    def get_local_buffer(self) -> torch.Tensor:
+        return self.heap.view(self.off_data, (2, self.world, self.slot_bytes), torch.uint8, rank=self.rank)
+
+    def _result(self, step: int, bs: int) -> torch.Tensor:
+        half = step & 1
+        off = self.off_data + half * self.world * self.slot_bytes
+        return self.heap.view(off, (self.world * bs, self.msg_size), self.dtype, rank=self.rank)
+
+    def _issue(self, x: torch.Tensor, do_wait: bool, max_blocks: int = 0) -> tuple[int, int]:
+        assert x.is_contiguous() and x.dtype == self.dtype and x.shape[-1] == self.msg_size
+        bs = x.numel() // self.msg_size
+        assert bs <= self.max_bs
+        self.step += 1
+        nbytes = x.numel() * self.itemsize
+        _lib.call("slime_ag_push", self._cfg, ptr(x), nbytes, nbytes, self.step, self._counter_ptr, int(do_wait),
+                  max_blocks, self.status.dev_ptr, stream_ptr())
+        return self.step, bs
+
+    def all_gather_ll(self, x: torch.Tensor) -> torch.Tensor:
+        """Gather ``x`` [bs, msg_size] from every rank -> [world * bs, msg_size] (a view of the buffer).
+
+        The view stays valid until the second-next call on this buffer. ``bs`` must be the
+        same on every rank.
+        """
+        step, bs = self._issue(x, do_wait=True)
+        return self._result(step, bs)
+
+    def all_gather_ll_hook(self, x: torch.Tensor):
+        """Issue the push now; the returned hook waits for the peers and yields the gathered view."""
+        step, bs = self._issue(x, do_wait=False)
+
+        def hook() -> torch.Tensor:
+            _lib.call("slime_ag_wait", self._cfg, step, self.status.dev_ptr, stream_ptr())
+            return self._result(step, bs)
+
+        return hook

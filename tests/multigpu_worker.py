@@ -1,0 +1,122 @@
+"""Multi-GPU checks, one process per GPU (launched by test_gpu_multi.py through torchrun).
+
+Every check compares against a PyTorch / NCCL restatement of the same operation.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def check_endpoint(rank, world):
+    from dlslime_b200.ops.nvlink import NVLinkEndpoint
+
+    peer = rank ^ 1
+    if peer >= world:
+        return
+    n = 8 << 20
+    gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+    buf = torch.randint(0, 255, (n,), dtype=torch.uint8, device="cuda", generator=gen)
+    orig = buf.clone()
+    ep = NVLinkEndpoint()
+    ep.register_memory_region(buf.data_ptr(), 0, n, "buffer")
+    infos = [None] * world
+    dist.all_gather_object(infos, ep.endpoint_info())
+    ep.connect(infos[peer])
+    peer_gen = torch.Generator(device="cuda").manual_seed(100 + peer)
+    peer_orig = torch.randint(0, 255, (n,), dtype=torch.uint8, device="cuda", generator=peer_gen)
+    dist.barrier()
+    half = n // 2
+    if rank < peer:
+        # read: pull scattered pieces of the peer's upper half into my lower half (odd sizes and offsets included)
+        segs = [("buffer", "buffer", half + 1000 * i + (i % 3), 2000 * i + (i % 5), 777 + 16 * i) for i in range(200)]
+        segs.append(("buffer", "buffer", half + (1 << 20), 1 << 20, 1 << 20))
+        fut = ep.read(segs)
+        assert fut.wait() == 0
+        expect = orig.clone()
+        for _, _, roff, loff, ln in segs:
+            expect[loff:loff + ln] = peer_orig[roff:roff + ln]
+        torch.cuda.synchronize()
+        assert torch.equal(buf, expect), "endpoint read mismatch"
+    dist.barrier()
+    if rank < peer:
+        # write with immediate data: push my lower half into the peer's lower half, then notify
+        lh, rh = ep.get_mr_handle("buffer"), ep.get_remote_mr_handle("buffer")
+        fut = ep.write_with_imm([(lh, rh, 4096, 4096, half - 8192)], imm_data=0xBEEF)
+        assert fut.wait() == 0
+    else:
+        status, imm = ep.imm_recv()
+        assert status == 0 and imm == 0xBEEF, (status, imm)
+        torch.cuda.synchronize()
+        # what the peer wrote is ITS buffer after its own reads; recompute that
+        psegs = [(half + 1000 * i + (i % 3), 2000 * i + (i % 5), 777 + 16 * i) for i in range(200)]
+        psegs.append((half + (1 << 20), 1 << 20, 1 << 20))
+        pbuf = peer_orig.clone()
+        for roff, loff, ln in psegs:
+            pbuf[loff:loff + ln] = orig[roff:roff + ln]
+        assert torch.equal(buf[4096:half - 4096], pbuf[4096:half - 4096]), "endpoint write mismatch"
+        assert torch.equal(buf[:4096], orig[:4096]) and torch.equal(buf[half:], orig[half:])
+    dist.barrier()
+    ep.close()
+
+
+def check_allgather(rank, world):
+    from dlslime_b200.ops.allgather import AllGatherLLBuffer
+
+    hidden = 7168
+    ag = AllGatherLLBuffer(1024, hidden, torch.bfloat16)
+    for step, bs in enumerate([1, 16, 128, 1024, 16, 1]):
+        x = torch.randn((bs, hidden), device="cuda").to(torch.bfloat16) + rank
+        ref = torch.empty((world * bs, hidden), dtype=torch.bfloat16, device="cuda")
+        dist.all_gather_into_tensor(ref, x)
+        if step % 2 == 0:
+            out = ag.all_gather_ll(x)
+        else:
+            out = ag.all_gather_ll_hook(x)()
+        torch.cuda.synchronize()
+        ag.status.check()
+        assert torch.equal(out, ref), f"all-gather mismatch at bs={bs}"
+    dist.barrier()
+
+
+def check_moe(rank, world):
+    from dlslime_b200.models.moe import ExpertParallelMoE, MoEConfig, init_expert_weights, ref_moe_forward
+
+    cfg = MoEConfig(num_experts=32, topk=4, hidden=1024, intermediate=256)
+    layer = ExpertParallelMoE(cfg, max_tokens=256, seed=7)
+    w13, w2 = init_expert_weights(cfg, range(cfg.num_experts), "cuda", seed=7)
+    for step in range(3):
+        T = [200, 1, 256, 33, 64, 128, 17, 255][(rank + step) % 8]
+        gen = torch.Generator(device="cuda").manual_seed(1000 * step + rank)
+        x = torch.randn((T, cfg.hidden), generator=gen, device="cuda").to(torch.bfloat16)
+        lg = torch.randn((T, cfg.num_experts), generator=gen, device="cuda")
+        out = layer(x, lg)
+        torch.cuda.synchronize()
+        layer.buf.status.check()
+        ref, idx, w = ref_moe_forward(cfg, x, lg, w13, w2)
+        assert torch.equal(layer.buf.topk_idx[:T].long(), idx)
+        err = (out.float() - ref.float()).abs()
+        tol = ref.float().abs() * 2 ** -6 + ref.float().abs().mean() * 2 ** -5
+        assert (err <= tol).all(), f"rank {rank} step {step}: max err {err.max().item()}"
+    dist.barrier()
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    which = sys.argv[1:] or ["endpoint", "allgather", "moe"]
+    for name in which:
+        globals()[f"check_{name}"](rank, world)
+        if rank == 0:
+            print(f"CHECK_OK {name}", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"WORKER_OK {rank}", flush=True)
+
+
+if __name__ == "__main__":
+    main()
