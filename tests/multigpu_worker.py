@@ -32,7 +32,7 @@ def check_endpoint(rank, world):
     half = n // 2
     if rank < peer:
         # read: pull scattered pieces of the peer's upper half into my lower half (odd sizes and offsets included)
-        segs = [("buffer", "buffer", half + 1000 * i + (i % 3), 2000 * i + (i % 5), 777 + 16 * i) for i in range(200)]
+        segs = [("buffer", "buffer", half + 1000 * i + (i % 3), 5000 * i + (i % 5), 777 + 16 * i) for i in range(200)]
         segs.append(("buffer", "buffer", half + (1 << 20), 1 << 20, 1 << 20))
         fut = ep.read(segs)
         assert fut.wait() == 0
@@ -52,7 +52,7 @@ def check_endpoint(rank, world):
         assert status == 0 and imm == 0xBEEF, (status, imm)
         torch.cuda.synchronize()
         # what the peer wrote is ITS buffer after its own reads; recompute that
-        psegs = [(half + 1000 * i + (i % 3), 2000 * i + (i % 5), 777 + 16 * i) for i in range(200)]
+        psegs = [(half + 1000 * i + (i % 3), 5000 * i + (i % 5), 777 + 16 * i) for i in range(200)]
         psegs.append((half + (1 << 20), 1 << 20, 1 << 20))
         pbuf = peer_orig.clone()
         for roff, loff, ln in psegs:
