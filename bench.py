@@ -206,7 +206,7 @@ def run_ours(args, rank, world, local):
     ms_e2e, _ = timed(step_e2e)
 
     # phase breakdown (one extra instrumented pass; not part of the reported value)
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
     sync_all(world)
     e = layer.buf.next_epoch()
     evs[0].record()
@@ -214,12 +214,16 @@ def run_ours(args, rank, world, local):
     evs[1].record()
     layer.step_dispatch(dev_x[0], e)
     evs[2].record()
-    layer.step_experts(T, e)
+    layer.step_recv(T, e)
     evs[3].record()
-    layer.step_combine(out, T, e)
+    layer.step_gate_up()
     evs[4].record()
+    layer.step_down()
+    evs[5].record()
+    layer.step_combine(out, T, e)
+    evs[6].record()
     sync_all(world)
-    names = ["route", "dispatch", "experts_ffn_and_combine_push", "combine_reduce"]
+    names = ["route", "dispatch_quant_push", "recv_wait_dequant", "gate_up_swiglu_gemm", "down_gemm_combine_push", "combine_wait_reduce"]
     breakdown = {n: round(max_over_ranks(evs[i].elapsed_time(evs[i + 1]) * 1e3, world), 1) for i, n in enumerate(names)}
 
     weights_gb = (layer.w_gate_up.numel() + layer.w_down.numel()) * 2 / 1e9

@@ -1,0 +1,125 @@
+#!/usr/bin/env python
+"""Single-GPU micro-benchmarks of the sm_100a kernels against their library baselines.
+
+    python bench/kernel_bench.py gemm [--m 8192 --n 8192 --k 8192]
+    python bench/kernel_bench.py grouped [--experts 32 --rows 1024]
+    python bench/kernel_bench.py quant
+
+Timing: CUDA events on the launching stream, 3 warm-up runs, a 256 MB buffer is
+rewritten between timed runs to flush L2, best and median of the timed runs are
+reported. Fractions are of the measured peaks in MEASURED_PEAKS.json when that
+file is present (else of 6.65 TB/s and 1.59 PFLOP/s, an earlier measurement).
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+_flush = None
+
+
+def timeit(fn, iters=10, warmup=3):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(iters):
+        _flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[0], times[len(times) // 2]
+
+
+def cmd_gemm(a):
+    from dlslime_b200.ops import gemm
+
+    hbm, tf, tag = peaks()
+    x = torch.randn(a.m, a.k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(a.n, a.k, device="cuda") * 0.02).to(torch.bfloat16)
+    out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+    flops = 2.0 * a.m * a.n * a.k
+    best, med = timeit(lambda: gemm.gemm_bf16(x, w, out=out), a.iters)
+    b2, m2 = timeit(lambda: torch.matmul(x, w.t(), out=out), a.iters)
+    print(json.dumps({"kernel": "gemm_bf16_tc", "m": a.m, "n": a.n, "k": a.k, "ms_best": round(best, 4), "ms_median": round(med, 4),
+                      "tflops_best": round(flops / best / 1e9, 1), "frac_of_peak": round(flops / best / 1e9 / tf, 3), "peak": tag,
+                      "cublas_ms_best": round(b2, 4), "cublas_tflops_best": round(flops / b2 / 1e9, 1)}))
+
+
+def cmd_grouped(a):
+    from dlslime_b200.ops import gemm
+
+    hbm, tf, tag = peaks()
+    g, rows, k, inter = a.experts, a.rows, 7168, 2048
+    offs = torch.arange(0, g + 1, dtype=torch.int32, device="cuda") * rows
+    x = torch.randn(g * rows, k, device="cuda").to(torch.bfloat16)
+    w13 = (torch.randn(g, 2 * inter, k, device="cuda") * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(g, k, inter, device="cuda") * 0.02).to(torch.bfloat16)
+    h = torch.empty(g * rows, inter, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty(g * rows, k, device="cuda", dtype=torch.bfloat16)
+    f1, f2 = 2.0 * g * rows * k * 2 * inter, 2.0 * g * rows * inter * k
+    b1, _ = timeit(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU), a.iters)
+    b2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y), a.iters)
+
+    def cublas_loop():
+        for e in range(g):
+            gu = x[e * rows:(e + 1) * rows] @ w13[e].t()
+            hh = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
+            torch.matmul(hh, w2[e].t(), out=y[e * rows:(e + 1) * rows])
+
+    b3, _ = timeit(cublas_loop, max(3, a.iters // 2))
+    print(json.dumps({"kernel": "grouped_swiglu_ffn", "experts": g, "rows_per_expert": rows,
+                      "gate_up_ms": round(b1, 4), "gate_up_tflops": round(f1 / b1 / 1e9, 1),
+                      "down_ms": round(b2, 4), "down_tflops": round(f2 / b2 / 1e9, 1),
+                      "frac_of_peak": round((f1 + f2) / (b1 + b2) / 1e9 / tf, 3), "peak": tag,
+                      "cublas_loop_ms": round(b3, 4), "cublas_loop_tflops": round((f1 + f2) / b3 / 1e9, 1)}))
+
+
+def cmd_quant(a):
+    from dlslime_b200.ops import quant
+
+    hbm, tf, tag = peaks()
+    x = torch.randn(a.rows_q, 7168, device="cuda").to(torch.bfloat16)
+    q = torch.empty_like(x, dtype=torch.float8_e4m3fn)
+    s = torch.empty(a.rows_q, 56, device="cuda")
+    y = torch.empty_like(x)
+    nbytes_q = x.numel() * 3 + s.numel() * 4
+    b1, _ = timeit(lambda: quant.fp8_quant_1x128(x, q, s), a.iters)
+    b2, _ = timeit(lambda: quant.fp8_dequant_1x128(q, s, y), a.iters)
+    b3, _ = timeit(lambda: quant.ref_quant_1x128(x), a.iters)
+    print(json.dumps({"kernel": "fp8_quant_1x128", "rows": a.rows_q, "quant_ms": round(b1, 4), "quant_gbs": round(nbytes_q / b1 / 1e6, 1),
+                      "dequant_ms": round(b2, 4), "dequant_gbs": round(nbytes_q / b2 / 1e6, 1),
+                      "frac_of_peak": round(nbytes_q / b1 / 1e6 / hbm, 3), "peak": tag, "torch_composite_ms": round(b3, 4)}))
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("cmd", choices=["gemm", "grouped", "quant"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--experts", type=int, default=32)
+    ap.add_argument("--rows", type=int, default=1024)
+    ap.add_argument("--rows-q", type=int, default=32768)
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    {"gemm": cmd_gemm, "grouped": cmd_grouped, "quant": cmd_quant}[args.cmd](args)

@@ -24,6 +24,7 @@ namespace gemm {
 constexpr int kBM      = 128;
 constexpr int kBK      = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kThreads = 192;
+constexpr int kEpiRowPitch = 144;  // 128 payload bytes + 16 so that 32 rows spread over all shared-memory banks
 
 enum Epilogue : int {
     kEpiStore  = 0,  // C = acc (bf16)
@@ -62,7 +63,8 @@ struct Smem {
     static constexpr int kBBytes     = BN * kBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarBytes   = (2 * STAGES + 4) * 8 + 16;
-    static constexpr int kTotal      = STAGES * kStageBytes + kBarBytes + 1024;  // + alignment slack
+    static constexpr int kEpiBytes   = 128 * kEpiRowPitch;  // one padded 128-byte slot per tile row
+    static constexpr int kTotal      = STAGES * kStageBytes + kEpiBytes + kBarBytes + 1024;  // + alignment slack
 };
 
 struct TileCoord {
@@ -143,7 +145,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
-    uint64_t* full_bar   = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
+    uint8_t*  epi_smem   = smem + STAGES * S::kStageBytes;
+    uint64_t* full_bar   = reinterpret_cast<uint64_t*>(epi_smem + S::kEpiBytes);
     uint64_t* empty_bar  = full_bar + STAGES;
     uint64_t* tfull_bar  = empty_bar + STAGES;  // [2] accumulator ready
     uint64_t* tempty_bar = tfull_bar + 2;       // [2] accumulator drained
@@ -297,59 +300,66 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
             const int      col0  = tc.nt * kBNOut;
 
-            if (EPI == kEpiSwiGLU) {
-                __nv_bfloat16* crow = args.C + static_cast<long long>(row) * args.ldc + col0;
-#pragma unroll 1
-                for (int c = 0; c < BN / 2; c += 16) {
-                    uint32_t g[16], u[16];
-                    tmem_ld_32x32b_x16(taddr + c, g);
-                    tmem_ld_32x32b_x16(taddr + BN / 2 + c, u);
-                    tmem_ld_wait();
-                    if (valid && col0 + c < args.N) {
-                        uint32_t o[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float h0 = silu(__uint_as_float(g[2 * i])) * __uint_as_float(u[2 * i]);
-                            const float h1 = silu(__uint_as_float(g[2 * i + 1])) * __uint_as_float(u[2 * i + 1]);
-                            o[i]           = pack_bf16(h0, h1);
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>(crow + c);
-                        dst[0]     = make_uint4(o[0], o[1], o[2], o[3]);
-                        dst[1]     = make_uint4(o[4], o[5], o[6], o[7]);
-                    }
-                }
+            // Destination of this thread's row (one thread owns one row of the tile).
+            unsigned long long drow = 0;  // byte address of column col0 of the row
+            float              scale = 1.0f;
+            bool               do_store = valid;
+            if (EPI == kEpiScatterRows) {
+                const unsigned long long inf    = valid ? args.row_info[row] : ~0ull;
+                const unsigned int       region = static_cast<unsigned int>(inf >> 48);
+                const unsigned long long slot   = inf & 0xffffffffffffull;
+                const unsigned long long base   = region < 8 ? args.scatter_base[region] : 0ull;
+                do_store                        = valid && base != 0ull && slot < args.scatter_slots;
+                drow = base + slot * args.scatter_row_bytes + static_cast<unsigned long long>(col0) * 2;
+                if (do_store && args.row_scale) scale = args.row_scale[row];
             }
             else {
-                __nv_bfloat16* crow;
-                float          scale = 1.0f;
-                bool           do_store = valid;
-                if (EPI == kEpiScatterRows) {
-                    const unsigned long long inf    = valid ? args.row_info[row] : ~0ull;
-                    const unsigned int       region = static_cast<unsigned int>(inf >> 48);
-                    const unsigned long long slot   = inf & 0xffffffffffffull;
-                    const unsigned long long base   = region < 8 ? args.scatter_base[region] : 0ull;
-                    do_store                        = valid && base != 0ull && slot < args.scatter_slots;
-                    crow = reinterpret_cast<__nv_bfloat16*>(base + slot * args.scatter_row_bytes) + col0;
-                    if (do_store && args.row_scale) scale = args.row_scale[row];
-                }
-                else {
-                    crow = args.C + static_cast<long long>(row) * args.ldc + col0;
-                }
+                drow = reinterpret_cast<unsigned long long>(args.C + static_cast<long long>(row) * args.ldc + col0);
+            }
+            // Rows leave through shared memory: the thread packs 64 output columns (128 bytes) of its
+            // row into its private, padded slot and hands them to the bulk-copy engine, which writes
+            // one contiguous 128-byte piece per row (local or peer memory) instead of scattered
+            // 16-byte stores.
+            uint8_t* my_slot = epi_smem + (quad * 32 + lane) * kEpiRowPitch;
 #pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
-                    uint32_t v[32];
-                    tmem_ld_32x32b_x32(taddr + c, v);
-                    tmem_ld_wait();
-                    if (do_store && col0 + c < args.N) {
-                        uint32_t o[16];
+            for (int c = 0; c < kBNOut; c += 64) {
+                uint32_t o[32];
+                if (EPI == kEpiSwiGLU) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            o[i] = pack_bf16(__uint_as_float(v[2 * i]) * scale, __uint_as_float(v[2 * i + 1]) * scale);
-                        uint4* dst = reinterpret_cast<uint4*>(crow + c);
+                    for (int hb = 0; hb < 2; ++hb) {
+                        uint32_t g[32], u[32];
+                        tmem_ld_32x32b_x32(taddr + c + hb * 32, g);
+                        tmem_ld_32x32b_x32(taddr + BN / 2 + c + hb * 32, u);
+                        tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                        for (int i = 0; i < 16; ++i) {
+                            const float h0 = silu(__uint_as_float(g[2 * i])) * __uint_as_float(u[2 * i]);
+                            const float h1 = silu(__uint_as_float(g[2 * i + 1])) * __uint_as_float(u[2 * i + 1]);
+                            o[hb * 16 + i] = pack_bf16(h0, h1);
+                        }
                     }
                 }
+                else {
+#pragma unroll
+                    for (int hb = 0; hb < 2; ++hb) {
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(taddr + c + hb * 32, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            o[hb * 16 + i] = pack_bf16(__uint_as_float(v[2 * i]) * scale, __uint_as_float(v[2 * i + 1]) * scale);
+                    }
+                }
+                tma_store_wait_read<0>();  // the previous piece has left this slot
+                uint4* sp = reinterpret_cast<uint4*>(my_slot);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sp[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                fence_proxy_async_smem();
+                int cols = args.N - (col0 + c);
+                if (cols > 64) cols = 64;
+                if (do_store && cols > 0)
+                    bulk_store_s2g(reinterpret_cast<void*>(drow + static_cast<unsigned long long>(c) * 2), my_slot, cols * 2);
+                tma_store_commit();
             }
             tc_fence_before_sync();
             mbar_arrive(&tempty_bar[acc]);
@@ -358,6 +368,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 acc_phase ^= 1;
             }
         }
+        tma_store_wait<0>();  // every row this thread handed to the copy engine has been written
     }
 
     // teardown: everyone meets, then the allocating warp frees TMEM

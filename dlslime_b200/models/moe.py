@@ -76,13 +76,23 @@ class ExpertParallelMoE:
     def step_dispatch(self, x, epoch):
         self.buf.dispatch(x, epoch)
 
-    def step_experts(self, T, epoch):
+    def step_recv(self, T, epoch):
         c = self.cfg
         self.buf.recv_dequant(self.xd, epoch, expected_rows=min(self.buf.recv_cap, max(1, 2 * T * c.topk)))
+
+    def step_gate_up(self):
         gemm.grouped_gemm_bf16(self.xd, self.w_gate_up, self.buf.group_offsets, out=self.h, epilogue=gemm.EPI_SWIGLU)
+
+    def step_down(self):
+        c = self.cfg
         gemm.grouped_gemm_bf16(self.h, self.w_down, self.buf.group_offsets, epilogue=gemm.EPI_SCATTER_ROWS,
                                row_info=self.buf.recv_info, scatter_bases=self._bases,
                                scatter_row_bytes=c.hidden * 2, scatter_slots=self.max_tokens * c.topk)
+
+    def step_experts(self, T, epoch):
+        self.step_recv(T, epoch)
+        self.step_gate_up()
+        self.step_down()
 
     def step_combine(self, out, T, epoch, do_signal=True):
         self.buf.combine_reduce(out, T, epoch, do_signal=do_signal)
