@@ -56,6 +56,11 @@ int slime_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
 int slime_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                           long long ldc, const void* a_ready, int a_ready_rows, unsigned long long a_ready_target,
                           int m_tile_rotate, void* status, void* stream);
+// Tensor-parallel all-gather -> GEMM over peer memory; see gemm.cu for the modes.
+int slime_ag_gemm(int mode, const void* x_local, const void* a_full, const void* B, void* C, int rows_local, int N,
+                  int K, long long ldb, long long ldc, int rank, int world, const unsigned long long* dst8,
+                  const unsigned long long* flags8, unsigned long long step, int push_blocks, void* status,
+                  void* stream);
 // Rows of A are split into num_groups consecutive groups by the device array
 // group_offsets[num_groups+1]; group g multiplies B rows [g*rowsB, (g+1)*rowsB).
 // epilogue 0: store; 1: SwiGLU (B holds N gate rows then N up rows per group, C is [M,N]);
@@ -106,6 +111,15 @@ int slime_ag_push(const void* cfg_bytes, const void* src, unsigned long long byt
                   unsigned long long step, unsigned int* block_counter, int do_wait, int max_blocks, void* status,
                   void* stream);
 int slime_ag_wait(const void* cfg_bytes, unsigned long long step, void* status, void* stream);
+
+// ---- paged KV-cache transfer / pack / unpack (kv_transfer.cu) -----------------
+// Moves K and V of one layer for n_tasks pages between a token-major plane pair and a paged plane
+// pair (addresses as integers; the paged side may be peer memory). to_paged: token-major -> paged.
+int slime_kv_transfer(unsigned long long tok_k, unsigned long long tok_v, unsigned long long page_k,
+                      unsigned long long page_v, const int* tok_off, const int* blk, const int* ntok, int n_tasks,
+                      int page_tokens, unsigned long long row_bytes, unsigned long long tok_rows,
+                      unsigned long long page_blocks, int to_paged, void* done_flag, unsigned long long done_value,
+                      unsigned int* block_counter, int max_blocks, void* status, void* stream);
 
 #ifdef __cplusplus
 }

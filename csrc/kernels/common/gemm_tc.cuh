@@ -53,6 +53,14 @@ struct Args {
     int                       a_ready_rows;  // rows covered by one flag
     unsigned long long        a_ready_target;
     int                       m_tile_rotate;  // start the m-tile order at this tile (own shard first)
+    // all-gather -> GEMM (fused form): extra warps of every CTA copy slices of this rank's shard of A
+    // into every rank's gathered matrix and bump that rank's arrival counters
+    const uint4*              ag_src;          // this rank's shard [ag_rows, K] (nullptr = no push in this kernel)
+    int                       ag_rows;         // rows per shard (multiple of 128)
+    int                       ag_rank, ag_world;
+    int                       ag_shard_order;  // visit m tiles shard by shard: own, rank-1, rank-2, ...
+    unsigned long long        ag_dst[8];       // address of the gathered A on every rank
+    unsigned long long        ag_flags[8];     // address of the arrival counters (u64 per 128 rows) on every rank
     KernelStatus*             status;
     unsigned long long        wait_ns;
 };
@@ -112,6 +120,11 @@ struct TileWalker {
                 const int local = t - cum;
                 int       mt    = local % g_mtiles;
                 if (a.m_tile_rotate) mt = (mt + a.m_tile_rotate) % g_mtiles;
+                if (a.ag_shard_order) {
+                    const int per   = a.ag_rows / kBM;
+                    const int shard = ((a.ag_rank - mt / per) % a.ag_world + a.ag_world) % a.ag_world;
+                    mt              = shard * per + mt % per;
+                }
                 c.group   = g;
                 c.row0    = g_begin + mt * kBM;
                 c.row_end = g_end;
@@ -137,8 +150,50 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template<int BN, int STAGES, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+// All-gather push executed by `nthreads` threads (tid in [0, nthreads)) that share named barrier
+// `bar_id`. Units are (32-row slice of the local shard, destination rank); every finished unit adds 1
+// to the destination's counter of the 128-row chunk it belongs to, so a chunk is complete at
+// 4 * step. Destinations are visited starting with rank+1, the order in which consumers use them.
+constexpr int kAgSliceRows = 32;
+__device__ __forceinline__ void ag_push_units(const Args& a, int tid, int nthreads, int bar_id, int cta, int n_cta)
+{
+    const unsigned long long row_vecs = static_cast<unsigned long long>(a.K) * 2 / 16;
+    const unsigned long long slice_v  = row_vecs * kAgSliceRows;
+    const int                slices   = a.ag_rows / kAgSliceRows;
+    const int                units    = slices * a.ag_world;
+    for (int u = cta; u < units; u += n_cta) {
+        const int    p   = (a.ag_rank + 1 + u % a.ag_world) % a.ag_world;
+        const int    sl  = u / a.ag_world;
+        const uint4* src = a.ag_src + sl * slice_v;
+        uint4* dst = reinterpret_cast<uint4*>(a.ag_dst[p]) + (static_cast<unsigned long long>(a.ag_rank) * slices + sl) * slice_v;
+        unsigned long long i = tid;
+        for (; i + 7ull * nthreads < slice_v; i += 8ull * nthreads) {
+            uint4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = src[i + j * nthreads];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[i + j * nthreads] = v[j];
+        }
+        for (; i < slice_v; i += nthreads) dst[i] = src[i];
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads) : "memory");
+        if (tid == 0) {
+            fence_acq_rel_sys();
+            unsigned long long* f = reinterpret_cast<unsigned long long*>(a.ag_flags[p])
+                                    + a.ag_rank * (a.ag_rows / kBM) + sl / (kBM / kAgSliceRows);
+            red_add_release_sys(f, 1ull);
+        }
+    }
+}
+
+constexpr int kAgThreads = 128;
+
+__global__ void __launch_bounds__(256) ag_push_only_kernel(const Args args)
+{
+    ag_push_units(args, threadIdx.x, blockDim.x, 1, blockIdx.x, gridDim.x);
+}
+
+template<int BN, int STAGES, int EPI, bool AG = false>
+__global__ void __launch_bounds__(kThreads + (AG ? kAgThreads : 0), 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args args)
 {
     using S = Smem<BN, STAGES>;
@@ -281,6 +336,10 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
             if (!ok) *fail_slot = 1;
         }
+    }
+    else if (AG && warp >= 6) {
+        // ------------------------------ all-gather push ---------------------------
+        if (args.ag_src != nullptr) ag_push_units(args, threadIdx.x - kThreads, kAgThreads, 1, blockIdx.x, gridDim.x);
     }
     else {
         // ------------------------------ epilogue ----------------------------------

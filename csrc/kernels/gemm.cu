@@ -36,6 +36,26 @@ int launch(const void* A, const void* B, const Args& args, long long lda, long l
     return 0;
 }
 
+template<bool FUSED>
+int launch_ag(const void* A, const void* B, const Args& args, long long lda, long long ldb, int grid_cap, cudaStream_t stream)
+{
+    using S = Smem<kBN, kStages>;
+    CUtensorMap tmA, tmB;
+    if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.M_total, args.K, lda, kBM, kBK)) return -1;
+    if (make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.rowsB, args.K, ldb, kBN / 2, kBK)) return -1;
+    auto kern = gemm_bf16_tc_kernel<kBN, kStages, kEpiStore, FUSED>;
+    static bool configured = false;
+    if (!configured) {
+        SLIME_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+        configured = true;
+    }
+    int grid = sm_count();
+    if (grid_cap > 0 && grid_cap < grid) grid = grid_cap;
+    kern<<<grid, kThreads + (FUSED ? kAgThreads : 0), S::kTotal, stream>>>(tmA, tmB, args);
+    SLIME_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
 int check_common(int M, int N, int K, long long lda, long long ldb)
 {
     if (M <= 0 || N <= 0 || K <= 0) return fail("gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
@@ -87,6 +107,56 @@ int slime_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, i
     a.status         = static_cast<KernelStatus*>(status);
     const int tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
     return launch<kEpiStore>(A, B, a, lda, ldb, tiles, static_cast<cudaStream_t>(stream));
+}
+
+// All-gather -> GEMM. a_full is this rank's gathered matrix [world * rows_local, K] inside its symmetric
+// region; dst8 / flags8 give the address of that matrix and of its arrival counters on every rank.
+// mode 0: push only (separate kernel); 1: GEMM only, gated on the counters; 2: one fused kernel in
+// which extra warps push this rank's shard while the tensor-core warps work through the tiles.
+int slime_ag_gemm(int mode, const void* x_local, const void* a_full, const void* B, void* C, int rows_local, int N,
+                  int K, long long ldb, long long ldc, int rank, int world, const unsigned long long* dst8,
+                  const unsigned long long* flags8, unsigned long long step, int push_blocks, void* status,
+                  void* stream)
+{
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail("ag_gemm: bad rank/world");
+    if (rows_local <= 0 || rows_local % kBM != 0) return fail("ag_gemm: rows per rank (%d) must be a multiple of %d", rows_local, kBM);
+    if (K % 8 != 0) return fail("ag_gemm: K must be a multiple of 8");
+    Args a{};
+    a.M_total    = rows_local * world;
+    a.N          = N;
+    a.K          = K;
+    a.rowsB      = N;
+    a.num_groups = 1;
+    a.C          = static_cast<__nv_bfloat16*>(C);
+    a.ldc        = ldc;
+    a.status     = static_cast<KernelStatus*>(status);
+    a.ag_rows    = rows_local;
+    a.ag_rank    = rank;
+    a.ag_world   = world;
+    for (int i = 0; i < 8; ++i) {
+        a.ag_dst[i]   = i < world ? dst8[i] : 0;
+        a.ag_flags[i] = i < world ? flags8[i] : 0;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (mode == 0 || mode == 2) {
+        if ((reinterpret_cast<unsigned long long>(x_local) & 15) != 0) return fail("ag_gemm: local shard must be 16-byte aligned");
+        a.ag_src = static_cast<const uint4*>(x_local);
+    }
+    if (mode == 0) {
+        int grid = push_blocks > 0 ? push_blocks : 32;
+        ag_push_only_kernel<<<grid, 256, 0, s>>>(a);
+        SLIME_CUDA_OK(cudaGetLastError());
+        return 0;
+    }
+    if (check_common(a.M_total, N, K, K, ldb)) return -1;
+    a.a_ready        = reinterpret_cast<const unsigned long long*>(flags8[rank]);
+    a.a_ready_rows   = kBM;
+    a.a_ready_target = step * (kBM / kAgSliceRows);
+    a.ag_shard_order = 1;
+    const int tiles = ((a.M_total + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
+    if (mode == 1) return launch_ag<false>(a_full, B, a, K, ldb, tiles, s);
+    if (mode == 2) return launch_ag<true>(a_full, B, a, K, ldb, 0, s);
+    return fail("ag_gemm: unknown mode %d", mode);
 }
 
 int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,

@@ -104,11 +104,70 @@ def check_moe(rank, world):
     dist.barrier()
 
 
+def check_ag_gemm(rank, world):
+    from dlslime_b200.ops.ag_gemm import AllGatherGemm
+
+    rows, k, n = 256, 1024, 512
+    ag = AllGatherGemm(rows, k)
+    w = (torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16)
+    for step in range(3):
+        x = torch.randn(rows, k, device="cuda").to(torch.bfloat16) + rank
+        full = torch.empty((world * rows, k), dtype=torch.bfloat16, device="cuda")
+        dist.all_gather_into_tensor(full, x)
+        out = ag(x, w)
+        torch.cuda.synchronize()
+        ag.status.check()
+        ref = full.float() @ w.float().t()
+        err = (out.float() - ref).abs()
+        assert (err <= ref.abs() * 2 ** -7 + ref.abs().mean() * 2 ** -7 + 1e-3).all(), f"ag_gemm rank {rank}: {err.max().item()}"
+        dist.barrier()  # nobody may overwrite the gathered matrix before every rank has consumed it
+
+
+def check_kv(rank, world):
+    """Ranks [0, world/2) play prefill and push into the paged cache of rank + world/2."""
+    from dlslime_b200.models.pd_kv import KVShape, PagedKVCache, PrefillSender, wait_layers
+    from dlslime_b200.ops._common import default_status
+    from dlslime_b200.parallel.symm import SymmetricHeap
+
+    half = world // 2
+    shape = KVShape(layers=4)
+    lens = [130, 64, 700, 1]
+    pages = sum((n + 63) // 64 for n in lens)
+    blocks = pages + 9
+    heap = SymmetricHeap(PagedKVCache.bytes_needed(shape, blocks))
+    is_prefill = rank < half
+    owner = rank + half if is_prefill else rank
+    cache = PagedKVCache(shape, blocks, heap, owner_rank=owner)
+    g = torch.Generator().manual_seed(50 + (rank % half))
+    dst_blocks = torch.randperm(blocks, generator=g)[:pages].tolist()
+    gen = torch.Generator(device="cuda").manual_seed(70 + (rank % half))
+    stage = torch.randn((shape.layers, 2, sum(lens), shape.row), generator=gen, device="cuda").to(shape.dtype)
+    dist.barrier()
+    if is_prefill:
+        sender = PrefillSender(shape, cache, max_tokens=sum(lens), comm_blocks=16)
+        sender.plan(lens, dst_blocks)
+        sender.kv_stage.copy_(stage)
+        d = 256
+        hidden = torch.randn(sum(lens), d, device="cuda").to(torch.bfloat16)
+        sender.run_prefill_with_transfer(hidden, [(torch.randn(d, d, device="cuda") * 0.05).to(torch.bfloat16)])
+        torch.cuda.synchronize()
+        default_status().check()
+    else:
+        assert wait_layers(cache, 1, timeout_s=20.0), "layers did not arrive"
+        from dlslime_b200.ops import kv as kvops
+
+        tok_off, blk, ntok = kvops.build_page_tasks(lens, shape.page_tokens, dst_blocks)
+        got = cache.tensor()
+        for t, b, n in zip(tok_off.tolist(), blk.tolist(), ntok.tolist()):
+            assert torch.equal(got[:, :, b, :n], stage[:, :, t:t + n]), "kv page mismatch"
+    dist.barrier()
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    which = sys.argv[1:] or ["endpoint", "allgather", "moe"]
+    which = sys.argv[1:] or ["endpoint", "allgather", "moe", "ag_gemm", "kv"]
     for name in which:
         globals()[f"check_{name}"](rank, world)
         if rank == 0:
