@@ -1,0 +1,201 @@
+#include "engine/memory_pool.h"
+
+#include <functional>
+
+#include "core/log.h"
+#include "obs/obs.h"
+
+namespace slime {
+
+static bool is_system_name(const std::string& n)
+{
+    return n.rfind("sys.", 0) == 0;
+}
+
+int32_t LocalMemoryPool::register_memory_region(uintptr_t addr, uint64_t length, const std::optional<std::string>& name)
+{
+    std::lock_guard<std::mutex> g(mu_);
+    int32_t handle = -1;
+    if (name) {
+        auto it = by_name_.find(*name);
+        if (it != by_name_.end()) handle = it->second;
+    }
+    if (handle < 0) {
+        auto it = by_ptr_.find(addr);
+        if (it != by_ptr_.end()) handle = it->second;
+    }
+    if (handle >= 0) {
+        MemoryRegion& r = regions_[handle];
+        if (r.addr == addr && r.length >= length) return handle;  // idempotent
+        // same name or same pointer, but moved or grown: register again under the same handle
+        if (on_unregister) on_unregister(r);
+        obs::record_mr_grow(r.system, r.length, length);
+        by_ptr_.erase(r.addr);
+        r.addr   = addr;
+        r.length = length;
+        if (on_register) on_register(r);
+        by_ptr_[addr] = handle;
+        return handle;
+    }
+    MemoryRegion r;
+    r.addr   = addr;
+    r.length = length;
+    r.alive  = true;
+    if (name) {
+        r.name = *name;
+    }
+    else {
+        char buf[40];
+        snprintf(buf, sizeof(buf), "auto_0x%llx", static_cast<unsigned long long>(addr));
+        r.name = buf;
+    }
+    r.system = is_system_name(r.name);
+    if (on_register) on_register(r);
+    regions_.push_back(r);
+    handle            = static_cast<int32_t>(regions_.size()) - 1;
+    by_name_[r.name]  = handle;
+    by_ptr_[addr]     = handle;
+    obs::record_mr_register(r.system, length);
+    return handle;
+}
+
+int32_t LocalMemoryPool::unregister_memory_region(int32_t handle)
+{
+    std::lock_guard<std::mutex> g(mu_);
+    if (handle < 0 || handle >= static_cast<int32_t>(regions_.size()) || !regions_[handle].alive) return -1;
+    MemoryRegion& r = regions_[handle];
+    if (on_unregister) on_unregister(r);
+    obs::record_mr_unregister(r.system, r.length);
+    by_name_.erase(r.name);
+    by_ptr_.erase(r.addr);
+    r.alive = false;
+    return 0;
+}
+
+int32_t LocalMemoryPool::unregister_memory_region(const std::string& name)
+{
+    int32_t h = get_mr_handle(name);
+    return h < 0 ? -1 : unregister_memory_region(h);
+}
+
+int32_t LocalMemoryPool::get_mr_handle(const std::string& name) const
+{
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = by_name_.find(name);
+    return it == by_name_.end() ? -1 : it->second;
+}
+
+int32_t LocalMemoryPool::get_mr_handle(uintptr_t addr) const
+{
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = by_ptr_.find(addr);
+    return it == by_ptr_.end() ? -1 : it->second;
+}
+
+bool LocalMemoryPool::get_mr(int32_t handle, MemoryRegion& out) const
+{
+    std::lock_guard<std::mutex> g(mu_);
+    if (handle < 0 || handle >= static_cast<int32_t>(regions_.size()) || !regions_[handle].alive) return false;
+    out = regions_[handle];
+    return true;
+}
+
+Json LocalMemoryPool::mr_info() const
+{
+    std::lock_guard<std::mutex> g(mu_);
+    Json out = Json::object();
+    for (size_t h = 0; h < regions_.size(); ++h) {
+        const MemoryRegion& r = regions_[h];
+        if (!r.alive) continue;
+        Json e      = Json::object();
+        e["handle"] = static_cast<long long>(h);
+        e["addr"]   = static_cast<unsigned long long>(r.addr);
+        e["rkey"]   = static_cast<unsigned long long>(r.rkey);
+        e["length"] = static_cast<unsigned long long>(r.length);
+        out[r.name] = e;
+    }
+    return out;
+}
+
+size_t LocalMemoryPool::live_count() const
+{
+    std::lock_guard<std::mutex> g(mu_);
+    size_t n = 0;
+    for (const auto& r : regions_) n += r.alive ? 1 : 0;
+    return n;
+}
+
+int32_t RemoteMemoryPool::register_remote_memory_region(const std::string& name, const Json& info)
+{
+    MemoryRegion r;
+    r.name   = name;
+    r.addr   = static_cast<uintptr_t>(info["addr"].as_uint());
+    r.length = info["length"].as_uint();
+    r.rkey   = info["rkey"].as_uint();
+    r.alive  = true;
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = by_name_.find(name);
+    if (it != by_name_.end()) {
+        MemoryRegion& cur = regions_[it->second];
+        if (cur.addr != r.addr || cur.length != r.length || cur.rkey != r.rkey || !cur.alive) cur = r;
+        return it->second;
+    }
+    regions_.push_back(r);
+    by_name_[name] = static_cast<int32_t>(regions_.size()) - 1;
+    return static_cast<int32_t>(regions_.size()) - 1;
+}
+
+int32_t RemoteMemoryPool::register_remote_memory_region(uintptr_t addr, uint64_t length, uint64_t rkey)
+{
+    char buf[40];
+    snprintf(buf, sizeof(buf), "remote_0x%llx", static_cast<unsigned long long>(addr));
+    Json info      = Json::object();
+    info["addr"]   = static_cast<unsigned long long>(addr);
+    info["length"] = static_cast<unsigned long long>(length);
+    info["rkey"]   = static_cast<unsigned long long>(rkey);
+    return register_remote_memory_region(buf, info);
+}
+
+int32_t RemoteMemoryPool::unregister_remote_memory_region(const std::string& name)
+{
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = by_name_.find(name);
+    if (it == by_name_.end()) return -1;
+    regions_[it->second].alive = false;
+    by_name_.erase(it);
+    return 0;
+}
+
+int32_t RemoteMemoryPool::get_remote_mr_handle(const std::string& name) const
+{
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = by_name_.find(name);
+    return it == by_name_.end() ? -1 : it->second;
+}
+
+bool RemoteMemoryPool::get_remote_mr(int32_t handle, MemoryRegion& out) const
+{
+    std::lock_guard<std::mutex> g(mu_);
+    if (handle < 0 || handle >= static_cast<int32_t>(regions_.size()) || !regions_[handle].alive) return false;
+    out = regions_[handle];
+    return true;
+}
+
+Json RemoteMemoryPool::remote_mr_info() const
+{
+    std::lock_guard<std::mutex> g(mu_);
+    Json out = Json::object();
+    for (size_t h = 0; h < regions_.size(); ++h) {
+        const MemoryRegion& r = regions_[h];
+        if (!r.alive) continue;
+        Json e      = Json::object();
+        e["handle"] = static_cast<long long>(h);
+        e["addr"]   = static_cast<unsigned long long>(r.addr);
+        e["rkey"]   = static_cast<unsigned long long>(r.rkey);
+        e["length"] = static_cast<unsigned long long>(r.length);
+        out[r.name] = e;
+    }
+    return out;
+}
+
+}  // namespace slime
