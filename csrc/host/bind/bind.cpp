@@ -185,6 +185,7 @@ PYBIND11_MODULE(_slime_c, m)
         .def("endpoint_info", &Endpoint::endpoint_info)
         .def("mr_info", &Endpoint::mr_info)
         .def("get_pool", &Endpoint::local_pool)
+        .def("set_pool", &Endpoint::set_local_pool, py::arg("pool"))
         .def("register_memory_region",
              py::overload_cast<const std::string&, uintptr_t, uintptr_t, size_t>(&Endpoint::register_memory_region),
              py::arg("name"), py::arg("data_ptr"), py::arg("offset"), py::arg("length"))

@@ -56,6 +56,8 @@ public:
     virtual void cancel_all() = 0;
     virtual int  process() { return 0; }  // one turn of the progress engine, for callers that drive it themselves
 
+    // Endpoints of one agent may share a registry so that a region has one handle agent-wide.
+    void set_local_pool(std::shared_ptr<LocalMemoryPool> pool) { local_pool_ = std::move(pool); }
     const std::shared_ptr<LocalMemoryPool>&  local_pool() const { return local_pool_; }
     const std::shared_ptr<RemoteMemoryPool>& remote_pool() const { return remote_pool_; }
 

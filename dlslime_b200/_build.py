@@ -15,13 +15,19 @@ independent translation units compile in parallel.
 
 from __future__ import annotations
 
-import concurrent.futures as cf
 import os
-import shutil
-import subprocess
 import sys
-import sysconfig
-from pathlib import Path
+
+# Run as a script, this file's directory comes first on sys.path, where the package's own
+# ``logging`` module would shadow the standard library's.
+_here = os.path.dirname(os.path.abspath(__file__))
+sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != _here]
+
+import concurrent.futures as cf  # noqa: E402
+import shutil  # noqa: E402
+import subprocess  # noqa: E402
+import sysconfig  # noqa: E402
+from pathlib import Path  # noqa: E402
 
 ROOT = Path(__file__).resolve().parent.parent
 CSRC = ROOT / "csrc"
