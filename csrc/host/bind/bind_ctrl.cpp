@@ -27,6 +27,16 @@ py::list entries_to_py(const std::vector<StreamEntry>& es)
     return out;
 }
 
+// Python callables kept by C++ threads: copies of the holder never touch the reference count, and the
+// last owner drops the callable with the GIL held.
+std::shared_ptr<py::function> hold(py::function fn)
+{
+    return std::shared_ptr<py::function>(new py::function(std::move(fn)), [](py::function* f) {
+        py::gil_scoped_acquire gil;
+        delete f;
+    });
+}
+
 std::vector<std::pair<std::string, std::string>> dict_fields(const py::dict& d)
 {
     std::vector<std::pair<std::string, std::string>> f;
@@ -44,9 +54,10 @@ void bind_ctrl(py::module_& m)
     py::class_<KvStore, std::shared_ptr<KvStore>>(c, "KvStore")
         .def(py::init<>())
         .def("set_clock", [](KvStore& s, py::function fn) {
-            s.set_clock([fn]() -> int64_t {
+            auto h = hold(std::move(fn));
+            s.set_clock([h]() -> int64_t {
                 py::gil_scoped_acquire gil;
-                return fn().cast<int64_t>();
+                return (*h)().cast<int64_t>();
             });
         })
         .def("now_ms", &KvStore::now_ms)
@@ -138,9 +149,10 @@ void bind_ctrl(py::module_& m)
         }, py::arg("key"), py::arg("min") = "-", py::arg("max") = "+", py::arg("count") = 0)
         .def("publish", &KvStore::publish)
         .def("subscribe", [](KvStore& s, const std::string& channel, py::function fn) {
-            return s.subscribe(channel, [fn](const std::string& ch, const std::string& msg) {
+            auto h = hold(std::move(fn));
+            return s.subscribe(channel, [h](const std::string& ch, const std::string& msg) {
                 py::gil_scoped_acquire gil;
-                fn(ch, msg);
+                (*h)(ch, msg);
             });
         })
         .def("unsubscribe", &KvStore::unsubscribe)

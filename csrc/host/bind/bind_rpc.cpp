@@ -22,9 +22,13 @@ py::bytes wait_bytes(ClientFuture& f)
 Writer python_writer(py::function fn)
 {
     // The Python callable receives (address, capacity) and returns the bytes it wrote.
-    return [fn](char* dst, size_t cap) -> size_t {
+    std::shared_ptr<py::function> h(new py::function(std::move(fn)), [](py::function* f) {
         py::gil_scoped_acquire gil;
-        return fn(reinterpret_cast<uintptr_t>(dst), cap).cast<size_t>();
+        delete f;
+    });
+    return [h](char* dst, size_t cap) -> size_t {
+        py::gil_scoped_acquire gil;
+        return (*h)(reinterpret_cast<uintptr_t>(dst), cap).cast<size_t>();
     };
 }
 

@@ -125,7 +125,10 @@ def build_host(verbose: bool = False, workers: int | None = None) -> Path:
     inc = [CSRC / "include", hdir, Path(pybind11.get_include()), Path(sysconfig.get_paths()["include"])]
     dep = _newest_header_mtime([CSRC / "include", hdir])
     (OBJ / "host").mkdir(parents=True, exist_ok=True)
-    cxx = os.environ.get("CXX", "g++")
+    # The system compiler links libstdc++ dynamically. Some environments export CXX as a wrapper that
+    # links it statically, and a second, exported copy of the C++ runtime inside an extension clashes
+    # with the one torch loads; --exclude-libs keeps any static archive private in either case.
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else os.environ.get("CXX", "g++")
     jobs, objs, main_objs = [], [], []
     for src in sorted(hdir.rglob("*.cpp")):
         rel = "_".join(src.relative_to(hdir).with_suffix("").parts)
@@ -139,7 +142,7 @@ def build_host(verbose: bool = False, workers: int | None = None) -> Path:
     changed = _compile_many(jobs, verbose, workers or min(8, os.cpu_count() or 4))
     out = host_ext_path()
     if changed or not out.exists():
-        _run([cxx, "-shared", "-o", out, *objs, "-pthread", "-ldl", "-lrt"], verbose)
+        _run([cxx, "-shared", "-o", out, *objs, "-Wl,--exclude-libs,ALL", "-pthread", "-ldl", "-lrt"], verbose)
     if main_objs:
         exe = nanoctrl_bin_path()
         if changed or not exe.exists():

@@ -25,3 +25,7 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(pytest.mark.skip(reason="no GPU in this environment"))
         if "multigpu" in item.keywords and n_gpu < 2:
             item.add_marker(pytest.mark.skip(reason="needs >= 2 GPUs"))
+
+
+def pytest_addoption(parser):
+    pass

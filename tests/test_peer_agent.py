@@ -1,0 +1,179 @@
+"""PeerAgent over the in-process control plane and TCP endpoints: handshake, named I/O translation,
+region lifecycle, scope isolation, peer exit, dropped handshake messages, lease expiry."""
+import ctypes
+import json
+import time
+
+import pytest
+
+from dlslime_b200.nanoctrl import start_local_nanoctrl
+from dlslime_b200.peer_agent import PeerAgent
+
+
+@pytest.fixture()
+def ctrl():
+    n = start_local_nanoctrl()
+    yield n
+    n.stop()
+
+
+def _region(agent, name, size=1 << 16, fill=None):
+    b = ctypes.create_string_buffer(size)
+    if fill is not None:
+        b.raw = bytes((fill + i) % 251 for i in range(size))
+    agent.register_memory_region(name, ctypes.addressof(b), 0, size)
+    return b
+
+
+def test_handshake_named_io_and_mirror_connection(ctrl):
+    a, b = PeerAgent(ctrl.url, alias="A", scope="s"), PeerAgent(ctrl.url, alias="B", scope="s")
+    try:
+        ba, bb = _region(a, "kv", fill=1), _region(b, "kv", fill=9)
+        conn = a.connect_to("B").wait(10)
+        assert conn.is_connected() and conn.conn_id == "A:tcp0:port1->B:tcp0:port1#qp1" and (conn.local_nic, conn.remote_nic) == ("tcp0", "tcp0")
+        assert a.list_agents() == ["A", "B"] and a.list_mem_keys("B") == ["kv"]
+        # (region, local_off, remote_off, len): local bytes [0,5000) land at remote offset 100
+        assert a.write("B", [("kv", 0, 100, 5000)]).wait(10) == 0 and bb.raw[100:5100] == ba.raw[:5000]
+        # 5-tuple names both regions; the peer answers on its mirrored connection
+        mirror = b.query_connection("A")
+        assert mirror is not None and mirror.wait(5).is_connected()
+        assert b.read("A", ("kv", "kv", 30000, 7, 1000)).wait(10) == 0 and bb.raw[30000:31000] == ba.raw[7:1007]
+        assert a.write_with_imm("B", [("kv", 0, 0, 16)], imm_data=42).wait(10) == 0
+        f = b.imm_recv("A")
+        assert f.wait(10) == 0 and f.imm_data() == 42
+        with pytest.raises(ValueError):
+            a.connect_to("A")
+        with pytest.raises(KeyError):
+            a.write("B", [("nope", 0, 0, 1)])
+    finally:
+        a.shutdown()
+        b.shutdown()
+
+
+def test_named_tuple_translation_is_pinned(ctrl):
+    """(local_region, remote_region, local_off, remote_off, len) -> (lh, rh, remote_off, local_off, len)."""
+    a, b = PeerAgent(ctrl.url, alias="A"), PeerAgent(ctrl.url, alias="B")
+    try:
+        keep = [_region(a, "x"), _region(a, "y"), _region(b, "x"), _region(b, "y")]  # registered memory must stay alive
+        a.connect_to("B").wait(10)
+        conn = a._get_connection("B")
+        lh, rh = a.get_handle(conn, "y"), a.get_handle(conn, "x", remote=True)
+        assert a._endpoint_assign(conn, ("y", "x", 16, 8, 32)) == (lh, rh, 8, 16, 32)
+        assert a._endpoint_assign(conn, ("x", 16, 8, 32))[2:] == (8, 16, 32)
+        assert a._maybe_endpoint_assign(conn, [(1, 2, 3, 4, 5)]) == [(1, 2, 3, 4, 5)]  # handle tuples pass through
+    finally:
+        a.shutdown()
+        b.shutdown()
+
+
+def test_region_publication_unregister_and_cache_validation(ctrl):
+    a, b = PeerAgent(ctrl.url, alias="A"), PeerAgent(ctrl.url, alias="B")
+    try:
+        ba = _region(a, "kv", fill=3)
+        bb = _region(b, "kv")
+        kv = ctrl.store
+        rec = json.loads(kv.get("mr:B:kv"))
+        assert rec == json.loads(kv.get("mr:B:kv:tcp0:1:TCP")) and rec["agent_name"] == "B" and rec["length"] == 1 << 16 and rec["lkey"] == 0
+        a.connect_to("B").wait(10)
+        assert a.write("B", [("kv", 0, 0, 64)]).wait(10) == 0
+        # B replaces the region by a bigger one at a new address: A notices through cache validation
+        big = ctypes.create_string_buffer(1 << 17)
+        assert b.unregister_memory_region("kv") and not b.unregister_memory_region("kv")
+        assert kv.get("mr:B:kv") is None and b.list_mem_keys() == []
+        b.register_memory_region("kv", ctypes.addressof(big), 0, 1 << 17)
+        assert a.write("B", [("kv", 0, 100000, 64)]).wait(10) == 0 and big.raw[100000:100064] == ba.raw[:64]
+        del bb
+    finally:
+        a.shutdown()
+        b.shutdown()
+
+
+def test_scopes_are_isolated_and_alias_conflict_is_fatal(ctrl):
+    a = PeerAgent(ctrl.url, alias="A", scope="one")
+    b = PeerAgent(ctrl.url, alias="A", scope="two")  # same alias, other scope: fine
+    try:
+        assert a.list_agents() == ["A"] and b.list_agents() == ["A"]
+        with pytest.raises(RuntimeError, match="already registered"):
+            PeerAgent(ctrl.url, alias="A", scope="one")
+        with pytest.raises(KeyError):
+            a.connect_to("B")
+        auto = PeerAgent(ctrl.url, scope="one")
+        assert auto.alias.startswith("agent-")
+        auto.shutdown()
+    finally:
+        a.shutdown()
+        b.shutdown()
+
+
+def test_peer_shutdown_drops_the_connection_and_fails_waiters(ctrl):
+    a, b = PeerAgent(ctrl.url, alias="A"), PeerAgent(ctrl.url, alias="B")
+    try:
+        keep = [_region(a, "kv"), _region(b, "kv")]  # registered memory must stay alive
+        a.connect_to("B").wait(10)
+        b.query_connection("A").wait(5)
+        waiter = b.imm_recv("A")
+        a.shutdown()
+        assert waiter.wait(5) == 403  # the cleanup notice shut B's endpoint down; nobody hangs
+        deadline = time.monotonic() + 5
+        while b.get_connections() and time.monotonic() < deadline:
+            time.sleep(0.02)
+        assert b.get_connections() == {}
+        assert not ctrl.store.exists("agent:A") and ctrl.store.keys("mr:A:*") == []
+        # and A can come back under the same alias and reconnect
+        a2 = PeerAgent(ctrl.url, alias="A")
+        keep.append(_region(a2, "kv"))
+        a2.connect_to("B").wait(10)
+        assert a2.write("B", [("kv", 0, 0, 8)]).wait(10) == 0
+        a2.shutdown()
+    finally:
+        a.shutdown()
+        b.shutdown()
+
+
+def test_dropped_handshake_message_times_out_cleanly(ctrl):
+    a, b = PeerAgent(ctrl.url, alias="A"), PeerAgent(ctrl.url, alias="B")
+    try:
+        b._mailbox.message_filter = lambda msg: msg.get("type") != "qp_ready"  # B never sees A's announcement
+        conn = a.connect_to("B")
+        with pytest.raises(TimeoutError):
+            conn.wait(0.5)
+        assert conn.state in ("pending", "connecting")
+    finally:
+        a.shutdown()
+        b.shutdown()
+
+
+def test_expired_lease_is_renewed_by_re_registration(ctrl):
+    a = PeerAgent(ctrl.url, alias="A")
+    try:
+        keep = _region(a, "kv")
+        ctrl.store.delete("agent:A")  # what a missed lease looks like to the control plane
+        a._heartbeat_once()
+        assert ctrl.store.exists("agent:A") and json.loads(ctrl.store.hget("agent:A", "memory_keys")) == ["kv"]
+    finally:
+        a.shutdown()
+
+
+def test_obs_reporter_snapshot_and_stopped_marker(ctrl):
+    from dlslime_b200 import _slime_c as c
+
+    c.obs_set_enabled_for_test(True)
+    c.obs_reset_for_test()
+    a, b = PeerAgent(ctrl.url, alias="A", enable_obs=True), PeerAgent(ctrl.url, alias="B")
+    try:
+        keep = [_region(a, "kv"), _region(b, "kv")]  # registered memory must stay alive
+        a.connect_to("B").wait(10)
+        assert a.write("B", [("kv", 0, 0, 4096)]).wait(10) == 0
+        snap = a._obs.report_once()
+        assert snap["schema_version"] == 1 and snap["peer_id"] == "A" and snap["summary"]["completed_bytes_total"] >= 4096
+        assert snap["connections"][0]["peer"] == "B" and snap["connections"][0]["connected"]
+        assert any(n["kind"] == "tcp" for n in snap["nics"])
+        stored = json.loads(ctrl.store.get("obs:peer:A"))
+        assert stored["session_id"] == snap["session_id"] and 0 < ctrl.store.pttl("obs:peer:A") <= 180_000
+    finally:
+        a.shutdown()
+        b.shutdown()
+        c.obs_reset_for_test()
+        c.obs_set_enabled_for_test(False)
+    stopped = json.loads(ctrl.store.get("obs:peer:A"))
+    assert stopped["status"] == "stopped" and ctrl.store.pttl("obs:peer:A") <= 15_000
