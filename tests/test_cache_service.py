@@ -1,0 +1,71 @@
+"""DLSlimeCache service + client over the control plane: HTTP contract, put/get of real bytes, discovery."""
+import ctypes
+import json
+import urllib.error
+import urllib.request
+
+import pytest
+
+from dlslime_b200._slime_c import Assignment
+from dlslime_b200.cache import CacheClient, CacheHttpServer, CacheServer, CacheService, discover_cache_url, get_json, post_json
+from dlslime_b200.nanoctrl import NanoCtrlClient, start_local_nanoctrl
+from dlslime_b200.peer_agent import PeerAgent
+
+K = 1024
+
+
+def test_http_contract_without_a_peer_agent():
+    http = CacheHttpServer(CacheService(slab_size=128 * K, memory_size=512 * K)).start()
+    try:
+        assert get_json(http.url, "/healthz") == {"ok": True}
+        assert get_json(http.url, "/stats")["num_slabs"] == 4
+        m = post_json(http.url, "/store", {"peer_agent_id": "e", "assignments": [{"mr_key": 1, "remote_mr_key": 2, "target_offset": 10, "source_offset": 0, "length": 200 * K}]})
+        assert m["version"] == 1 and m["slab_ids"] == [0, 1] and m["total_bytes"] == 200 * K
+        assert [(a["target_offset"], a["source_offset"], a["length"]) for a in m["assignments"]] == [(10, 0, 128 * K), (10 + 128 * K, 128 * K, 72 * K)]
+        assert post_json(http.url, "/query", {"peer_agent_id": "e", "version": 1}) == m
+        with pytest.raises(RuntimeError, match="HTTP 404"):
+            post_json(http.url, "/query", {"peer_agent_id": "e", "version": 9})
+        with pytest.raises(RuntimeError, match="HTTP 400"):
+            post_json(http.url, "/store", {"peer_agent_id": "", "assignments": []})
+        with pytest.raises(RuntimeError, match="HTTP 503"):
+            get_json(http.url, "/peer-agent")
+        assert post_json(http.url, "/delete", {"peer_agent_id": "e", "version": 1}) == {"deleted": True}
+        assert post_json(http.url, "/delete", {"peer_agent_id": "e", "version": 1}) == {"deleted": False}
+        req = urllib.request.Request(http.url + "/store", data=b"not json", method="POST")
+        with pytest.raises(urllib.error.HTTPError) as e:
+            urllib.request.build_opener(urllib.request.ProxyHandler({})).open(req)
+        assert e.value.code == 400 and "error" in json.loads(e.value.read())
+    finally:
+        http.stop()
+
+
+def test_put_get_roundtrip_through_the_control_plane():
+    ctrl = start_local_nanoctrl()
+    srv = CacheServer(ctrl.url, slab_size=128 * K, memory_size=8 * 128 * K, alias="cache-agent:0", scope="c")
+    eng = PeerAgent(ctrl.url, alias="engine-a", scope="c")
+    try:
+        assert discover_cache_url(ctrl.url, scope="c") == srv.url
+        ent = NanoCtrlClient(ctrl.url, scope="c").get_entity_info("cache:0")
+        assert ent["kind"] == "cache" and ent["endpoint"]["protocol"] == "http" and ent["endpoint"]["port"] == srv.http.port
+        buf = ctypes.create_string_buffer(1 << 20)
+        buf.raw = bytes(i % 253 for i in range(1 << 20))
+        eng.register_memory_region("kv", ctypes.addressof(buf), 0, 1 << 20)
+        cl = CacheClient(ctrl=ctrl.url, scope="c", peer_agent=eng)
+        info = cl.connect_to_server()
+        assert info["peer_agent_id"] == "cache-agent:0" and info["cache_mr_name"] == "cache" and info["memory_size"] == 8 * 128 * K
+        m = cl.put("kv", [(4096, 300 * K), (800000, 1000)])
+        assert m["slab_ids"] == [0, 1, 2, 3] and cl.stats()["used_slabs"] == 4
+        # the manifest's source_offset is the offset inside the cache region: the bytes really are there
+        first = m["assignments"][0]
+        assert bytes(srv.service.cache_storage)[first["source_offset"]:first["source_offset"] + 16] == buf.raw[4096:4112]
+        orig = buf.raw
+        ctypes.memset(ctypes.addressof(buf), 0, 1 << 20)
+        cl.get("kv", "engine-a", m["version"])
+        assert buf.raw[4096:4096 + 300 * K] == orig[4096:4096 + 300 * K] and buf.raw[800000:801000] == orig[800000:801000]
+        assert buf.raw[:4096] == bytes(4096)
+        assert cl.delete("engine-a", m["version"]) and cl.stats()["used_slabs"] == 0
+        assert cl.store([Assignment(0, 0, 0, 0, 64)], peer_agent_id="other")["peer_agent_id"] == "other"
+    finally:
+        eng.shutdown()
+        srv.stop()
+        ctrl.stop()
