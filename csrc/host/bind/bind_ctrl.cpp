@@ -4,6 +4,7 @@
 #include "ctrl/kvstore.h"
 #include "ctrl/nanoctrl.h"
 #include "ctrl/net_server.h"
+#include "ctrl/obs_view.h"
 
 using namespace slime;
 using namespace slime::ctrl;
@@ -183,6 +184,18 @@ void bind_ctrl(py::module_& m)
                 return py::make_tuple(r.status, r.body);
             },
             py::arg("method"), py::arg("path"), py::arg("body") = "", "Dispatch one request without going through a socket.");
+
+    c.def("snapshot_state", &snapshot_state, py::arg("snapshot"), py::arg("now_ms"), py::arg("stale_ms") = 45000);
+    c.def("human_bps", &human_bps);
+    c.def("human_bytes", &human_bytes);
+    c.def("obs_view", [](const std::string& address, const std::string& scope, const std::string& view, int64_t stale_ms, bool as_json) {
+        std::vector<PeerSnapshot> peers;
+        {
+            py::gil_scoped_release nogil;
+            peers = fetch_snapshots(address, scope, stale_ms);
+        }
+        return render_obs_view(peers, view, as_json);
+    }, py::arg("address"), py::arg("scope") = "", py::arg("view") = "status", py::arg("stale_ms") = 45000, py::arg("as_json") = false);
 
     py::class_<RespServer, std::shared_ptr<RespServer>>(c, "RespServer")
         .def(py::init<std::shared_ptr<KvStore>>())
