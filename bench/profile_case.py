@@ -1,0 +1,85 @@
+#!/usr/bin/env python
+"""Small, self-terminating cases for profiler captures (one or a few launches of one kernel).
+
+    python bench/profile_case.py gemm        # 4096 x 4096 x 4096 bf16 GEMM, 3 launches
+    python bench/profile_case.py grouped     # grouped SwiGLU gate/up + down GEMM, 8 experts x 512 rows, 2 launches each
+    python bench/profile_case.py moe_step    # one single-GPU MoE layer step (T=1024, 32 experts of the 7168/2048 shape)
+    python bench/profile_case.py quant       # fp8 1x128 quantise + dequantise of 16384 x 7168
+    python bench/profile_case.py copy        # 1024 x 64 KiB segment batch through the NVLink endpoint (local peer)
+
+Each case holds well under 4 GB on the device and exits by itself in seconds.
+"""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def gemm_case():
+    from dlslime_b200.ops import gemm
+
+    a = torch.randn(4096, 4096, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(4096, 4096, device="cuda") * 0.02).to(torch.bfloat16)
+    out = torch.empty(4096, 4096, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        gemm.gemm_bf16(a, b, out=out)
+
+
+def grouped_case():
+    from dlslime_b200.ops import gemm
+
+    g, rows, k, inter = 8, 512, 7168, 2048
+    offs = torch.arange(0, g + 1, dtype=torch.int32, device="cuda") * rows
+    x = torch.randn(g * rows, k, device="cuda").to(torch.bfloat16)
+    w13 = (torch.randn(g, 2 * inter, k, device="cuda") * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(g, k, inter, device="cuda") * 0.02).to(torch.bfloat16)
+    h = torch.empty(g * rows, inter, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty(g * rows, k, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):
+        gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU)
+        gemm.grouped_gemm_bf16(h, w2, offs, out=y)
+
+
+def moe_case():
+    from dlslime_b200.models.moe import ExpertParallelMoE, MoEConfig
+
+    cfg = MoEConfig(num_experts=32, topk=8, hidden=7168, intermediate=2048)
+    layer = ExpertParallelMoE(cfg, max_tokens=1024)
+    x = torch.randn(1024, cfg.hidden, device="cuda").to(torch.bfloat16)
+    lg = torch.randn(1024, cfg.num_experts, device="cuda")
+    for _ in range(2):
+        layer(x, lg)
+
+
+def quant_case():
+    from dlslime_b200.ops import quant
+
+    x = torch.randn(16384, 7168, device="cuda").to(torch.bfloat16)
+    for _ in range(2):
+        q, s = quant.fp8_quant_1x128(x)
+        quant.fp8_dequant_1x128(q, s)
+
+
+def copy_case():
+    from dlslime_b200.ops.nvlink import NVLinkEndpoint
+
+    n, seg = 1024, 64 << 10
+    src = torch.randint(0, 255, (n * seg * 2,), dtype=torch.uint8, device="cuda")
+    dst = torch.zeros(n * seg, dtype=torch.uint8, device="cuda")
+    a, b = NVLinkEndpoint(), NVLinkEndpoint()
+    a.register_memory_region(dst.data_ptr(), 0, dst.numel(), "dst")
+    b.register_memory_region(src.data_ptr(), 0, src.numel(), "src")
+    a.connect(b.endpoint_info())
+    perm = torch.randperm(2 * n)[:n].tolist()
+    for _ in range(2):
+        a.read([("dst", "src", p * seg, i * seg, seg) for i, p in enumerate(perm)]).wait()
+    a.close()
+    b.close()
+
+
+if __name__ == "__main__":
+    {"gemm": gemm_case, "grouped": grouped_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
+    torch.cuda.synchronize()
+    print("done", sys.argv[1])
