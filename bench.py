@@ -174,13 +174,25 @@ def run_ours(args, rank, world, local):
     x_stage = torch.empty_like(dev_x[0])
     lg_stage = torch.empty_like(dev_lg[0])
 
+    # Decode-size steps are launch-bound: the whole layer is replayed from one CUDA graph on fixed buffers.
+    graph = layer.capture(x_stage, lg_stage, out) if args.mode == "ll" and not args.no_graph else None
+
+    def run_layer(x, lg):
+        if graph is None:
+            layer.forward(x, lg, out=out)
+        else:
+            if x is not x_stage:
+                x_stage.copy_(x, non_blocking=True)
+                lg_stage.copy_(lg, non_blocking=True)
+            graph.replay()
+
     def step_device(i):
-        layer.forward(dev_x[i % n_in], dev_lg[i % n_in], out=out)
+        run_layer(dev_x[i % n_in], dev_lg[i % n_in])
 
     def step_e2e(i):
         x_stage.copy_(host_x[i % n_in], non_blocking=True)
         lg_stage.copy_(host_lg[i % n_in], non_blocking=True)
-        layer.forward(x_stage, lg_stage, out=out)
+        run_layer(x_stage, lg_stage)
         host_out.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads the result every step
 
@@ -208,7 +220,7 @@ def run_ours(args, rank, world, local):
     # phase breakdown (one extra instrumented pass; not part of the reported value)
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
     sync_all(world)
-    e = layer.buf.next_epoch()
+    e = None  # device-resident step counter, as in the timed loops
     evs[0].record()
     layer.step_route(dev_lg[0], T, e)
     evs[1].record()
@@ -232,7 +244,7 @@ def run_ours(args, rank, world, local):
     return {
         "ms_dev": ms_dev, "ms_e2e": ms_e2e, "clocks": clocks, "breakdown_us": breakdown, "T": T,
         "h2d": host_x[0].numel() * 2 + host_lg[0].numel() * 4, "d2h": host_out.numel() * 2,
-        "launches": 6 * args.steps, "weights_gb": weights_gb, "nvlink_bytes_per_rank": nvlink_bytes,
+        "launches": 6 * args.steps, "cuda_graph": graph is not None, "weights_gb": weights_gb, "nvlink_bytes_per_rank": nvlink_bytes,
     }
 
 
@@ -255,6 +267,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--mode", choices=["ll", "normal"], default="normal")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-graph", action="store_true", help="ll mode: launch the kernels one by one instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -281,7 +294,7 @@ def main():
         "nvlink_gbs_per_rank": round(res["nvlink_bytes_per_rank"] / (res["ms_dev"] * 1e-3) / 1e9, 2),
         "config": {
             "model": "DeepSeek-V3-shaped MoE layer: 256 experts, top-8, hidden 7168, intermediate 2048",
-            "mode": args.mode, "tokens_per_rank": T, "global_batch": world * T, "seq_len": 1,
+            "mode": args.mode, "cuda_graph": bool(res.get("cuda_graph")), "tokens_per_rank": T, "global_batch": world * T, "seq_len": 1,
             "parallelism": f"ep{world}", "experts_per_rank": E // world,
             "l2": f"inputs larger than L2: {res['weights_gb']:.1f} GB of expert weights per rank are streamed every step",
         },

@@ -38,6 +38,7 @@ int slime_ipc_open(const unsigned char* ipc_handle64, void** ptr_out);
 int slime_ipc_close(void* ptr);
 int slime_enable_peer_access(int peer_device);
 int slime_memset_async(void* ptr, int value, unsigned long long bytes, void* stream);
+int slime_memcpy_async(void* dst, const void* src, unsigned long long bytes, void* stream);
 
 // ---- fp8 block-scaled quantisation (fp8_quant.cu) ---------------------------
 int slime_fp8_quant_1x128(const void* x, void* q, float* scales, long long rows, int cols, long long ldx,

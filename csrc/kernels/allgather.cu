@@ -26,12 +26,17 @@ struct AgConfig {
     unsigned long long slot_bytes;  // capacity of one rank's contribution
     unsigned long long peers[8];
     unsigned long long wait_ns;
+    // Optional device-resident step counter: when set, `step` arguments are offsets to *step_ptr (push passes 1
+    // and stores the new value when its last CTA is done, wait passes 0), which makes a call replayable from
+    // a CUDA graph.
+    unsigned long long step_ptr;
 };
 
 __global__ void __launch_bounds__(256) ag_push_kernel(AgConfig cfg, const uint4* __restrict__ src, unsigned long long nvec,
                                                      unsigned long long stride_bytes, unsigned long long step,
                                                      unsigned int* block_counter, int do_wait, KernelStatus* st)
 {
+    if (cfg.step_ptr) step += *reinterpret_cast<const volatile unsigned long long*>(cfg.step_ptr);
     const int                half = static_cast<int>(step & 1);
     const unsigned long long base = cfg.off_data + (static_cast<unsigned long long>(half) * cfg.world) * cfg.slot_bytes
                                     + static_cast<unsigned long long>(cfg.rank) * stride_bytes;
@@ -61,10 +66,13 @@ __global__ void __launch_bounds__(256) ag_push_kernel(AgConfig cfg, const uint4*
         const unsigned long long* f = reinterpret_cast<const unsigned long long*>(cfg.peers[cfg.rank] + cfg.off_flags) + half * cfg.world + threadIdx.x;
         wait_flag_ge(f, step, st, 70, threadIdx.x, cfg.wait_ns ? cfg.wait_ns : kDefaultWaitNs);
     }
+    // only this CTA is still running, and every CTA read the old value on entry
+    if (cfg.step_ptr && threadIdx.x == 0) *reinterpret_cast<volatile unsigned long long*>(cfg.step_ptr) = step;
 }
 
 __global__ void ag_wait_kernel(AgConfig cfg, unsigned long long step, KernelStatus* st)
 {
+    if (cfg.step_ptr) step += *reinterpret_cast<const volatile unsigned long long*>(cfg.step_ptr);
     const int half = static_cast<int>(step & 1);
     if (threadIdx.x < cfg.world) {
         const unsigned long long* f = reinterpret_cast<const unsigned long long*>(cfg.peers[cfg.rank] + cfg.off_flags) + half * cfg.world + threadIdx.x;

@@ -50,7 +50,16 @@ struct EpConfig {
     unsigned long long off_combine;        // bf16 [max_tokens * topk][hidden]
     unsigned long long peers[kMaxWorld];   // base address of every rank's region in this rank's address space
     unsigned long long wait_ns;
+    // Optional device-resident step counter. When set, the `epoch` argument of every kernel is an offset
+    // to *epoch_ptr (route passes 1 and stores the new value when its last CTA finishes, the kernels that
+    // follow pass 0), so a whole step can be replayed from a CUDA graph with nothing changing on the host.
+    unsigned long long epoch_ptr;
 };
+
+__device__ __forceinline__ unsigned long long resolve_epoch(const EpConfig& c, unsigned long long arg)
+{
+    return c.epoch_ptr ? *reinterpret_cast<const volatile unsigned long long*>(c.epoch_ptr) + arg : arg;
+}
 
 template<typename T>
 __device__ __forceinline__ T* at(const EpConfig& c, int rank, unsigned long long off)
@@ -71,6 +80,7 @@ __global__ void __launch_bounds__(256) ep_route_kernel(EpConfig cfg, const float
     const int t    = blockIdx.x * 8 + warp;
     const int E    = cfg.num_experts;
     const int K    = cfg.topk;
+    epoch          = resolve_epoch(cfg, epoch);  // read by every CTA before it reports in below
     if (t < T) {
         int   my_e = -1;
         float my_w = 0.f;
@@ -154,7 +164,11 @@ __global__ void __launch_bounds__(256) ep_route_kernel(EpConfig cfg, const float
                 st_release_sys(dst, word);
             }
         }
-        if (threadIdx.x == 0) *block_counter = 0;
+        if (threadIdx.x == 0) {
+            *block_counter = 0;
+            // every other CTA has read the old value already (it did so before counting itself in)
+            if (cfg.epoch_ptr) *reinterpret_cast<volatile unsigned long long*>(cfg.epoch_ptr) = epoch;
+        }
     }
 }
 
@@ -174,6 +188,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpConfig cfg, const __
     const int E = cfg.num_experts, El = cfg.experts_per_rank, W = cfg.world, K = cfg.topk, H = cfg.hidden;
     const unsigned long long lim = cfg.wait_ns ? cfg.wait_ns : kDefaultWaitNs;
 
+    epoch = resolve_epoch(cfg, epoch);
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
     // 1. wait for the W count rows of this epoch and derive the layout
@@ -295,6 +310,7 @@ __global__ void __launch_bounds__(256) ep_recv_dequant_kernel(EpConfig cfg, cons
                                                              __nv_bfloat16* __restrict__ y, long long ldy,
                                                              unsigned long long epoch, KernelStatus* st)
 {
+    epoch = resolve_epoch(cfg, epoch);
     if (!wait_all_ranks(cfg, cfg.off_dispatch_done, epoch, st, 30)) return;
     const int       rows = group_offsets[cfg.experts_per_rank];
     const int       gpr  = cfg.hidden / 128;
@@ -346,6 +362,7 @@ __global__ void __launch_bounds__(256) ep_combine_push_kernel(EpConfig cfg, cons
 // ---------------------------------------------------------------------------
 __global__ void ep_signal_kernel(EpConfig cfg, unsigned long long off, unsigned long long epoch)
 {
+    epoch = resolve_epoch(cfg, epoch);
     if (threadIdx.x < cfg.world) {
         fence_acq_rel_sys();
         st_release_sys(at<unsigned long long>(cfg, threadIdx.x, off) + cfg.rank, epoch);
@@ -357,6 +374,7 @@ __global__ void __launch_bounds__(256) ep_combine_reduce_kernel(EpConfig cfg, in
                                                                __nv_bfloat16* __restrict__ out, long long ldo,
                                                                unsigned long long epoch, int do_signal, KernelStatus* st)
 {
+    epoch = resolve_epoch(cfg, epoch);
     if (do_signal && blockIdx.x == 0 && threadIdx.x < cfg.world) {
         fence_acq_rel_sys();
         st_release_sys(at<unsigned long long>(cfg, threadIdx.x, cfg.off_combine_done) + cfg.rank, epoch);

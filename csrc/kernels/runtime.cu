@@ -169,6 +169,14 @@ int slime_enable_peer_access(int peer_device)
     return 0;
 }
 
+// Plain cudaMemcpyAsync between two device addresses (local or peer-mapped): the per-segment copy that
+// benchmarks use as the baseline for the batched kernels.
+int slime_memcpy_async(void* dst, const void* src, unsigned long long bytes, void* stream)
+{
+    SLIME_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+    return 0;
+}
+
 int slime_memset_async(void* ptr, int value, unsigned long long bytes, void* stream)
 {
     SLIME_CUDA_OK(cudaMemsetAsync(ptr, value, bytes, static_cast<cudaStream_t>(stream)));

@@ -32,6 +32,7 @@ _SIGNATURES = {
     "slime_ipc_close": [c_void_p],
     "slime_enable_peer_access": [c_int],
     "slime_memset_async": [c_void_p, c_int, c_ulonglong, c_void_p],
+    "slime_memcpy_async": [c_void_p, c_void_p, c_ulonglong, c_void_p],
     "slime_fp8_quant_1x128": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong, c_void_p],
     "slime_fp8_dequant_1x128": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong, c_void_p],
     "slime_fp8_quant_128x128": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p],

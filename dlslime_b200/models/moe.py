@@ -102,14 +102,32 @@ class ExpertParallelMoE:
         T = x.shape[0]
         if out is None:
             out = torch.empty_like(x)
-        e = self.buf.next_epoch()
-        self.step_route(logits, T, e)
-        self.step_dispatch(x, e)
-        self.step_experts(T, e)
-        self.step_combine(out, T, e)
+        # epoch=None: the step counter lives on the device, so this sequence of launches is graph-capturable
+        self.step_route(logits, T, None)
+        self.step_dispatch(x, None)
+        self.step_experts(T, None)
+        self.step_combine(out, T, None)
         return out
 
     __call__ = forward
+
+    def capture(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor) -> "torch.cuda.CUDAGraph":
+        """Capture one forward on fixed buffers into a CUDA graph (decode-size steps are launch-bound).
+
+        ``x``, ``logits`` and ``out`` become the graph's static input / output buffers: copy new inputs into
+        them and call ``graph.replay()``. Runs two eager warm-up steps first, on every rank alike.
+        """
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.forward(x, logits, out)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.forward(x, logits, out)
+        return graph
 
 
 def emulated_forward(layers: list[ExpertParallelMoE], xs, logits):

@@ -83,7 +83,7 @@ class PrefillSender:
     def __init__(self, shape: KVShape, dst_cache: PagedKVCache, max_tokens: int, comm_blocks: int = 32):
         self.shape, self.dst, self.max_tokens = shape, dst_cache, max_tokens
         self.kv_stage = torch.empty((shape.layers, 2, max_tokens, shape.row), dtype=shape.dtype, device="cuda")
-        self.comm_stream = torch.cuda.Stream()
+        self.comm_stream = torch.cuda.Stream(priority=-1)  # transfer CTAs should be placed ahead of the next GEMM's
         self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.comm_blocks = comm_blocks
         self.step = 0

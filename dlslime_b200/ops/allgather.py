@@ -22,7 +22,7 @@ from ._common import default_status, ptr, stream_ptr
 _v, _i, _ull = ctypes.c_void_p, ctypes.c_int, ctypes.c_ulonglong
 _lib.declare("slime_ag_push", [ctypes.c_char_p, _v, _ull, _ull, _ull, _v, _i, _i, _v, _v])
 _lib.declare("slime_ag_wait", [ctypes.c_char_p, _ull, _v, _v])
-_CFG_FMT = "<2i3Q8QQ"
+_CFG_FMT = "<2i3Q8QQQ"
 
 
 class AllGatherLLBuffer:
@@ -46,15 +46,20 @@ class AllGatherLLBuffer:
         self.off_data = self.base_off
         self.off_flags = self.base_off + 2 * self.world * self.slot_bytes
         self.step = 0
+        # Device-resident step counter: the kernels read and advance it themselves, so calls can be captured in
+        # a CUDA graph and replayed. ``self.step`` mirrors it on the host for the view bookkeeping.
+        self.step_dev = torch.zeros(1, dtype=torch.int64, device="cuda")
         self.wait_ns = wait_ns
         self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")
         self._counter_ptr = self.counter.data_ptr()
         self.status = default_status()
         self._cfg = self._pack()
+        self._views: dict = {}
 
     def _pack(self) -> bytes:
         peers = list(self.heap.peer_ptrs) + [0] * (8 - self.world)
-        return struct.pack(_CFG_FMT, self.rank, self.world, self.off_data, self.off_flags, self.slot_bytes, *peers, self.wait_ns)
+        return struct.pack(_CFG_FMT, self.rank, self.world, self.off_data, self.off_flags, self.slot_bytes, *peers, self.wait_ns,
+                           self.step_dev.data_ptr())
 
     @classmethod
     def emulated_group(cls, world: int, max_bs: int, msg_size: int, dtype: torch.dtype, wait_ns: int = 0):
@@ -75,17 +80,22 @@ class AllGatherLLBuffer:
 
     def _result(self, step: int, bs: int) -> torch.Tensor:
         half = step & 1
-        off = self.off_data + half * self.world * self.slot_bytes
-        return self.heap.view(off, (self.world * bs, self.msg_size), self.dtype, rank=self.rank)
+        v = self._views.get((half, bs))
+        if v is None:  # building a tensor over raw memory is slow; the handful of shapes in use are kept
+            off = self.off_data + half * self.world * self.slot_bytes
+            v = self._views[(half, bs)] = self.heap.view(off, (self.world * bs, self.msg_size), self.dtype, rank=self.rank)
+        return v
 
     def _issue(self, x: torch.Tensor, do_wait: bool, max_blocks: int = 0) -> tuple[int, int]:
-        assert x.is_contiguous() and x.dtype == self.dtype and x.shape[-1] == self.msg_size
+        if not (x.is_contiguous() and x.dtype == self.dtype and x.shape[-1] == self.msg_size):
+            raise ValueError("all_gather_ll needs a contiguous [bs, msg_size] tensor of the buffer's dtype")
         bs = x.numel() // self.msg_size
-        assert bs <= self.max_bs
+        if bs > self.max_bs:
+            raise ValueError(f"batch of {bs} exceeds max_bs={self.max_bs}")
         self.step += 1
         nbytes = x.numel() * self.itemsize
-        _lib.call("slime_ag_push", self._cfg, ptr(x), nbytes, nbytes, self.step, self._counter_ptr, int(do_wait),
-                  max_blocks, self.status.dev_ptr, stream_ptr())
+        _lib.call("slime_ag_push", self._cfg, x.data_ptr(), nbytes, nbytes, 1, self._counter_ptr, int(do_wait),
+                  max_blocks, self.status.dev_ptr, torch.cuda.current_stream().cuda_stream)
         return self.step, bs
 
     def all_gather_ll(self, x: torch.Tensor) -> torch.Tensor:
@@ -102,7 +112,7 @@ class AllGatherLLBuffer:
         step, bs = self._issue(x, do_wait=False)
 
         def hook() -> torch.Tensor:
-            _lib.call("slime_ag_wait", self._cfg, step, self.status.dev_ptr, stream_ptr())
+            _lib.call("slime_ag_wait", self._cfg, 0, self.status.dev_ptr, stream_ptr())
             return self._result(step, bs)
 
         return hook

@@ -18,7 +18,7 @@ from .. import _lib
 from ..parallel.symm import SymmetricHeap
 from ._common import default_status, ptr, stream_ptr
 
-_CFG_FMT = "<8i8Q8QQ"
+_CFG_FMT = "<8i8Q8QQQ"
 
 
 @dataclass
@@ -103,18 +103,22 @@ class EpBuffer:
         self.send_count = torch.zeros(num_experts, dtype=torch.int32, device=dev)
         self.block_counters = torch.zeros(4, dtype=torch.int32, device=dev)
         self.group_offsets = torch.zeros(self.experts_per_rank + 1, dtype=torch.int32, device=dev)
+        # Device-resident step counter for graph-replayable steps (methods called with epoch=None use it).
+        self.epoch_dev = torch.zeros(1, dtype=torch.int64, device=dev)
         self._cfg = self._pack_cfg()
+        self._cfg_dev = self._pack_cfg(self.epoch_dev.data_ptr())
         self.status = default_status()
+        self._bc0, self._bc1 = self.block_counters[0:].data_ptr(), self.block_counters[1:].data_ptr()
 
     # -- config ------------------------------------------------------------------
-    def _pack_cfg(self) -> bytes:
+    def _pack_cfg(self, epoch_ptr: int = 0) -> bytes:
         L, b = self.layout, self.base_off
         peers = list(self.heap.peer_ptrs) + [0] * (8 - self.world)
         return struct.pack(
             _CFG_FMT, self.rank, self.world, self.num_experts, self.experts_per_rank, self.topk, self.hidden,
             self.max_tokens, self.recv_cap,
             b + L.off_counts, b + L.off_dispatch_done, b + L.off_combine_done, b + L.off_barrier,
-            b + L.off_x, b + L.off_scale, b + L.off_info, b + L.off_combine, *peers, self.wait_ns)
+            b + L.off_x, b + L.off_scale, b + L.off_info, b + L.off_combine, *peers, self.wait_ns, epoch_ptr)
 
     @classmethod
     def emulated_group(cls, world: int, num_experts: int, topk: int, hidden: int, max_tokens: int,
@@ -138,6 +142,7 @@ class EpBuffer:
     def connect_full_mesh(self, infos) -> None:
         self.heap.connect(infos)
         self._cfg = self._pack_cfg()
+        self._cfg_dev = self._pack_cfg(self.epoch_dev.data_ptr())
 
     # -- views into this rank's region ----------------------------------------------
     def _view(self, off, shape, dtype):
@@ -173,34 +178,44 @@ class EpBuffer:
         self.epoch += 1
         return self.epoch
 
-    def route(self, logits: torch.Tensor | None, T: int, epoch: int, renormalize: bool = False) -> None:
-        """Top-k routing (or counting of caller-provided ``topk_idx``) and count broadcast."""
-        _lib.call("slime_ep_route", self._cfg, ptr(logits), T, ptr(self.topk_idx), ptr(self.topk_w), ptr(self.slot),
-                  ptr(self.send_count), self.block_counters[0:].data_ptr(), epoch, int(renormalize), stream_ptr())
+    # Every step method takes ``epoch``: an explicit step number (the caller counts), or None to use the
+    # device-resident counter, which route() advances; the latter form can be captured in a CUDA graph.
+    def _mode(self, epoch, first: bool = False):
+        return (self._cfg_dev, 1 if first else 0) if epoch is None else (self._cfg, epoch)
 
-    def dispatch(self, x: torch.Tensor, epoch: int, max_blocks: int = 0) -> None:
+    def route(self, logits: torch.Tensor | None, T: int, epoch: int | None = None, renormalize: bool = False) -> None:
+        """Top-k routing (or counting of caller-provided ``topk_idx``) and count broadcast."""
+        cfg, e = self._mode(epoch, first=True)
+        _lib.call("slime_ep_route", cfg, ptr(logits), T, ptr(self.topk_idx), ptr(self.topk_w), ptr(self.slot),
+                  ptr(self.send_count), self._bc0, e, int(renormalize), stream_ptr())
+
+    def dispatch(self, x: torch.Tensor, epoch: int | None = None, max_blocks: int = 0) -> None:
         """Quantise ``x`` [T, hidden] bf16 to fp8 and push every (token, expert) copy to its owner."""
         T = x.shape[0]
         assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.shape[1] == self.hidden
-        _lib.call("slime_ep_dispatch", self._cfg, ptr(x), x.stride(0), T, ptr(self.topk_idx), ptr(self.slot),
-                  ptr(self.group_offsets), self.block_counters[1:].data_ptr(), epoch, max_blocks,
+        cfg, e = self._mode(epoch)
+        _lib.call("slime_ep_dispatch", cfg, ptr(x), x.stride(0), T, ptr(self.topk_idx), ptr(self.slot),
+                  ptr(self.group_offsets), self._bc1, e, max_blocks,
                   self.status.dev_ptr, stream_ptr())
 
-    def recv_dequant(self, out: torch.Tensor, epoch: int, expected_rows: int) -> None:
+    def recv_dequant(self, out: torch.Tensor, epoch: int | None, expected_rows: int) -> None:
         """Wait for every rank's rows, then expand the packed fp8 rows to bf16 ``out`` [recv_cap, hidden]."""
-        _lib.call("slime_ep_recv_dequant", self._cfg, ptr(self.group_offsets), ptr(out), out.stride(0), expected_rows,
-                  epoch, self.status.dev_ptr, stream_ptr())
+        cfg, e = self._mode(epoch)
+        _lib.call("slime_ep_recv_dequant", cfg, ptr(self.group_offsets), ptr(out), out.stride(0), expected_rows,
+                  e, self.status.dev_ptr, stream_ptr())
 
     def combine_push(self, y: torch.Tensor, expected_rows: int) -> None:
         _lib.call("slime_ep_combine_push", self._cfg, ptr(y), y.stride(0), ptr(self.group_offsets), expected_rows,
                   self.status.dev_ptr, stream_ptr())
 
-    def signal(self, which: int, epoch: int) -> None:
-        _lib.call("slime_ep_signal", self._cfg, which, epoch, stream_ptr())
+    def signal(self, which: int, epoch: int | None = None) -> None:
+        cfg, e = self._mode(epoch)
+        _lib.call("slime_ep_signal", cfg, which, e, stream_ptr())
 
-    def combine_reduce(self, out: torch.Tensor, T: int, epoch: int, do_signal: bool = True) -> None:
-        _lib.call("slime_ep_combine_reduce", self._cfg, T, ptr(self.topk_idx), ptr(self.topk_w), ptr(out), out.stride(0),
-                  epoch, int(do_signal), self.status.dev_ptr, stream_ptr())
+    def combine_reduce(self, out: torch.Tensor, T: int, epoch: int | None = None, do_signal: bool = True) -> None:
+        cfg, e = self._mode(epoch)
+        _lib.call("slime_ep_combine_reduce", cfg, T, ptr(self.topk_idx), ptr(self.topk_w), ptr(out), out.stride(0),
+                  e, int(do_signal), self.status.dev_ptr, stream_ptr())
 
     def barrier(self, epoch: int) -> None:
         _lib.call("slime_ep_barrier", self._cfg, epoch, self.status.dev_ptr, stream_ptr())
