@@ -118,17 +118,27 @@ struct TileWalker {
             const int tiles_g = g_mtiles * ntiles_n;
             if (t < cum + tiles_g) {
                 const int local = t - cum;
-                int       mt    = local % g_mtiles;
-                if (a.m_tile_rotate) mt = (mt + a.m_tile_rotate) % g_mtiles;
+                int       mt, nt;
                 if (a.ag_shard_order) {
-                    const int per   = a.ag_rows / kBM;
-                    const int shard = ((a.ag_rank - mt / per) % a.ag_world + a.ag_world) % a.ag_world;
-                    mt              = shard * per + mt % per;
+                    // shard-major order: every tile of the local shard first, then the shard of rank-1, rank-2, ...
+                    // (the order in which the shards finish arriving), n tiles before m tiles inside a shard
+                    const int per       = a.ag_rows / kBM;
+                    const int per_shard = per * ntiles_n;
+                    const int j         = local / per_shard;
+                    const int rem       = local - j * per_shard;
+                    const int shard     = ((a.ag_rank - j) % a.ag_world + a.ag_world) % a.ag_world;
+                    nt                  = rem / per;
+                    mt                  = shard * per + rem % per;
+                }
+                else {
+                    mt = local % g_mtiles;
+                    if (a.m_tile_rotate) mt = (mt + a.m_tile_rotate) % g_mtiles;
+                    nt = local / g_mtiles;
                 }
                 c.group   = g;
                 c.row0    = g_begin + mt * kBM;
                 c.row_end = g_end;
-                c.nt      = local / g_mtiles;
+                c.nt      = nt;
                 t += gridDim.x;
                 return true;
             }
@@ -153,7 +163,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 // All-gather push executed by `nthreads` threads (tid in [0, nthreads)) that share named barrier
 // `bar_id`. Units are (32-row slice of the local shard, destination rank); every finished unit adds 1
 // to the destination's counter of the 128-row chunk it belongs to, so a chunk is complete at
-// 4 * step. Destinations are visited starting with rank+1, the order in which consumers use them.
+// 4 * step.
 constexpr int kAgSliceRows = 32;
 __device__ __forceinline__ void ag_push_units(const Args& a, int tid, int nthreads, int bar_id, int cta, int n_cta)
 {
@@ -162,8 +172,10 @@ __device__ __forceinline__ void ag_push_units(const Args& a, int tid, int nthrea
     const int                slices   = a.ag_rows / kAgSliceRows;
     const int                units    = slices * a.ag_world;
     for (int u = cta; u < units; u += n_cta) {
-        const int    p   = (a.ag_rank + 1 + u % a.ag_world) % a.ag_world;
-        const int    sl  = u / a.ag_world;
+        // destination-major: the whole shard goes to this rank itself, then to rank+1, rank+2, ...; at any moment
+        // every rank receives from one source at full link rate, and shards complete in the order they are consumed
+        const int    p   = (a.ag_rank + u / slices) % a.ag_world;
+        const int    sl  = u % slices;
         const uint4* src = a.ag_src + sl * slice_v;
         uint4* dst = reinterpret_cast<uint4*>(a.ag_dst[p]) + (static_cast<unsigned long long>(a.ag_rank) * slices + sl) * slice_v;
         unsigned long long i = tid;
