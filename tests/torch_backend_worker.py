@@ -1,0 +1,42 @@
+"""Worker of test_torch_backend.py: two CPU ranks exchange tensors through the "dlslime" c10d backend."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import dlslime_b200.torch_backend  # noqa: F401,E402  (registers the backend)
+
+
+def main():
+    dist.init_process_group("dlslime")
+    rank = dist.get_rank()
+    peer = 1 - rank
+    for i in range(4):  # ordered pairs
+        t = torch.full((1000 + i,), float(10 * rank + i))
+        if rank == 0:
+            dist.send(t, dst=1)
+            got = torch.empty(1000 + i)
+            dist.recv(got, src=1)
+        else:
+            got = torch.empty(1000 + i)
+            dist.recv(got, src=0)
+            dist.send(t, dst=0)
+        assert torch.all(got == float(10 * peer + i)), (rank, i, got[:3])
+    a, b = torch.arange(64.0) + rank, torch.empty(64)
+    ops = [dist.P2POp(dist.isend, a, peer), dist.P2POp(dist.irecv, b, peer)]
+    for w in dist.batch_isend_irecv(ops):
+        w.wait()
+    assert torch.equal(b, torch.arange(64.0) + peer)
+    try:
+        dist.all_reduce(torch.ones(1))
+        raise SystemExit("all_reduce should not be supported")
+    except (NotImplementedError, RuntimeError) as e:
+        assert "not supported" in str(e)
+    print(f"BACKEND_OK {rank}", flush=True)
+    os._exit(0)  # skip the default teardown barrier, which this backend does not implement
+
+
+if __name__ == "__main__":
+    main()
