@@ -71,7 +71,6 @@ static void bind_future(py::module_& m, const char* name)
 PYBIND11_MODULE(_slime_c, m)
 {
     m.doc() = "Host runtime of the B200-native DLSlime-capability framework";
-    m.attr("_BUILD_RDMA")      = false;  // replaced by bind_extra_transports when verbs can be loaded
     m.attr("_BUILD_NVLINK")    = true;   // the NVLink endpoint lives in libslime_cuda (dlslime_b200.ops.nvlink)
     m.attr("_BUILD_TCP")       = true;
     m.attr("_BUILD_INTRA_OPS") = true;   // dlslime_b200.ops: all-gather, EP dispatch/combine, AG-GEMM

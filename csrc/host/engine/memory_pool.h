@@ -26,6 +26,7 @@ struct MemoryRegion {
     uint64_t    length = 0;
     uint64_t    rkey   = 0;  // transport key published to peers
     uint64_t    lkey   = 0;
+    uint64_t    opaque = 0;  // transport object behind the keys (for example the verbs memory region)
     bool        alive  = false;
     bool        system = false;
 

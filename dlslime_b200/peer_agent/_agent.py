@@ -173,6 +173,14 @@ class PeerAgent:
         for i in range(n_gpu):
             nics.append({"name": f"cuda:{i}", "health": "AVAILABLE", "numa_node": -1, "pci_bus_id": "",
                          "ports": [{"port": 1, "state": "ACTIVE", "link_type": "NVLink"}]})
+        # devices of a verbs provider that sysfs does not list (the software loopback fabric)
+        known = {n["name"] for n in nics}
+        if _slime_c.rdma_provider()[0] == "loopback":
+            for dev in _slime_c.rdma_devices():
+                if dev not in known:
+                    link = _slime_c.RDMAContext.acquire(dev, 1, "").link_type()
+                    nics.append({"name": dev, "health": "AVAILABLE", "numa_node": -1, "pci_bus_id": "",
+                                 "ports": [{"port": 1, "state": "ACTIVE", "link_type": link}]})
         return res
 
     @staticmethod
@@ -365,6 +373,12 @@ class PeerAgent:
                     ep.register_memory_region(r.name, r.ptr, r.offset, r.length)
         else:
             raise RuntimeError(f"no transport for link type {link!r} in this build")
+        if link != "TCP":
+            # the keys peers need exist only now: publish them for this resource
+            with self._regions_lock:
+                names = list(self._logical_regions)
+            for name in names:
+                self._materialize_region(name, conn.local_key, endpoint=ep)
         return ep
 
     def _ensure_endpoint(self, conn: DirectedConnection):
@@ -491,6 +505,7 @@ class PeerAgent:
         for c in list(self._connections.values()):
             if c.endpoint is not None and c.local_key.link_type != "TCP":
                 c.endpoint.register_memory_region(mr_name, int(ptr), int(offset), int(length))
+                self._materialize_region(mr_name, c.local_key, endpoint=c.endpoint)
         m = self._materialize_region(mr_name, self._default_local_resource_key())
         self._publish_memory_keys()
         return m.handler

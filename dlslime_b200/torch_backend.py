@@ -16,6 +16,7 @@ GPU-to-GPU traffic inside a node the NVLink ops of this package are the fast pat
 from __future__ import annotations
 
 import json
+import os
 from datetime import timedelta
 
 import torch
@@ -70,12 +71,23 @@ class SlimeProcessGroup(dist.ProcessGroup):
         for peer in range(size):
             if peer == rank:
                 continue
-            ep = _slime_c.TcpEndpoint(bind_host, 0, 1)
+            ep = self._make_endpoint(bind_host, peer)
             self._eps[peer] = ep
             store.set(f"SLIME_ENDPOINT_{rank}_{peer}", json.dumps(ep.endpoint_info()))
         for peer, ep in self._eps.items():
             info = json.loads(store.get(f"SLIME_ENDPOINT_{peer}_{rank}"))  # blocks until the peer published it
             ep.connect(info)
+
+    def _make_endpoint(self, bind_host: str, peer: int):
+        """RDMA when a verbs provider with a device exists (NIC picked round robin by rank, as the reference
+        backend does), else TCP. ``SLIME_BACKEND_TRANSPORT=tcp|rdma`` forces one."""
+        want = os.environ.get("SLIME_BACKEND_TRANSPORT", "")
+        devices = _slime_c.rdma_devices() if want != "tcp" else []
+        if want == "rdma" and not devices:
+            raise RuntimeError(f"SLIME_BACKEND_TRANSPORT=rdma but no RDMA provider: {_slime_c.rdma_provider()[1]}")
+        if devices and (want == "rdma" or _slime_c.rdma_provider()[0] == "ibverbs"):
+            return _slime_c.RDMAEndpoint(devices[self._rank % len(devices)], 1, "", 0)
+        return _slime_c.TcpEndpoint(bind_host, 0, 1)
 
     def getBackendName(self) -> str:
         return "dlslime"

@@ -1,0 +1,304 @@
+"""RDMA endpoint, context, channel logic and worker on the software loopback fabric (no NIC needed).
+
+Covers what the reference's RDMA tests need hardware for (tests/python/test_rdma_*.py in the reference):
+one-sided read / write with striping over queue pairs, write-with-immediate ordering over lanes,
+immediate events that arrive before / after imm_recv, rendezvous send / recv (ordering, overflow), credit
+back-pressure with batches larger than the send queue, failure statuses (bad remote key, injected
+completion error), cancel_all and shutdown.
+"""
+import ctypes
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def run_child(body: str, env_extra=None, timeout=120):
+    env = dict(os.environ, SLIME_RDMA_PROVIDER="loopback", PYTHONPATH=REPO)
+    env.update(env_extra or {})
+    prelude = textwrap.dedent("""
+        import ctypes, os, sys, threading, time
+        from dlslime_b200 import _slime_c as C
+
+        def buf(n, fill=None):
+            b = (ctypes.c_ubyte * n)()
+            if fill is not None:
+                ctypes.memset(b, fill, n)
+            return b
+
+        def pair(num_qp=2, dev_a="rdma_lo0", dev_b="rdma_lo0"):
+            a = C.RDMAEndpoint(dev_a, 1, "", num_qp)
+            b = C.RDMAEndpoint(dev_b, 1, "", num_qp)
+            return a, b
+
+        def link(a, b):
+            ia, ib = a.endpoint_info(), b.endpoint_info()
+            assert a.connect(ib) == 0 and b.connect(ia) == 0
+    """)
+    r = subprocess.run([sys.executable, "-c", prelude + textwrap.dedent(body)], env=env, capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, f"child failed\nstdout:\n{r.stdout}\nstderr:\n{r.stderr}"
+    return r.stdout
+
+
+def test_provider_selection_and_context():
+    out = run_child("""
+        assert C._BUILD_RDMA
+        name, why = C.rdma_provider()
+        assert name == "loopback", (name, why)
+        assert C.rdma_devices() == ["rdma_lo0", "rdma_lo1", "rdma_lo2"]
+        ctx = C.RDMAContext.acquire("rdma_lo0", 1, "RoCE")
+        assert ctx.link_type() == "RoCE" and ctx.gid_index() == 1 and ctx.mtu() == 5
+        ib = C.RDMAContext.acquire("rdma_lo1", 1, "IB")
+        assert ib.link_type() == "IB" and ib.lid() == 7
+        try:
+            C.RDMAContext.acquire("rdma_lo1", 1, "RoCE")   # cached under the same key: asks again with another link type
+        except RuntimeError:
+            pass
+        # an unknown device falls back to the first one
+        fb = C.RDMAContext.acquire("mlx5_nope", 1, "")
+        assert fb.device_name() == "rdma_lo0"
+        # link-type mismatch on a fresh key is refused
+        try:
+            C.RDMAContext.acquire("rdma_lo0", 2, "IB")
+            raise SystemExit("port 2 is not active; must fail")
+        except RuntimeError as e:
+            assert "not active" in str(e)
+        print("ok")
+    """)
+    assert "ok" in out
+
+
+def test_without_provider_reports_reason():
+    out = run_child("""
+        name, why = C.rdma_provider()
+        print(name, "|", why)
+        try:
+            C.RDMAEndpoint("", 1, "", 1)
+            print("created")
+        except RuntimeError as e:
+            print("refused:", e)
+    """, env_extra={"SLIME_RDMA_PROVIDER": "ibverbs"})
+    # this host has no libibverbs / no NIC: the endpoint refuses with the reason; with a NIC it would be created
+    assert "refused: no RDMA provider" in out or "created" in out
+
+
+def test_one_sided_read_write_striped():
+    out = run_child("""
+        a, b = pair(num_qp=4)
+        n = 1 << 20
+        src = buf(n); dst = buf(n); back = buf(n)
+        for i in range(n):
+            pass
+        ctypes.memmove(src, bytes((i * 7 + 3) & 0xff for i in range(n)), n)
+        a.register_memory_region("src", ctypes.addressof(src), 0, n)
+        a.register_memory_region("back", ctypes.addressof(back), 0, n)
+        b.register_memory_region("dst", ctypes.addressof(dst), 0, n)
+        link(a, b)
+        ha, hb = a.get_mr_handle("src"), a.get_remote_mr_handle("dst")
+        assert ha >= 0 and hb >= 0
+        # (local, remote, remote_off, local_off, len): one big striped piece, small pieces round-robin, odd offsets
+        f = a.write([(ha, hb, 0, 0, 512 << 10), (ha, hb, (512 << 10) + 5, (512 << 10) + 5, 1000), (ha, hb, 700000, 700000, 3)])
+        assert f.wait(5000) == 0
+        assert bytes(dst[:512 << 10]) == bytes(src[:512 << 10])
+        assert bytes(dst[(512 << 10) + 5:(512 << 10) + 1005]) == bytes(src[(512 << 10) + 5:(512 << 10) + 1005])
+        assert bytes(dst[700000:700003]) == bytes(src[700000:700003]) and dst[700003] == 0
+        # 4 stripes + 2 unstriped pieces
+        assert a.posted_wrs() == 6, a.posted_wrs()
+        hback = a.get_mr_handle("back")
+        f = a.read([(hback, hb, 0, 0, 512 << 10)])
+        assert f.wait(5000) == 0 and bytes(back[:512 << 10]) == bytes(src[:512 << 10])
+        # an empty batch completes at once
+        assert a.write([]).wait(1000) == 0
+        a.shutdown(); b.shutdown()
+        print("ok")
+    """)
+    assert "ok" in out
+
+
+def test_write_with_imm_all_lanes_and_event_queue():
+    out = run_child("""
+        a, b = pair(num_qp=3)
+        n = 300000
+        src = buf(n, 0x5a); dst = buf(n)
+        a.register_memory_region("src", ctypes.addressof(src), 0, n)
+        b.register_memory_region("dst", ctypes.addressof(dst), 0, n)
+        link(a, b)
+        ha, hb = a.get_mr_handle("src"), a.get_remote_mr_handle("dst")
+        # events that arrive before anyone asks are queued in order
+        for k in range(5):
+            assert a.write_with_imm([(ha, hb, k * 10, k * 10, 10)], 100 + k).wait(5000) == 0
+        got = []
+        for k in range(5):
+            f = b.imm_recv()
+            assert f.wait(5000) == 0
+            got.append(f.imm_data())
+        assert got == [100, 101, 102, 103, 104], got
+        # a waiter that is posted first is completed by the next event; a striped payload has landed by then
+        f = b.imm_recv()
+        assert f.wait(50) == 402          # TIME_OUT, still pending
+        assert a.write_with_imm([(ha, hb, 0, 0, n)], 7).wait(5000) == 0
+        assert f.wait(5000) == 0 and f.imm_data() == 7
+        assert bytes(dst) == bytes(src)
+        # every lane carried exactly one immediate per operation: 6 ops x 3 lanes signaled at least that many
+        assert a.signaled_wrs() >= 18
+        a.shutdown(); b.shutdown()
+        print("ok")
+    """)
+    assert "ok" in out
+
+
+def test_send_recv_rendezvous_order_and_overflow():
+    out = run_child("""
+        a, b = pair(num_qp=2)
+        link(a, b)
+        msgs = [bytes([k]) * (1000 + k * 70000) for k in range(4)]
+        sbufs = [ctypes.create_string_buffer(m, len(m)) for m in msgs]
+        rbufs = [ctypes.create_string_buffer(len(m)) for m in msgs]
+        # receives first on b, sends on a; then the other way round for the last two
+        rf = [b.recv((ctypes.addressof(rbufs[k]), 0, len(msgs[k]))) for k in range(2)]
+        sf = [a.send((ctypes.addressof(sbufs[k]), 0, len(msgs[k]))) for k in range(4)]
+        rf += [b.recv((ctypes.addressof(rbufs[k]), 0, len(msgs[k]))) for k in range(2, 4)]
+        for f in sf + rf:
+            assert f.wait(5000) == 0
+        for k in range(4):
+            assert rbufs[k].raw == msgs[k], k
+        # a send larger than the posted receive buffer: both sides learn it (400), nothing past the buffer is written
+        small = ctypes.create_string_buffer(64 + 8)
+        big = ctypes.create_string_buffer(b"x" * 128, 128)
+        r = b.recv((ctypes.addressof(small), 0, 64))
+        s = a.send((ctypes.addressof(big), 0, 128))
+        assert s.wait(5000) == 400 and r.wait(5000) == 400
+        assert small.raw[:64] == b"x" * 64 and small.raw[64:] == bytes(8)
+        a.shutdown(); b.shutdown()
+        print("ok")
+    """)
+    assert "ok" in out
+
+
+def test_credit_backpressure_and_signal_interval():
+    out = run_child("""
+        a, b = pair(num_qp=1)
+        n = 64 * 1000
+        src = buf(n, 1); dst = buf(n)
+        a.register_memory_region("src", ctypes.addressof(src), 0, n)
+        b.register_memory_region("dst", ctypes.addressof(dst), 0, n)
+        link(a, b)
+        ha, hb = a.get_mr_handle("src"), a.get_remote_mr_handle("dst")
+        # 1000 work requests through a send queue of 64 credits
+        f = a.write([(ha, hb, i * 64, i * 64, 64) for i in range(1000)])
+        assert f.wait(10000) == 0
+        assert bytes(dst) == bytes(src)
+        assert a.posted_wrs() == 1000
+        assert a.signaled_wrs() == 32, a.signaled_wrs()      # every 32nd (31) + the last one
+        assert a.credit_stalls() > 0
+        a.shutdown(); b.shutdown()
+        print("ok")
+    """, env_extra={"SLIME_MAX_SEND_WR": "64"})
+    assert "ok" in out
+
+
+def test_failures_cancel_and_shutdown():
+    out = run_child("""
+        a, b = pair(num_qp=2)
+        n = 4096
+        src = buf(n, 9); dst = buf(n)
+        a.register_memory_region("src", ctypes.addressof(src), 0, n)
+        b.register_memory_region("dst", ctypes.addressof(dst), 0, n)
+        link(a, b)
+        ha, hb = a.get_mr_handle("src"), a.get_remote_mr_handle("dst")
+        # out-of-range assignment is refused before anything is posted
+        f = a.write([(ha, hb, n - 10, 0, 100)])
+        try:
+            f.wait(1000); raise SystemExit("must throw")
+        except RuntimeError as e:
+            assert "403" in str(e)
+        # the peer drops its region: the stale remote key fails the transfer with FAILED, the future throws
+        b.unregister_memory_region("dst")
+        f = a.write([(ha, hb, 0, 0, 100)])
+        try:
+            f.wait(5000); raise SystemExit("must throw")
+        except RuntimeError as e:
+            assert "403" in str(e)
+        # pending immediate waiters are failed by cancel_all
+        w = b.imm_recv()
+        b.cancel_all()
+        assert w.wait(1000) == 403
+        a.shutdown(); a.shutdown(); b.shutdown()
+        # after shutdown every call fails fast
+        try:
+            a.write([(ha, hb, 0, 0, 1)]).wait(1000); raise SystemExit("must throw")
+        except RuntimeError:
+            pass
+        snap = C.obs_snapshot()
+        print("ok")
+    """, env_extra={"DLSLIME_OBS": "1"})
+    assert "ok" in out
+
+
+def test_injected_completion_error_and_recovery_on_new_endpoint():
+    out = run_child("""
+        a, b = pair(num_qp=1)
+        n = 1 << 16
+        src = buf(n, 3); dst = buf(n)
+        a.register_memory_region("src", ctypes.addressof(src), 0, n)
+        b.register_memory_region("dst", ctypes.addressof(dst), 0, n)
+        link(a, b)
+        ha, hb = a.get_mr_handle("src"), a.get_remote_mr_handle("dst")
+        C.rdma_loopback_inject_error(0, 12, 1)     # next WRITE completes with retry-exceeded
+        f = a.write([(ha, hb, i * 64, i * 64, 64) for i in range(100)])
+        try:
+            f.wait(5000); raise SystemExit("must throw")
+        except RuntimeError as e:
+            assert "403" in str(e)
+        a.shutdown(); b.shutdown()
+        # a fresh pair works again
+        a2, b2 = pair(num_qp=1)
+        a2.register_memory_region("src", ctypes.addressof(src), 0, n)
+        b2.register_memory_region("dst", ctypes.addressof(dst), 0, n)
+        link(a2, b2)
+        assert a2.write([(a2.get_mr_handle("src"), a2.get_remote_mr_handle("dst"), 0, 0, n)]).wait(5000) == 0
+        assert bytes(dst) == bytes(src)
+        a2.shutdown(); b2.shutdown()
+        print("ok")
+    """)
+    assert "ok" in out
+
+
+def test_peer_agent_over_rdma_links():
+    """Two agents in one process, each on a RoCE device of its own: handshake through the control plane, named
+    I/O with keys published per resource, write-with-immediate, a region registered after the link came up."""
+    out = run_child("""
+        from dlslime_b200.nanoctrl import start_local_nanoctrl
+        from dlslime_b200.peer_agent import PeerAgent
+        ctrl = start_local_nanoctrl()
+        a = PeerAgent(ctrl.url, alias="A", scope="r", device="rdma_lo0", link_type="RoCE")
+        b = PeerAgent(ctrl.url, alias="B", scope="r", device="rdma_lo2", link_type="RoCE")
+        try:
+            n = 1 << 18
+            ba = ctypes.create_string_buffer(bytes((i * 3 + 1) & 0xff for i in range(n)), n)
+            bb = ctypes.create_string_buffer(n)
+            a.register_memory_region("kv", ctypes.addressof(ba), 0, n)
+            b.register_memory_region("kv", ctypes.addressof(bb), 0, n)
+            conn = a.connect_to("B", local_device="rdma_lo0", peer_device="rdma_lo2").wait(10)
+            assert conn.is_connected() and (conn.local_nic, conn.remote_nic) == ("rdma_lo0", "rdma_lo2"), conn.conn_id
+            assert a.write("B", [("kv", 0, 4096, 200000)]).wait(10) == 0
+            assert bb.raw[4096:204096] == ba.raw[:200000]
+            assert b.query_connection("A").wait(5).is_connected()
+            assert b.read("A", ("kv", "kv", 0, 7, 100)).wait(10) == 0 and bb.raw[:100] == ba.raw[7:107]
+            assert a.write_with_imm("B", [("kv", 0, 0, 16)], imm_data=77).wait(10) == 0
+            f = b.imm_recv("A")
+            assert f.wait(10) == 0 and f.imm_data() == 77
+            late = ctypes.create_string_buffer(b"z" * 512, 512)
+            b.register_memory_region("late", ctypes.addressof(late), 0, 512)
+            got = ctypes.create_string_buffer(512)
+            a.register_memory_region("got", ctypes.addressof(got), 0, 512)
+            assert a.read("B", ("got", "late", 0, 0, 512)).wait(10) == 0 and got.raw == b"z" * 512
+        finally:
+            a.shutdown(); b.shutdown(); ctrl.stop()
+        print("ok")
+    """)
+    assert "ok" in out
