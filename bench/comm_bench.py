@@ -205,16 +205,35 @@ def case_ag_gemm(rank, world):
     def barrier_only():
         dist.barrier()
 
+    # the two halves on their own, as separate kernels: the push of this rank's shard to every rank, and the
+    # gated GEMM over the gathered matrix once everything has arrived (its counters are already satisfied)
+    def push_only():
+        ag.step += 1
+        ag.push(x, ag.step, push_blocks=148)
+        dist.barrier()
+
+    def gemm_only():
+        ag.gemm(w, out, ag.step)
+
+    def local_gemm():
+        gemm.gemm_bf16(full, w, out=out)
+
+    from dlslime_b200.ops import gemm
+
     b = timed(barrier_only, 50, sync=dist.barrier)
     ms = max_ms(timed(fused, 50, sync=dist.barrier) - b, world)
     base = max_ms(timed(baseline, 50, sync=dist.barrier) - b, world)
+    push_ms = max_ms(timed(push_only, 20, sync=dist.barrier) - b, world)
+    gemm_ms = max_ms(timed(gemm_only, 20, sync=dist.barrier), world)
+    plain_ms = max_ms(timed(local_gemm, 20, sync=dist.barrier), world)
     ag.status.check()
     flops = 2.0 * world * rows * k * n
     gathered = (world - 1) * rows * k * 2
     roof_ms = max(flops / (tf * 1e9), gathered / (NVLINK_GBS * 1e6))
     emit(rank, case="ag_gemm_bf16", world=world, M=world * rows, N=n, K=k, us=round(ms * 1e3, 1), tflops=round(flops / ms / 1e9, 1),
          nccl_cublas_us=round(base * 1e3, 1), speedup=round(base / ms, 2), roofline_us=round(roof_ms * 1e3, 1),
-         frac_of_roofline=round(roof_ms / ms, 3), peak=tag)
+         frac_of_roofline=round(roof_ms / ms, 3), peak=tag, push_kernel_alone_us=round(push_ms * 1e3, 1),
+         gated_gemm_alone_us=round(gemm_ms * 1e3, 1), plain_gemm_same_shape_us=round(plain_ms * 1e3, 1))
 
 
 # ------------------------------------------------------------------------------------------ kv

@@ -60,8 +60,11 @@ def cmd_gemm(a):
     flops = 2.0 * a.m * a.n * a.k
     best, med = timeit(lambda: gemm.gemm_bf16(x, w, out=out), a.iters)
     b2, m2 = timeit(lambda: torch.matmul(x, w.t(), out=out), a.iters)
+    bp, mp = timeit(lambda: gemm.gemm_bf16_pair(x, w, out=out), a.iters)
     print(json.dumps({"kernel": "gemm_bf16_tc", "m": a.m, "n": a.n, "k": a.k, "ms_best": round(best, 4), "ms_median": round(med, 4),
                       "tflops_best": round(flops / best / 1e9, 1), "frac_of_peak": round(flops / best / 1e9 / tf, 3), "peak": tag,
+                      "pair_ms_best": round(bp, 4), "pair_ms_median": round(mp, 4), "pair_tflops_best": round(flops / bp / 1e9, 1),
+                      "pair_frac_of_peak": round(flops / bp / 1e9 / tf, 3),
                       "cublas_ms_best": round(b2, 4), "cublas_tflops_best": round(flops / b2 / 1e9, 1)}))
 
 

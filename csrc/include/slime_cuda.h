@@ -54,6 +54,8 @@ int slime_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
                     long long ldc, void* status, void* stream);
 // Same, but a tile of A rows is read only after its arrival flag reached the target
 // (a_ready[row / a_ready_rows] >= a_ready_target); m tiles start at m_tile_rotate.
+int slime_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                         long long ldc, void* status, void* stream);
 int slime_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                           long long ldc, const void* a_ready, int a_ready_rows, unsigned long long a_ready_target,
                           int m_tile_rotate, void* status, void* stream);

@@ -59,20 +59,29 @@ struct Args {
     int                       ag_rows;         // rows per shard (multiple of 128)
     int                       ag_rank, ag_world;
     int                       ag_shard_order;  // visit m tiles shard by shard: own, rank-1, rank-2, ...
+    int                       ag_local_direct; // tiles of the own shard read ag_src through the third tensor map and wait for nothing
     unsigned long long        ag_dst[8];       // address of the gathered A on every rank
     unsigned long long        ag_flags[8];     // address of the arrival counters (u64 per 128 rows) on every rank
     KernelStatus*             status;
     unsigned long long        wait_ns;
 };
 
-template<int BN, int STAGES>
+constexpr int kAgChunkBytes = 4096;  // staging buffer of the in-kernel all-gather push
+constexpr int kAgMaxBufs    = 6;
+constexpr int kSmemLimit    = 227 * 1024;
+
+template<int BN, int STAGES, bool AG = false>
 struct Smem {
     static constexpr int kABytes     = kBM * kBK * 2;
     static constexpr int kBBytes     = BN * kBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kBarBytes   = (2 * STAGES + 4) * 8 + 16;
+    static constexpr int kBarBytes   = (2 * STAGES + 4 + kAgMaxBufs) * 8 + 16;
     static constexpr int kEpiBytes   = 128 * kEpiRowPitch;  // one padded 128-byte slot per tile row
-    static constexpr int kTotal      = STAGES * kStageBytes + kEpiBytes + kBarBytes + 1024;  // + alignment slack
+    static constexpr int kBase       = STAGES * kStageBytes + kEpiBytes + kBarBytes + 1024;  // + alignment slack
+    // the push stages its chunks in whatever shared memory the tile ring leaves free
+    static constexpr int kAgBufs = !AG ? 0 : ((kSmemLimit - kBase - 128) / kAgChunkBytes > kAgMaxBufs ? kAgMaxBufs : (kSmemLimit - kBase - 128) / kAgChunkBytes);
+    static constexpr int kTotal  = kBase + (AG ? kAgBufs * kAgChunkBytes + 128 : 0);
+    static_assert(!AG || kAgBufs >= 2, "no room for the push buffers");
 };
 
 struct TileCoord {
@@ -161,10 +170,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 }
 
 // All-gather push executed by `nthreads` threads (tid in [0, nthreads)) that share named barrier
-// `bar_id`. Units are (32-row slice of the local shard, destination rank); every finished unit adds 1
-// to the destination's counter of the 128-row chunk it belongs to, so a chunk is complete at
-// 4 * step.
-constexpr int kAgSliceRows = 32;
+// `bar_id`. A unit is (destination, 8-row slice of the local shard); units are numbered destination by
+// destination (rank+1, rank+2, ..., and this rank itself last), so the CTAs of the grid, which take
+// units round robin, all work on the same destination at the same time: every rank then receives from
+// one source at a time at full link rate, and the shards complete in the order in which the tiles
+// consume them. Every finished unit adds 1 to the destination's counter of the 128-row chunk it
+// belongs to, so a chunk is complete at 16 * step.
+constexpr int kAgSliceRows = 8;
 __device__ __forceinline__ void ag_push_units(const Args& a, int tid, int nthreads, int bar_id, int cta, int n_cta)
 {
     const unsigned long long row_vecs = static_cast<unsigned long long>(a.K) * 2 / 16;
@@ -172,9 +184,7 @@ __device__ __forceinline__ void ag_push_units(const Args& a, int tid, int nthrea
     const int                slices   = a.ag_rows / kAgSliceRows;
     const int                units    = slices * a.ag_world;
     for (int u = cta; u < units; u += n_cta) {
-        // destination-major: the whole shard goes to this rank itself, then to rank+1, rank+2, ...; at any moment
-        // every rank receives from one source at full link rate, and shards complete in the order they are consumed
-        const int    p   = (a.ag_rank + u / slices) % a.ag_world;
+        const int    p   = (a.ag_rank + 1 + u / slices) % a.ag_world;
         const int    sl  = u % slices;
         const uint4* src = a.ag_src + sl * slice_v;
         uint4* dst = reinterpret_cast<uint4*>(a.ag_dst[p]) + (static_cast<unsigned long long>(a.ag_rank) * slices + sl) * slice_v;
@@ -197,7 +207,82 @@ __device__ __forceinline__ void ag_push_units(const Args& a, int tid, int nthrea
     }
 }
 
-constexpr int kAgThreads = 128;
+// The same push through the bulk-copy engine, executed by ONE thread: chunks of the local shard are
+// loaded into a ring of shared-memory buffers (completion on an mbarrier each) and handed on to the
+// destination with shared -> global bulk copies, which also reach peer memory. Loads run ahead of
+// stores by the ring depth; a buffer is reloaded once the copy engine has read it. A unit's counter is
+// bumped when its copies are complete, which is checked two chunks into the next unit so that the
+// pipeline never drains. Returns false when a wait ran out.
+__device__ __forceinline__ bool ag_push_bulk(const Args& a, uint8_t* bufs, uint64_t* bars, int nb, int cta, int n_cta,
+                                             KernelStatus* st, unsigned long long lim)
+{
+    const unsigned long long slice_bytes = static_cast<unsigned long long>(a.K) * 2 * kAgSliceRows;
+    const int                slices      = a.ag_rows / kAgSliceRows;
+    const int                units       = slices * a.ag_world;
+    const int                chunks      = static_cast<int>((slice_bytes + kAgChunkBytes - 1) / kAgChunkBytes);
+    const uint8_t*           src_base    = reinterpret_cast<const uint8_t*>(a.ag_src);
+    auto chunk_bytes = [&](int c) -> uint32_t {
+        const unsigned long long left = slice_bytes - static_cast<unsigned long long>(c) * kAgChunkBytes;
+        return left < kAgChunkBytes ? static_cast<uint32_t>(left) : kAgChunkBytes;
+    };
+    auto signal_unit = [&](int u) {
+        const int p  = (a.ag_rank + 1 + u / slices) % a.ag_world;
+        const int sl = u % slices;
+        fence_proxy_async();
+        fence_acq_rel_sys();
+        unsigned long long* f = reinterpret_cast<unsigned long long*>(a.ag_flags[p]) + a.ag_rank * (a.ag_rows / kBM)
+                                + sl / (kBM / kAgSliceRows);
+        red_add_release_sys(f, 1ull);
+    };
+    int lu = cta, lc = 0, n_ld = 0;  // load cursor
+    auto issue_load = [&]() {
+        const int      b     = n_ld % nb;
+        const uint32_t bytes = chunk_bytes(lc);
+        mbar_arrive_expect_tx(&bars[b], bytes);
+        bulk_load_g2s(bufs + b * kAgChunkBytes, src_base + static_cast<unsigned long long>(lu % slices) * slice_bytes
+                                                     + static_cast<unsigned long long>(lc) * kAgChunkBytes, bytes, &bars[b]);
+        ++n_ld;
+        if (++lc == chunks) {
+            lc = 0;
+            lu += n_cta;
+        }
+    };
+    while (n_ld < nb && lu < units) issue_load();
+    int n_st = 0, pending = -1;
+    for (int u = cta; u < units; u += n_cta) {
+        const int p  = (a.ag_rank + 1 + u / slices) % a.ag_world;
+        const int sl = u % slices;
+        uint8_t*  dst = reinterpret_cast<uint8_t*>(a.ag_dst[p]) + (static_cast<unsigned long long>(a.ag_rank) * slices + sl) * slice_bytes;
+        for (int c = 0; c < chunks; ++c) {
+            const int b = n_st % nb;
+            if (!mbar_wait(&bars[b], (n_st / nb) & 1, st, 12, b, lim)) return false;
+            bulk_store_s2g(dst + static_cast<unsigned long long>(c) * kAgChunkBytes, bufs + b * kAgChunkBytes, chunk_bytes(c));
+            tma_store_commit();
+            ++n_st;
+            if (n_st >= 2 && lu < units) {
+                tma_store_wait_read<1>();  // the buffer of the previous chunk has been read: load the next chunk into it
+                issue_load();
+            }
+            if (pending >= 0 && c == 1) {
+                tma_store_wait<2>();  // everything older than the last two copies has landed: that covers the previous unit
+                signal_unit(pending);
+                pending = -1;
+            }
+        }
+        if (chunks < 3) {
+            tma_store_wait<0>();
+            signal_unit(u);
+        }
+        else {
+            pending = u;
+        }
+    }
+    tma_store_wait<0>();
+    if (pending >= 0) signal_unit(pending);
+    return true;
+}
+
+constexpr int kAgThreads = 32;
 
 __global__ void __launch_bounds__(256) ag_push_only_kernel(const Args args)
 {
@@ -206,9 +291,10 @@ __global__ void __launch_bounds__(256) ag_push_only_kernel(const Args args)
 
 template<int BN, int STAGES, int EPI, bool AG = false>
 __global__ void __launch_bounds__(kThreads + (AG ? kAgThreads : 0), 1)
-gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args args)
+gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmAL, const Args args)
 {
-    using S = Smem<BN, STAGES>;
+    using S = Smem<BN, STAGES, AG>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -217,7 +303,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint64_t* empty_bar  = full_bar + STAGES;
     uint64_t* tfull_bar  = empty_bar + STAGES;  // [2] accumulator ready
     uint64_t* tempty_bar = tfull_bar + 2;       // [2] accumulator drained
-    uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+    uint64_t* ag_bar     = tempty_bar + 2;      // [kAgMaxBufs] push chunk loaded
+    uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(ag_bar + kAgMaxBufs);
+    uint8_t*  ag_bufs    = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(epi_smem + S::kEpiBytes + S::kBarBytes) + 127) & ~uintptr_t(127));
     volatile uint32_t* fail_slot = tmem_slot + 1;  // set by any role whose wait ran out
 
     const int          warp    = threadIdx.x >> 5;
@@ -225,7 +313,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int          kblocks = (args.K + kBK - 1) / kBK;
     KernelStatus*      st      = args.status;
     const unsigned long long lim = args.wait_ns ? args.wait_ns : kDefaultWaitNs;
-    constexpr int      kTmemCols = 2 * BN;  // double-buffered accumulator (power of two >= 32)
+    constexpr int      kAccStride = BN <= 128 ? 128 : 256;  // TMEM columns between the two accumulators
+    constexpr int      kTmemCols  = 2 * kAccStride;         // double-buffered accumulator (a power of two >= 32)
+    static_assert(BN % 32 == 0 && BN >= 64 && BN <= 256, "tile width");
     constexpr int      kBNOut    = (EPI == kEpiSwiGLU) ? BN / 2 : BN;
 
     if (threadIdx.x == 0) {
@@ -238,9 +328,12 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             mbar_init(&tfull_bar[s], 1);
             mbar_init(&tempty_bar[s], 128);
         }
+        if (AG)
+            for (int s = 0; s < kAgMaxBufs; ++s) mbar_init(&ag_bar[s], 1);
         fence_mbar_init();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
+        if (AG) tma_prefetch_desc(&tmAL);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
@@ -260,7 +353,16 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t   phase = 0;
             bool       ok    = true;
             while (ok && walk.next(tc)) {
-                if (args.a_ready) {
+                const CUtensorMap* mapA = &tmA;
+                int                arow = tc.row0;
+                bool               gate = args.a_ready != nullptr;
+                if (AG && args.ag_local_direct && tc.row0 / args.ag_rows == args.ag_rank) {
+                    // the own shard is read where it lies: nothing to wait for
+                    mapA = &tmAL;
+                    arow = tc.row0 - args.ag_rank * args.ag_rows;
+                    gate = false;
+                }
+                if (gate) {
                     // rows [row0, row0+128) must have arrived in local memory
                     const int f0 = tc.row0 / args.a_ready_rows;
                     int       last_row = tc.row0 + kBM - 1;
@@ -288,7 +390,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     uint8_t* sa = smem + stage * S::kStageBytes;
                     uint8_t* sb = sa + S::kABytes;
                     mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
-                    tma_load_2d(sa, &tmA, &full_bar[stage], kb * kBK, tc.row0);
+                    tma_load_2d(sa, mapA, &full_bar[stage], kb * kBK, arow);
                     tma_load_2d(sb, &tmB, &full_bar[stage], kb * kBK, yb0);
                     tma_load_2d(sb + S::kBBytes / 2, &tmB, &full_bar[stage], kb * kBK, yb1);
                     if (++stage == STAGES) {
@@ -317,7 +419,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t tmem_d = tmem_base + acc * BN;
+                const uint32_t tmem_d = tmem_base + acc * kAccStride;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, st, 3, stage, lim)) {
                         ok = false;
@@ -351,7 +453,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     else if (AG && warp >= 6) {
         // ------------------------------ all-gather push ---------------------------
-        if (args.ag_src != nullptr) ag_push_units(args, threadIdx.x - kThreads, kAgThreads, 1, blockIdx.x, gridDim.x);
+        if (args.ag_src != nullptr && lane == 0) {
+            if (!ag_push_bulk(args, ag_bufs, ag_bar, S::kAgBufs, blockIdx.x, gridDim.x, st, lim)) *fail_slot = 1;
+        }
     }
     else {
         // ------------------------------ epilogue ----------------------------------
@@ -368,7 +472,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tc_fence_after_sync();
             const int      row   = tc.row0 + quad * 32 + lane;
             const bool     valid = row < tc.row_end;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kAccStride;
             const int      col0  = tc.nt * kBNOut;
 
             // Destination of this thread's row (one thread owns one row of the tile).
@@ -428,6 +532,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 fence_proxy_async_smem();
                 int cols = args.N - (col0 + c);
                 if (cols > 64) cols = 64;
+                if (cols > kBNOut - c) cols = kBNOut - c;  // tile widths that are not a multiple of 64
                 if (do_store && cols > 0)
                     bulk_store_s2g(reinterpret_cast<void*>(drow + static_cast<unsigned long long>(c) * 2), my_slot, cols * 2);
                 tma_store_commit();

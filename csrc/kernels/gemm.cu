@@ -2,7 +2,7 @@
 // synthetic prefill stand-in), a grouped GEMM over device-side row groups (the
 // expert FFN), its SwiGLU-fused variant, and a variant whose epilogue scatters
 // weighted rows to arbitrary (possibly peer) addresses.
-#include "common/gemm_tc.cuh"
+#include "common/gemm_tc2.cuh"
 #include "common/host_utils.h"
 #include "slime_cuda.h"
 
@@ -14,46 +14,133 @@ namespace {
 constexpr int kBN     = 256;
 constexpr int kStages = 4;
 
-template<int EPI>
-int launch(const void* A, const void* B, const Args& args, long long lda, long long ldb, int grid_cap,
-           cudaStream_t stream)
+// Tile width for one-group GEMMs: the widest tile wins unless a narrower one saves whole waves of the
+// persistent grid (cost = waves x (width + a fixed per-tile overhead expressed in columns)).
+int pick_bn(int M, int N)
 {
-    using S = Smem<kBN, kStages>;
-    CUtensorMap tmA, tmB;
+    const int  sms    = sm_count();
+    const long mtiles = (M + kBM - 1) / kBM;
+    int        best = 256;
+    long       best_cost = -1;
+    for (int bn : {256, 224, 192}) {
+        const long tiles = mtiles * ((N + bn - 1) / bn);
+        const long cost  = ((tiles + sms - 1) / sms) * (bn + 12);
+        if (best_cost < 0 || cost < best_cost) {
+            best      = bn;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
+template<int BN, int EPI, bool AG>
+int launch_bn(const void* A, const void* B, const void* A_local, int rows_local, const Args& args, long long lda, long long ldb,
+              int threads, cudaStream_t stream)
+{
+    using S = Smem<BN, kStages, AG>;
+    CUtensorMap tmA, tmB, tmAL;
     const unsigned long long rowsB_total = static_cast<unsigned long long>(args.rowsB) * args.num_groups;
     if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.M_total, args.K, lda, kBM, kBK)) return -1;
-    if (make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rowsB_total, args.K, ldb, kBN / 2, kBK)) return -1;
-    auto kern = gemm_bf16_tc_kernel<kBN, kStages, EPI>;
+    if (make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rowsB_total, args.K, ldb, BN / 2, kBK)) return -1;
+    if (A_local) {
+        if (make_tmap_2d(&tmAL, A_local, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_local, args.K, args.K, kBM, kBK)) return -1;
+    }
+    else {
+        tmAL = tmA;
+    }
+    auto kern = gemm_bf16_tc_kernel<BN, kStages, EPI, AG>;
     static bool configured = false;
     if (!configured) {
         SLIME_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
         configured = true;
     }
-    int grid = sm_count();
-    if (grid_cap > 0 && grid_cap < grid) grid = grid_cap;
-    kern<<<grid, kThreads, S::kTotal, stream>>>(tmA, tmB, args);
+    const long tiles = static_cast<long>((args.M_total + kBM - 1) / kBM) * ((args.N + BN - 1) / BN);
+    int        grid  = sm_count();
+    // a fused all-gather kernel keeps the full grid (its extra warps push whatever the tile count is);
+    // grouped launches do not know their tile count on the host
+    if (!AG && args.num_groups == 1 && tiles < grid) grid = static_cast<int>(tiles);
+    kern<<<grid, threads, S::kTotal, stream>>>(tmA, tmB, tmAL, args);
     SLIME_CUDA_OK(cudaGetLastError());
     return 0;
 }
 
-template<bool FUSED>
-int launch_ag(const void* A, const void* B, const Args& args, long long lda, long long ldb, int grid_cap, cudaStream_t stream)
+template<int EPI>
+int launch(const void* A, const void* B, const Args& args, long long lda, long long ldb, cudaStream_t stream)
 {
-    using S = Smem<kBN, kStages>;
-    CUtensorMap tmA, tmB;
+    if (EPI == kEpiStore && args.num_groups == 1) {
+        switch (pick_bn(args.M_total, args.N)) {
+            case 224: return launch_bn<224, kEpiStore, false>(A, B, nullptr, 0, args, lda, ldb, kThreads, stream);
+            case 192: return launch_bn<192, kEpiStore, false>(A, B, nullptr, 0, args, lda, ldb, kThreads, stream);
+            default: break;
+        }
+    }
+    return launch_bn<kBN, EPI, false>(A, B, nullptr, 0, args, lda, ldb, kThreads, stream);
+}
+
+template<bool FUSED>
+int launch_ag(const void* A, const void* B, const void* A_local, const Args& args, long long lda, long long ldb, cudaStream_t stream)
+{
+    const int threads = kThreads + (FUSED ? kAgThreads : 0);
+    switch (pick_bn(args.M_total, args.N)) {
+        case 224: return launch_bn<224, kEpiStore, FUSED>(A, B, A_local, args.ag_rows, args, lda, ldb, threads, stream);
+        case 192: return launch_bn<192, kEpiStore, FUSED>(A, B, A_local, args.ag_rows, args, lda, ldb, threads, stream);
+        default: return launch_bn<kBN, kEpiStore, FUSED>(A, B, A_local, args.ag_rows, args, lda, ldb, threads, stream);
+    }
+}
+
+// CTA-pair kernels: 256-row tiles on clusters of two CTAs (one-group GEMMs only).
+int pick_bn_pair(int M, int N)
+{
+    const int  clusters = sm_count() / 2;
+    const long mtiles   = (M + kPairBM - 1) / kPairBM;
+    int        best = 256;
+    long       best_cost = -1;
+    for (int bn : {256, 224, 192}) {
+        const long tiles = mtiles * ((N + bn - 1) / bn);
+        const long cost  = ((tiles + clusters - 1) / clusters) * (bn + 12);
+        if (best_cost < 0 || cost < best_cost) {
+            best      = bn;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
+template<int BN, int STAGES, bool AG>
+int launch_pair_bn(const void* A, const void* B, const void* A_local, const Args& args, long long lda, long long ldb, cudaStream_t stream)
+{
+    using S = SmemPair<BN, STAGES, AG>;
+    CUtensorMap tmA, tmB, tmAL;
     if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.M_total, args.K, lda, kBM, kBK)) return -1;
-    if (make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.rowsB, args.K, ldb, kBN / 2, kBK)) return -1;
-    auto kern = gemm_bf16_tc_kernel<kBN, kStages, kEpiStore, FUSED>;
+    if (make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.rowsB, args.K, ldb, BN / 2, kBK)) return -1;
+    if (A_local) {
+        if (make_tmap_2d(&tmAL, A_local, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.ag_rows, args.K, args.K, kBM, kBK)) return -1;
+    }
+    else {
+        tmAL = tmA;
+    }
+    auto kern = gemm_bf16_pair_kernel<BN, STAGES, AG>;
     static bool configured = false;
     if (!configured) {
         SLIME_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
         configured = true;
     }
-    int grid = sm_count();
-    if (grid_cap > 0 && grid_cap < grid) grid = grid_cap;
-    kern<<<grid, kThreads + (FUSED ? kAgThreads : 0), S::kTotal, stream>>>(tmA, tmB, args);
+    const long tiles    = static_cast<long>((args.M_total + kPairBM - 1) / kPairBM) * ((args.N + BN - 1) / BN);
+    int        clusters = sm_count() / 2;
+    if (!AG && tiles < clusters) clusters = static_cast<int>(tiles);
+    kern<<<2 * clusters, kThreads + (AG ? kAgThreads : 0), S::kTotal, stream>>>(tmA, tmB, tmAL, args);
     SLIME_CUDA_OK(cudaGetLastError());
     return 0;
+}
+
+template<bool AG>
+int launch_pair(const void* A, const void* B, const void* A_local, const Args& args, long long lda, long long ldb, cudaStream_t stream)
+{
+    switch (pick_bn_pair(args.M_total, args.N)) {
+        case 224: return launch_pair_bn<224, 6, AG>(A, B, A_local, args, lda, ldb, stream);
+        case 192: return launch_pair_bn<192, 7, AG>(A, B, A_local, args, lda, ldb, stream);
+        default: return launch_pair_bn<256, 6, AG>(A, B, A_local, args, lda, ldb, stream);
+    }
 }
 
 int check_common(int M, int N, int K, long long lda, long long ldb)
@@ -82,8 +169,25 @@ int slime_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
     a.C          = static_cast<__nv_bfloat16*>(C);
     a.ldc        = ldc;
     a.status     = static_cast<KernelStatus*>(status);
-    const int tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
-    return launch<kEpiStore>(A, B, a, lda, ldb, tiles, static_cast<cudaStream_t>(stream));
+    return launch<kEpiStore>(A, B, a, lda, ldb, static_cast<cudaStream_t>(stream));
+}
+
+// The same product on CTA pairs (256-row tiles, tcgen05 cta_group::2).
+int slime_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                         long long ldc, void* status, void* stream)
+{
+    if (check_common(M, N, K, lda, ldb)) return -1;
+    if (ldc % 8 != 0) return fail("gemm: ldc must be a multiple of 8 elements");
+    Args a{};
+    a.M_total    = M;
+    a.N          = N;
+    a.K          = K;
+    a.rowsB      = N;
+    a.num_groups = 1;
+    a.C          = static_cast<__nv_bfloat16*>(C);
+    a.ldc        = ldc;
+    a.status     = static_cast<KernelStatus*>(status);
+    return launch_pair<false>(A, B, nullptr, a, lda, ldb, static_cast<cudaStream_t>(stream));
 }
 
 int slime_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
@@ -105,8 +209,7 @@ int slime_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, i
     a.a_ready_target = a_ready_target;
     a.m_tile_rotate  = m_tile_rotate;
     a.status         = static_cast<KernelStatus*>(status);
-    const int tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
-    return launch<kEpiStore>(A, B, a, lda, ldb, tiles, static_cast<cudaStream_t>(stream));
+    return launch<kEpiStore>(A, B, a, lda, ldb, static_cast<cudaStream_t>(stream));
 }
 
 // All-gather -> GEMM. a_full is this rank's gathered matrix [world * rows_local, K] inside its symmetric
@@ -138,7 +241,7 @@ int slime_ag_gemm(int mode, const void* x_local, const void* a_full, const void*
         a.ag_flags[i] = i < world ? flags8[i] : 0;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (mode == 0 || mode == 2) {
+    if (mode == 0 || mode == 2 || mode == 3) {
         if ((reinterpret_cast<unsigned long long>(x_local) & 15) != 0) return fail("ag_gemm: local shard must be 16-byte aligned");
         a.ag_src = static_cast<const uint4*>(x_local);
     }
@@ -153,9 +256,13 @@ int slime_ag_gemm(int mode, const void* x_local, const void* a_full, const void*
     a.a_ready_rows   = kBM;
     a.a_ready_target = step * (kBM / kAgSliceRows);
     a.ag_shard_order = 1;
-    const int tiles = ((a.M_total + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
-    if (mode == 1) return launch_ag<false>(a_full, B, a, K, ldb, tiles, s);
-    if (mode == 2) return launch_ag<true>(a_full, B, a, K, ldb, 0, s);
+    if (mode == 1) return launch_ag<false>(a_full, B, nullptr, a, K, ldb, s);
+    a.ag_local_direct = 1;
+    if (mode == 2) return launch_ag<true>(a_full, B, x_local, a, K, ldb, s);
+    if (mode == 3) {  // fused, on CTA pairs
+        if (rows_local % kPairBM != 0) return fail("ag_gemm: the pair kernel needs rows per rank to be a multiple of %d", kPairBM);
+        return launch_pair<true>(a_full, B, x_local, a, K, ldb, s);
+    }
     return fail("ag_gemm: unknown mode %d", mode);
 }
 
@@ -180,11 +287,11 @@ int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* gr
     switch (epilogue) {
         case kEpiStore:
             a.rowsB = N;
-            return launch<kEpiStore>(A, B, a, lda, ldb, 0, s);
+            return launch<kEpiStore>(A, B, a, lda, ldb, s);
         case kEpiSwiGLU:
             if (N % (kBN / 2) != 0) return fail("grouped gemm: SwiGLU needs N to be a multiple of %d", kBN / 2);
             a.rowsB = 2 * N;
-            return launch<kEpiSwiGLU>(A, B, a, lda, ldb, 0, s);
+            return launch<kEpiSwiGLU>(A, B, a, lda, ldb, s);
         case kEpiScatterRows:
             if (row_info == nullptr || scatter_bases8 == nullptr) return fail("grouped gemm: scatter epilogue needs row_info and bases");
             if (scatter_row_bytes % 16 != 0) return fail("grouped gemm: scatter rows must be 16-byte aligned");
@@ -194,7 +301,7 @@ int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* gr
             for (int i = 0; i < 8; ++i) a.scatter_base[i] = scatter_bases8[i];
             a.scatter_row_bytes = scatter_row_bytes;
             a.scatter_slots     = scatter_slots;
-            return launch<kEpiScatterRows>(A, B, a, lda, ldb, 0, s);
+            return launch<kEpiScatterRows>(A, B, a, lda, ldb, s);
         default:
             return fail("grouped gemm: unknown epilogue %d", epilogue);
     }

@@ -14,6 +14,20 @@ from ._common import default_status, ptr, require_cuda, stream_ptr
 EPI_STORE, EPI_SWIGLU, EPI_SCATTER_ROWS = 0, 1, 2
 
 
+def gemm_bf16_pair(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[M, N] = a[M, K] @ b[N, K].T`` on CTA pairs (256-row tiles, ``tcgen05`` ``cta_group::2``)."""
+    require_cuda(a, b)
+    assert a.dtype == b.dtype == torch.bfloat16 and a.stride(1) == 1 and b.stride(1) == 1
+    m, k = a.shape
+    n, kb = b.shape
+    assert k == kb
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    _lib.call("slime_gemm_bf16_pair", ptr(a), ptr(b), ptr(out), m, n, k, a.stride(0), b.stride(0), out.stride(0),
+              default_status().dev_ptr, stream_ptr())
+    return out
+
+
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """``out[M, N] = a[M, K] @ b[N, K].T``."""
     require_cuda(a, b)

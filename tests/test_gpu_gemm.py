@@ -14,7 +14,8 @@ def _check(out, ref, k):
     assert bad == 0, f"{bad} of {out.numel()} elements off; max err {err.max().item():.4g}"
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 512), (256, 512, 4096), (1000, 4096, 4096), (77, 96, 136)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 512), (256, 512, 4096), (1000, 4096, 4096), (77, 96, 136),
+                                   (8192, 3584, 512), (4096, 1152, 256), (300, 4128, 192)])  # tile widths 224 and 192, ragged last tile
 def test_gemm_bf16(m, n, k):
     from dlslime_b200.ops import gemm
     from dlslime_b200.ops._common import default_status
@@ -102,3 +103,19 @@ def test_grouped_gemm_scatter_rows():
     expect[perm] = ref
     expect[perm[3]] = 0
     _check(dst, expect, k)
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 512, 512), (1000, 4096, 4096), (8192, 3584, 512), (4096, 1152, 256), (300, 4128, 192)])
+def test_gemm_bf16_cta_pair(m, n, k):
+    """The cta_group::2 kernel (256-row tiles on two SMs): same product, ragged edges in M and N, all three tile widths."""
+    from dlslime_b200.ops import gemm
+    from dlslime_b200.ops._common import default_status
+
+    torch.manual_seed(m + n + k + 1)
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16)
+    out = gemm.gemm_bf16_pair(a, b)
+    torch.cuda.synchronize()
+    default_status().check()
+    ref = a.float() @ b.float().t()
+    _check(out, ref, k)
