@@ -45,6 +45,7 @@ class AllGatherGemm:
         self._dst = (ctypes.c_ulonglong * 8)(*[p + self.base_off for p in heap.peer_ptrs], *([0] * (8 - self.world)))
         self._flags = (ctypes.c_ulonglong * 8)(*[p + self.flags_off for p in heap.peer_ptrs], *([0] * (8 - self.world)))
         self.status = default_status()
+        self.pair = True  # use the cta_group::2 kernel in forward() when the shard allows it
 
     @staticmethod
     def bytes_needed(rows_local: int, k: int, world: int) -> int:
@@ -81,7 +82,8 @@ class AllGatherGemm:
         if out is None:
             out = torch.empty((self.world * self.rows_local, w.shape[0]), dtype=torch.bfloat16, device=x.device)
         self.step += 1
-        self._call(2, x, w, out, self.step)
+        # CTA pairs (256-row tiles) when the shard is a whole number of them
+        self._call(3 if self.rows_local % 256 == 0 and self.pair else 2, x, w, out, self.step)
         return out
 
     __call__ = forward

@@ -28,8 +28,8 @@ def gemm_bf16_pair(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = 
     return out
 
 
-def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``out[M, N] = a[M, K] @ b[N, K].T``."""
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, pair: bool | None = None) -> torch.Tensor:
+    """``out[M, N] = a[M, K] @ b[N, K].T``. ``pair`` picks the CTA-pair kernel (default: when M >= 256)."""
     require_cuda(a, b)
     assert a.dtype == b.dtype == torch.bfloat16 and a.stride(1) == 1 and b.stride(1) == 1
     m, k = a.shape
@@ -37,6 +37,10 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None)
     assert k == kb
     if out is None:
         out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    if pair is None:
+        pair = m >= 256  # two SMs per 256-row tile pay off as soon as there is a full tile
+    if pair:
+        return gemm_bf16_pair(a, b, out)
     _lib.call("slime_gemm_bf16", ptr(a), ptr(b), ptr(out), m, n, k, a.stride(0), b.stride(0), out.stride(0),
               default_status().dev_ptr, stream_ptr())
     return out
