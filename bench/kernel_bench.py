@@ -2,6 +2,7 @@
 """Single-GPU micro-benchmarks of the sm_100a kernels against their library baselines.
 
     python bench/kernel_bench.py gemm [--m 8192 --n 8192 --k 8192]
+    python bench/kernel_bench.py gemm_fp8 [--m 8192 --n 8192 --k 8192]   # e4m3, 1x128 / 128x128 block scales
     python bench/kernel_bench.py grouped [--experts 32 --rows 1024]
     python bench/kernel_bench.py quant
 
@@ -68,6 +69,23 @@ def cmd_gemm(a):
                       "cublas_ms_best": round(b2, 4), "cublas_tflops_best": round(flops / b2 / 1e9, 1)}))
 
 
+def cmd_gemm_fp8(a):
+    from dlslime_b200.ops import gemm, quant
+
+    hbm, tf, tag = peaks()
+    x = torch.randn(a.m, a.k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(a.n, a.k, device="cuda") * 0.02).to(torch.bfloat16)
+    xq, sx = quant.fp8_quant_1x128(x)
+    wq, sw = quant.fp8_quant_128x128(w)
+    out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+    flops = 2.0 * a.m * a.n * a.k
+    best, med = timeit(lambda: gemm.gemm_fp8_blockscaled(xq, sx, wq, sw, out=out), a.iters)
+    b2, _ = timeit(lambda: gemm.gemm_bf16(x, w, out=out), a.iters)
+    print(json.dumps({"kernel": "gemm_fp8_blockscaled", "m": a.m, "n": a.n, "k": a.k, "ms_best": round(best, 4), "ms_median": round(med, 4),
+                      "tflops_best": round(flops / best / 1e9, 1), "vs_measured_bf16_peak": round(flops / best / 1e9 / tf, 3), "peak": tag,
+                      "bf16_pair_kernel_ms_best": round(b2, 4)}))
+
+
 def cmd_grouped(a):
     from dlslime_b200.ops import gemm
 
@@ -116,7 +134,7 @@ def cmd_quant(a):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("cmd", choices=["gemm", "grouped", "quant"])
+    ap.add_argument("cmd", choices=["gemm", "gemm_fp8", "grouped", "quant"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -125,4 +143,4 @@ if __name__ == "__main__":
     ap.add_argument("--rows-q", type=int, default=32768)
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
-    {"gemm": cmd_gemm, "grouped": cmd_grouped, "quant": cmd_quant}[args.cmd](args)
+    {"gemm": cmd_gemm, "gemm_fp8": cmd_gemm_fp8, "grouped": cmd_grouped, "quant": cmd_quant}[args.cmd](args)

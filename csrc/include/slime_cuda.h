@@ -56,6 +56,12 @@ int slime_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
 // (a_ready[row / a_ready_rows] >= a_ready_target); m tiles start at m_tile_rotate.
 int slime_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                          long long ldc, void* status, void* stream);
+int slime_gemm_fp8_blockscaled(const void* Aq, const float* sa, const void* Bq, const float* sb, void* C, int M, int N, int K,
+                               long long lda, long long ldb, long long ldc, void* status, void* stream);
+int slime_ag_gemm_fp8(int mode, const void* xq_local, const float* sx_local, const void* aq_full, const float* sa_full,
+                      const void* Bq, const float* sb, void* C, int rows_local, int N, int K, long long ldb, long long ldc, int rank,
+                      int world, const unsigned long long* dst8, const unsigned long long* sdst8, const unsigned long long* flags8,
+                      unsigned long long step, int push_blocks, void* status, void* stream);
 int slime_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                           long long ldc, const void* a_ready, int a_ready_rows, unsigned long long a_ready_target,
                           int m_tile_rotate, void* status, void* stream);

@@ -284,7 +284,7 @@ __device__ __forceinline__ bool ag_push_bulk(const Args& a, uint8_t* bufs, uint6
 
 constexpr int kAgThreads = 32;
 
-__global__ void __launch_bounds__(256) ag_push_only_kernel(const Args args)
+static __global__ void __launch_bounds__(256) ag_push_only_kernel(const Args args)
 {
     ag_push_units(args, threadIdx.x, blockDim.x, 1, blockIdx.x, gridDim.x);
 }

@@ -75,3 +75,34 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
               ldc, epilogue, ptr(row_info), scatter_bases, scatter_row_bytes, scatter_slots, ptr(row_scale),
               default_status().dev_ptr, stream_ptr())
     return out
+
+
+def gemm_fp8_blockscaled(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.Tensor,
+                         out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[M, N]`` (bf16) ``= dequant(aq, sa) @ dequant(bq, sb).T`` on the fp8 tensor cores.
+
+    ``aq [M, K]`` / ``bq [N, K]`` are e4m3; ``sa [M, K/128]`` are per-token 1x128 scales, ``sb [ceil(N/128), K/128]``
+    128x128 weight-block scales (what :func:`dlslime_b200.ops.quant.fp8_quant_1x128` / ``fp8_quant_128x128`` produce).
+    """
+    require_cuda(aq, bq, sa, sb)
+    assert aq.dtype == bq.dtype == torch.float8_e4m3fn and aq.stride(1) == 1 and bq.stride(1) == 1
+    assert sa.dtype == sb.dtype == torch.float32 and sa.is_contiguous() and sb.is_contiguous()
+    m, k = aq.shape
+    n, kb = bq.shape
+    assert k == kb and k % 128 == 0
+    assert sa.shape == (m, k // 128) and sb.shape == ((n + 127) // 128, k // 128)
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=aq.device)
+    _lib.call("slime_gemm_fp8_blockscaled", ptr(aq), ptr(sa), ptr(bq), ptr(sb), ptr(out), m, n, k, aq.stride(0), bq.stride(0),
+              out.stride(0), default_status().dev_ptr, stream_ptr())
+    return out
+
+
+def ref_gemm_fp8_blockscaled(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.Tensor) -> torch.Tensor:
+    """fp32 oracle of :func:`gemm_fp8_blockscaled`."""
+    m, k = aq.shape
+    n = bq.shape[0]
+    a = aq.float().view(m, k // 128, 128) * sa.unsqueeze(-1)
+    sb_full = sb.repeat_interleave(128, dim=0)[:n]
+    b = bq.float().view(n, k // 128, 128) * sb_full.unsqueeze(-1)
+    return a.view(m, k) @ b.view(n, k).t()

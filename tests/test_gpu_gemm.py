@@ -119,3 +119,27 @@ def test_gemm_bf16_cta_pair(m, n, k):
     default_status().check()
     ref = a.float() @ b.float().t()
     _check(out, ref, k)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (256, 512, 1024), (1000, 3584, 2048), (300, 4128, 512)])
+def test_gemm_fp8_blockscaled(m, n, k):
+    """e4m3 x e4m3 with 1x128 activation scales and 128x128 weight scales against the fp32 product of the dequantised operands."""
+    from dlslime_b200.ops import gemm, quant
+    from dlslime_b200.ops._common import default_status
+
+    torch.manual_seed(m * 3 + n + k)
+    a = (torch.randn(m, k, device="cuda") * torch.rand(m, 1, device="cuda") * 4).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16)
+    aq, sa = quant.fp8_quant_1x128(a)
+    wq, sb = quant.fp8_quant_128x128(w)
+    out = gemm.gemm_fp8_blockscaled(aq, sa, wq, sb)
+    torch.cuda.synchronize()
+    default_status().check()
+    ref = gemm.ref_gemm_fp8_blockscaled(aq, sa, wq, sb)
+    # same quantised operands on both sides: only fp32 summation order and the bf16 rounding of the output differ
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item() + 1e-3, err
+    # and the product is a faithful fp8 approximation of the bf16 one
+    full = a.float() @ w.float().t()
+    rel = (out.float() - full).norm() / full.norm()
+    assert rel < 0.08, rel.item()
