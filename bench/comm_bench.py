@@ -8,6 +8,7 @@ Cases (shapes from the benchmark definition of this project):
              scatter of 4096 x 64 KiB segments at permuted offsets; baseline = one cudaMemcpyAsync per segment
              (what the reference's NVLinkEndpoint.read does per assignment).
   allgather  low-latency all-gather of [T, 7168] bf16, T in {1, 16, 128, 1024}; baseline = NCCL all_gather_into_tensor.
+  ag_gemm_fp8  the same shape in e4m3 with 1x128 / 128x128 block scales (fp8 payload + scales cross NVLink)
   ag_gemm    per-rank [1024, 8192] bf16 gathered and multiplied by W[28672 / world, 8192]; fused kernel vs
              NCCL all-gather + torch.matmul (cuBLAS).
   kv         TP(world/2) -> TP(world/2) transfer of a 32-layer, 64-token-page KV cache for 16 prompts of
@@ -236,6 +237,54 @@ def case_ag_gemm(rank, world):
          gated_gemm_alone_us=round(gemm_ms * 1e3, 1), plain_gemm_same_shape_us=round(plain_ms * 1e3, 1))
 
 
+def case_ag_gemm_fp8(rank, world):
+    """The same shape in e4m3 with 1x128 / 128x128 block scales: quantise + fused kernel vs NCCL all-gather of the
+    fp8 payload and scales + the block-scaled GEMM alone, and vs the bf16 fused kernel."""
+    from dlslime_b200.ops import gemm, quant
+    from dlslime_b200.ops.ag_gemm import AllGatherGemm, AllGatherGemmFp8
+
+    _, tf, tag = peaks()
+    rows, k, n = 1024, 8192, 28672 // world
+    ag = AllGatherGemmFp8(rows, k)
+    ag16 = AllGatherGemm(rows, k)
+    x = torch.randn(rows, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+    wq, sb = quant.fp8_quant_128x128(w)
+    out = torch.empty(world * rows, n, device="cuda", dtype=torch.bfloat16)
+    fq = torch.empty(world * rows, k, device="cuda", dtype=torch.uint8)
+    fs = torch.empty(world * rows, k // 128, device="cuda", dtype=torch.float32)
+
+    def fused():
+        ag.forward(x, wq, sb, out)
+        dist.barrier()
+
+    def fused_bf16():
+        ag16.forward(x, w, out)
+        dist.barrier()
+
+    def baseline():
+        xq, sx = quant.fp8_quant_1x128(x)
+        dist.all_gather_into_tensor(fq, xq.view(torch.uint8))
+        dist.all_gather_into_tensor(fs, sx)
+        gemm.gemm_fp8_blockscaled(fq.view(torch.float8_e4m3fn), fs, wq, sb, out=out)
+        dist.barrier()
+
+    def gemm_alone():
+        gemm.gemm_fp8_blockscaled(fq.view(torch.float8_e4m3fn), fs, wq, sb, out=out)
+
+    b = timed(lambda: dist.barrier(), 50, sync=dist.barrier)
+    ms = max_ms(timed(fused, 50, sync=dist.barrier) - b, world)
+    ms16 = max_ms(timed(fused_bf16, 50, sync=dist.barrier) - b, world)
+    base = max_ms(timed(baseline, 50, sync=dist.barrier) - b, world)
+    alone = max_ms(timed(gemm_alone, 20, sync=dist.barrier), world)
+    ag.status.check()
+    flops = 2.0 * world * rows * k * n
+    emit(rank, case="ag_gemm_fp8_blockscaled", world=world, M=world * rows, N=n, K=k, us=round(ms * 1e3, 1), tflops=round(flops / ms / 1e9, 1),
+         includes="1x128 quantisation of the local shard", bf16_fused_us=round(ms16 * 1e3, 1),
+         nccl_plus_fp8_gemm_us=round(base * 1e3, 1), speedup_vs_nccl=round(base / ms, 2), fp8_gemm_alone_us=round(alone * 1e3, 1),
+         nvlink_bytes_in_per_rank=(world - 1) * rows * (k + k // 128 * 4))
+
+
 # ------------------------------------------------------------------------------------------ kv
 def case_kv(rank, world):
     from dlslime_b200.models.pd_kv import KVShape, PagedKVCache, PrefillSender, wait_layers
@@ -317,7 +366,7 @@ def main():
     os.environ.setdefault("MASTER_PORT", "29650")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local), rank=rank, world_size=world)
     for case in sys.argv[1:]:
-        {"p2p": case_p2p, "allgather": case_allgather, "ag_gemm": case_ag_gemm, "kv": case_kv}[case](rank, world)
+        {"p2p": case_p2p, "allgather": case_allgather, "ag_gemm": case_ag_gemm, "ag_gemm_fp8": case_ag_gemm_fp8, "kv": case_kv}[case](rank, world)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -2,6 +2,8 @@
 """Small, self-terminating cases for profiler captures (one or a few launches of one kernel).
 
     python bench/profile_case.py gemm        # 4096 x 4096 x 4096 bf16 GEMM, 3 launches
+    python bench/profile_case.py gemm_pair   # the same product on CTA pairs (cta_group::2), 3 launches
+    python bench/profile_case.py gemm_fp8    # the same shape in block-scaled fp8 (e4m3), 3 launches
     python bench/profile_case.py grouped     # grouped SwiGLU gate/up + down GEMM, 8 experts x 512 rows, 2 launches each
     python bench/profile_case.py moe_step    # one single-GPU MoE layer step (T=1024, 32 experts of the 7168/2048 shape)
     python bench/profile_case.py quant       # fp8 1x128 quantise + dequantise of 16384 x 7168
@@ -24,7 +26,29 @@ def gemm_case():
     b = (torch.randn(4096, 4096, device="cuda") * 0.02).to(torch.bfloat16)
     out = torch.empty(4096, 4096, device="cuda", dtype=torch.bfloat16)
     for _ in range(3):
-        gemm.gemm_bf16(a, b, out=out)
+        gemm.gemm_bf16(a, b, out=out, pair=False)
+
+
+def gemm_pair_case():
+    from dlslime_b200.ops import gemm
+
+    a = torch.randn(4096, 4096, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(4096, 4096, device="cuda") * 0.02).to(torch.bfloat16)
+    out = torch.empty(4096, 4096, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        gemm.gemm_bf16_pair(a, b, out=out)
+
+
+def gemm_fp8_case():
+    from dlslime_b200.ops import gemm, quant
+
+    a = torch.randn(4096, 4096, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(4096, 4096, device="cuda") * 0.02).to(torch.bfloat16)
+    aq, sa = quant.fp8_quant_1x128(a)
+    bq, sb = quant.fp8_quant_128x128(b)
+    out = torch.empty(4096, 4096, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        gemm.gemm_fp8_blockscaled(aq, sa, bq, sb, out=out)
 
 
 def grouped_case():
@@ -80,6 +104,6 @@ def copy_case():
 
 
 if __name__ == "__main__":
-    {"gemm": gemm_case, "grouped": grouped_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
+    {"gemm": gemm_case, "gemm_pair": gemm_pair_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
     torch.cuda.synchronize()
     print("done", sys.argv[1])

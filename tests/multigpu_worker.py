@@ -123,6 +123,29 @@ def check_ag_gemm(rank, world):
         dist.barrier()  # nobody may overwrite the gathered matrix before every rank has consumed it
 
 
+def check_ag_gemm_fp8(rank, world):
+    from dlslime_b200.ops import gemm, quant
+    from dlslime_b200.ops.ag_gemm import AllGatherGemmFp8
+
+    rows, k, n = 256, 1024, 512
+    ag = AllGatherGemmFp8(rows, k)
+    wq, sb = quant.fp8_quant_128x128((torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16))
+    for step in range(3):
+        x = (torch.randn(rows, k, device="cuda") * (1 + rank)).to(torch.bfloat16)
+        xq, sx = quant.fp8_quant_1x128(x)
+        fq = torch.empty((world * rows, k), dtype=torch.uint8, device="cuda")
+        fs = torch.empty((world * rows, k // 128), dtype=torch.float32, device="cuda")
+        dist.all_gather_into_tensor(fq, xq.view(torch.uint8))
+        dist.all_gather_into_tensor(fs, sx)
+        out = ag(x, wq, sb)
+        torch.cuda.synchronize()
+        ag.status.check()
+        ref = gemm.ref_gemm_fp8_blockscaled(fq.view(torch.float8_e4m3fn), fs, wq, sb)
+        err = (out.float() - ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item() + 1e-3, f"ag_gemm_fp8 rank {rank}: {err}"
+        dist.barrier()
+
+
 def check_kv(rank, world):
     """Ranks [0, world/2) play prefill and push into the paged cache of rank + world/2."""
     from dlslime_b200.models.pd_kv import KVShape, PagedKVCache, PrefillSender, wait_layers
@@ -167,7 +190,7 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    which = sys.argv[1:] or ["endpoint", "allgather", "moe", "ag_gemm", "kv"]
+    which = sys.argv[1:] or ["endpoint", "allgather", "moe", "ag_gemm", "ag_gemm_fp8", "kv"]
     for name in which:
         globals()[f"check_{name}"](rank, world)
         if rank == 0:
