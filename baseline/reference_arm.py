@@ -187,12 +187,13 @@ def run(args, rank, world, local, T, make_inputs, sync_all, max_over_ranks, Cloc
         torch.cuda.current_stream().synchronize()
 
     def timed(fn):
-        for i in range(args.warmup):
-            fn(i)
-        sync_all(world)
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
+        for i in range(args.warmup):
+            fn(i)
+        sync_all(world)
+        sampler.mark_begin()
         layer.copies = 0
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -200,6 +201,7 @@ def run(args, rank, world, local, T, make_inputs, sync_all, max_over_ranks, Cloc
             fn(i)
         e1.record()
         sync_all(world)
+        sampler.mark_end()
         clocks = sampler.stop() if rank == 0 else None
         return max_over_ranks(e0.elapsed_time(e1) / args.steps, world), clocks
 

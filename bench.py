@@ -55,6 +55,14 @@ class ClockSampler:
         self.gpu_index = gpu_index
         self.proc = None
         self.path = None
+        self.t0 = self.t1 = None
+
+    def mark_begin(self):
+        """The timed region starts now (the sampler may have been started earlier, e.g. before the warm-up)."""
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def start(self):
         try:
@@ -62,7 +70,7 @@ class ClockSampler:
             os.close(fd)
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu=timestamp,{self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu_index)], stdout=self.out, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -79,19 +87,30 @@ class ClockSampler:
         self.out.close()
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         with open(self.path) as f:
             for line in f:
                 parts = [p.strip() for p in line.split(",")]
-                if len(parts) < 9:
+                if len(parts) < 10:
                     continue
                 try:
-                    sm.append(float(parts[1]))
-                    smax.append(float(parts[2]))
+                    import datetime
+
+                    ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
                 except ValueError:
-                    continue
-                for name, val in zip(names, parts[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
+                    ts = None
+                rows.append((ts, parts[1:]))
+        # samples taken inside the marked window; if the marks are missing or nothing falls inside, all of them
+        inside = [r for r in rows if r[0] is not None and self.t0 is not None and self.t1 is not None and self.t0 <= r[0] <= self.t1 + 0.05]
+        for _, parts in (inside or rows):
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
         os.unlink(self.path)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
@@ -116,6 +135,11 @@ def init_dist(n_gpus: int):
             raise SystemExit(subprocess.call(cmd))
         raise SystemExit(f"WORLD_SIZE={world} does not match --gpus {n_gpus}")
     torch.cuda.set_device(local)
+    if os.environ.get("SLIME_NO_NUMA_BIND", "0") != "1":
+        # staging buffers pinned after this point live on the socket this rank's GPU hangs off
+        from dlslime_b200.utils.numa import bind_to_device_numa
+
+        bind_to_device_numa(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -244,14 +268,15 @@ def run_ours(args, rank, world, local):
     pipe = Pipelined() if graph is None else None
 
     def timed(fn):
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()  # nvidia-smi needs a moment to come up: started before the warm-up, windowed below
         for i in range(args.warmup):
             fn(i)
         if fn is pipe:
             pipe.drain()
         sync_all(world)
-        sampler = ClockSampler(local)
-        if rank == 0:
-            sampler.start()
+        sampler.mark_begin()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
         for i in range(args.steps):
@@ -262,6 +287,7 @@ def run_ours(args, rank, world, local):
         if fn is pipe:
             pipe.drain()
         sync_all(world)
+        sampler.mark_end()
         clocks = sampler.stop() if rank == 0 else None
         ms = ev0.elapsed_time(ev1) / args.steps
         layer.buf.status.check()
@@ -317,7 +343,7 @@ def run_reference(args, rank, world, local):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--mode", choices=["ll", "normal"], default="normal")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
