@@ -343,7 +343,7 @@ def run_reference(args, rank, world, local):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--mode", choices=["ll", "normal"], default="normal")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
