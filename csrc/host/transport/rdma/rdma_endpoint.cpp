@@ -301,6 +301,7 @@ std::shared_ptr<ReadWriteFuture> RdmaEndpoint::submit_one_sided(OpCode opcode, c
         obs::record_submit(st->link_id, obs::op_index(opcode), assign.size(), bytes);
         if (stream != nullptr && !engine_env().bypass_device_signal) st->signal->bind_stream(stream);
         st->signal->record_gpu_ready();
+        track(st);
         tx_fifo_[CH_IO].push_back(std::move(op));
     }
     wake_worker();
@@ -370,6 +371,7 @@ std::shared_ptr<SendFuture> RdmaEndpoint::send(const chunk_tuple_t& chunk, void*
     op.lkey   = static_cast<uint32_t>(mr.lkey);
     if (stream != nullptr && !engine_env().bypass_device_signal) st->signal->bind_stream(stream);
     st->signal->record_gpu_ready();
+    track(st);
     {
         std::lock_guard<std::mutex> g(fifo_mu_);
         send_fifo_.push_back(std::move(op));
@@ -400,6 +402,7 @@ std::shared_ptr<RecvFuture> RdmaEndpoint::recv(const chunk_tuple_t& chunk, void*
     op.rkey   = static_cast<uint32_t>(mr.rkey);
     if (stream != nullptr && !engine_env().bypass_device_signal) st->signal->bind_stream(stream);
     st->signal->record_gpu_ready();
+    track(st);
     {
         std::lock_guard<std::mutex> g(fifo_mu_);
         op.seq = recv_seq_++;
@@ -412,9 +415,19 @@ std::shared_ptr<RecvFuture> RdmaEndpoint::recv(const chunk_tuple_t& chunk, void*
 // ---------------------------------------------------------------------------------------------------
 // progress thread
 
+void RdmaEndpoint::track(const std::shared_ptr<EndpointOpState>& st)
+{
+    std::lock_guard<std::mutex> g(inflight_mu_);
+    inflight_[st.get()] = st;
+}
+
 void RdmaEndpoint::complete_state(const std::shared_ptr<EndpointOpState>& st)
 {
     if (st->obs_completed.exchange(true)) return;
+    {
+        std::lock_guard<std::mutex> g(inflight_mu_);
+        inflight_.erase(st.get());
+    }
     st->trace_end_ns.store(monotonic_ns());
     obs::OpIndex oi = obs::op_index(st->opcode);
     if (st->completion_status.load() == SUCCESS)
@@ -779,9 +792,12 @@ void RdmaEndpoint::cancel_all()
         for (auto& op : announced_) victims.push_back(op.state);
         announced_.clear();
     }
-    for (auto& tl : tx_slots_) {
-        auto st = tl.state;
-        if (st) victims.push_back(st);
+    {
+        // operations whose work requests are already with the device: their lane slots are released by the
+        // completions (or flushes) that are still to come; here they are only settled towards the caller
+        std::lock_guard<std::mutex> g(inflight_mu_);
+        for (auto& kv : inflight_)
+            if (auto st = kv.second.lock()) victims.push_back(st);
     }
     for (auto& st : victims) {
         const uint32_t done = st->signal->get_comm_done_mask();

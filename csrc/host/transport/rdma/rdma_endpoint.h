@@ -34,6 +34,7 @@
 #include <deque>
 #include <mutex>
 #include <optional>
+#include <unordered_map>
 #include <vector>
 
 #include "core/ring.h"
@@ -174,6 +175,11 @@ private:
     std::deque<SendOp>  send_fifo_;
     size_t              rr_lane_ = 0;     // round robin for unstriped chunks (fifo_mu_)
     uint64_t            recv_seq_ = 0;
+
+    // operations submitted and not yet settled, for cancel_all (weak: the futures own the state)
+    std::mutex                                                            inflight_mu_;
+    std::unordered_map<EndpointOpState*, std::weak_ptr<EndpointOpState>> inflight_;
+    void track(const std::shared_ptr<EndpointOpState>& st);
 
     // in-flight lane slots
     std::vector<TxLane>  tx_slots_;

@@ -16,6 +16,8 @@
 #include <string>
 #include <vector>
 
+#include <cstdlib>
+
 #include "common/host_utils.h"
 #include "common/ptx.cuh"
 #include "slime_cuda.h"
@@ -113,6 +115,73 @@ __global__ void __launch_bounds__(kThreads) p2p_scatter_gather_kernel(CopyArgs a
             fence_acq_rel_sys();
             is_last = atomicAdd(a.block_counter, 1u) == gridDim.x - 1;
             if (is_last) {
+                fence_acq_rel_sys();
+                if (a.signal_add)
+                    red_add_release_sys(a.signal, a.signal_value);
+                else
+                    st_release_sys(a.signal, a.signal_value);
+                *a.block_counter = 0;
+            }
+        }
+    }
+}
+
+// The same batch through the bulk-copy engine, for batches whose addresses and lengths are all multiples of 16 bytes.
+// One thread per CTA drives a ring of shared-memory buffers: a 64 KiB unit is fetched with up to eight 8 KiB
+// global -> shared bulk loads that are all in flight together (loads from peer memory included), and every chunk
+// is handed on with a shared -> global bulk store as soon as it has landed. The engine keeps tens of KB per CTA
+// in flight, which is what a read from peer memory needs to cover the NVLink round trip; 16-byte loads issued by
+// threads stall at a few hundred GB/s.
+constexpr int kBulkBufs  = 8;
+constexpr int kBulkChunk = 8192;
+
+__global__ void __launch_bounds__(32) p2p_bulk_kernel(CopyArgs a, InlineBatch inl)
+{
+    extern __shared__ __align__(128) unsigned char bulk_smem[];
+    __shared__ uint64_t bars[kBulkBufs];
+    if (threadIdx.x == 0) {
+        for (int b = 0; b < kBulkBufs; ++b) mbar_init(&bars[b], 1);
+        fence_mbar_init();
+        unsigned int parity = 0;  // bit c: phase of barrier c
+        bool         ok     = true;
+        for (unsigned long long u = blockIdx.x; u < a.n_units && ok; u += gridDim.x) {
+            int lo = 0, hi = a.n_seg - 1;
+            while (lo < hi) {
+                const int                mid = (lo + hi + 1) >> 1;
+                const unsigned long long fu  = a.table ? a.table[mid].first_unit : inl.seg[mid].first_unit;
+                if (fu <= u)
+                    lo = mid;
+                else
+                    hi = mid - 1;
+            }
+            const Segment            seg = a.table ? a.table[lo] : inl.seg[lo];
+            const unsigned long long off = (u - seg.first_unit) * kUnitBytes;
+            const unsigned long long n   = min(kUnitBytes, seg.len - off);
+            const int                nch = static_cast<int>((n + kBulkChunk - 1) / kBulkChunk);
+            tma_store_wait_read<0>();  // the stores of the previous unit have left the buffers
+            for (int c = 0; c < nch; ++c) {
+                const unsigned long long o     = static_cast<unsigned long long>(c) * kBulkChunk;
+                const uint32_t           bytes = static_cast<uint32_t>(min(static_cast<unsigned long long>(kBulkChunk), n - o));
+                mbar_arrive_expect_tx(&bars[c], bytes);
+                bulk_load_g2s(bulk_smem + c * kBulkChunk, reinterpret_cast<const void*>(seg.src + off + o), bytes, &bars[c]);
+            }
+            for (int c = 0; c < nch; ++c) {
+                const unsigned long long o     = static_cast<unsigned long long>(c) * kBulkChunk;
+                const uint32_t           bytes = static_cast<uint32_t>(min(static_cast<unsigned long long>(kBulkChunk), n - o));
+                if (!mbar_wait(&bars[c], (parity >> c) & 1u, nullptr, 20, c)) {
+                    ok = false;  // the load never landed: stop issuing, leave through the common exit
+                    break;
+                }
+                parity ^= 1u << c;
+                bulk_store_s2g(reinterpret_cast<void*>(seg.dst + off + o), bulk_smem + c * kBulkChunk, bytes);
+                tma_store_commit();
+            }
+        }
+        tma_store_wait<0>();  // every byte has been written before the CTA reports in
+        fence_proxy_async();
+        if (a.signal != nullptr) {
+            fence_acq_rel_sys();
+            if (atomicAdd(a.block_counter, 1u) == gridDim.x - 1) {
                 fence_acq_rel_sys();
                 if (a.signal_add)
                     red_add_release_sys(a.signal, a.signal_value);
@@ -345,6 +414,7 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
             seg_out = slot->host;
         }
         unsigned long long units = 0;
+        bool               all_aligned = true;
         {
             std::lock_guard<std::mutex> g(ep->mu);
             for (int i = 0; i < batch; ++i) {
@@ -364,6 +434,7 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
                 s.dst        = is_write ? R.addr + roff : L.addr + loff;
                 s.src        = is_write ? L.addr + loff : R.addr + roff;
                 s.len        = len;
+                if (((s.dst | s.src | len) & 15ull) != 0) all_aligned = false;
                 s.first_unit = units;
                 units += (len + kUnitBytes - 1) / kUnitBytes;
                 if (len == 0) units += 0;
@@ -384,10 +455,25 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
             SLIME_CUDA_OK(cudaMemcpyAsync(slot->dev, slot->host, sizeof(Segment) * batch, cudaMemcpyHostToDevice, stream));
             a.table = slot->dev;
         }
-        long long grid = static_cast<long long>(std::min<unsigned long long>(units, static_cast<unsigned long long>(sm_count()) * 8));
-        if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
-        if (grid < 1) grid = 1;
-        p2p_scatter_gather_kernel<<<static_cast<int>(grid), kThreads, 0, stream>>>(a, inl);
+        static const bool bulk_off = std::getenv("SLIME_NVLINK_NO_BULK") != nullptr;
+        if (all_aligned && !bulk_off && units > 0) {
+            // three 64 KiB rings fit in one SM's shared memory
+            constexpr int kBulkSmem = kBulkBufs * kBulkChunk;
+            static bool   configured = false;
+            if (!configured) {
+                SLIME_CUDA_OK(cudaFuncSetAttribute(p2p_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmem));
+                configured = true;
+            }
+            long long grid = static_cast<long long>(std::min<unsigned long long>(units, static_cast<unsigned long long>(sm_count()) * 3));
+            if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
+            p2p_bulk_kernel<<<static_cast<int>(grid), 32, kBulkSmem, stream>>>(a, inl);
+        }
+        else {
+            long long grid = static_cast<long long>(std::min<unsigned long long>(units, static_cast<unsigned long long>(sm_count()) * 8));
+            if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
+            if (grid < 1) grid = 1;
+            p2p_scatter_gather_kernel<<<static_cast<int>(grid), kThreads, 0, stream>>>(a, inl);
+        }
         SLIME_CUDA_OK(cudaGetLastError());
         if (slot) SLIME_CUDA_OK(cudaEventRecord(slot->done, stream));  // the slot is free once the kernel has read its table
         done += batch;

@@ -131,6 +131,8 @@ def build_host(verbose: bool = False, workers: int | None = None) -> Path:
     cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else os.environ.get("CXX", "g++")
     jobs, objs, main_objs = [], [], []
     for src in sorted(hdir.rglob("*.cpp")):
+        if "stress" in src.relative_to(hdir).parts:
+            continue  # sanitizer stress programs are built by build_stress()
         rel = "_".join(src.relative_to(hdir).with_suffix("").parts)
         obj = OBJ / "host" / (rel + ".o")
         cmd = [cxx, *CXX_FLAGS, *sum((["-I", i] for i in inc), []), "-c", src, "-o", obj]
@@ -150,6 +152,32 @@ def build_host(verbose: bool = False, workers: int | None = None) -> Path:
             core = [o for o in objs if not o.name.startswith("bind")]
             _run([cxx, "-o", exe, *main_objs, *core, "-pthread", "-ldl", "-lrt"], verbose)
     return out
+
+
+def build_stress(sanitizer: str, verbose: bool = False) -> Path:
+    """Builds csrc/host/stress/host_stress.cpp with the whole host runtime (minus the Python bindings) under a
+    sanitizer: ``thread`` or ``address,undefined``. Returns the program's path."""
+    hdir = CSRC / "host"
+    tag = sanitizer.replace(",", "_")
+    odir = OBJ / f"san_{tag}"
+    odir.mkdir(parents=True, exist_ok=True)
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else os.environ.get("CXX", "g++")
+    flags = ["-O1", "-g", "-std=c++17", "-pthread", f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer"]
+    inc = [CSRC / "include", hdir]
+    dep = _newest_header_mtime([CSRC / "include", hdir])
+    jobs, objs = [], []
+    for src in sorted(hdir.rglob("*.cpp")):
+        parts = src.relative_to(hdir).parts
+        if parts[0] == "bind" or src.name == "nanoctrl_main.cpp":
+            continue
+        obj = odir / ("_".join(src.relative_to(hdir).with_suffix("").parts) + ".o")
+        jobs.append((src, obj, [cxx, *flags, *sum((["-I", i] for i in inc), []), "-c", src, "-o", obj], dep))
+        objs.append(obj)
+    changed = _compile_many(jobs, verbose, min(8, os.cpu_count() or 4))
+    exe = odir / "host_stress"
+    if changed or not exe.exists():
+        _run([cxx, *flags, "-o", exe, *objs, "-ldl", "-lrt"], verbose)
+    return exe
 
 
 def build_all(verbose: bool = False) -> None:

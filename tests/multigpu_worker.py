@@ -41,6 +41,14 @@ def check_endpoint(rank, world):
             expect[loff:loff + ln] = peer_orig[roff:roff + ln]
         torch.cuda.synchronize()
         assert torch.equal(buf, expect), "endpoint read mismatch"
+        # aligned batch (the bulk-copy-engine path): 40 scattered 64 KiB pieces, one 200 KiB piece, one 48-byte piece
+        segs = [("buffer", "buffer", half + (2 << 20) + 65536 * ((7 * i) % 40), (2 << 20) + 65536 * i, 65536) for i in range(20)]
+        segs += [("buffer", "buffer", half + 4096, 4096, 200 << 10), ("buffer", "buffer", half + 16, 1 << 19, 48)]
+        assert ep.read(segs).wait() == 0
+        for _, _, roff, loff, ln in segs:
+            expect[loff:loff + ln] = peer_orig[roff:roff + ln]
+        torch.cuda.synchronize()
+        assert torch.equal(buf, expect), "endpoint bulk read mismatch"
     dist.barrier()
     if rank < peer:
         # write with immediate data: push my lower half into the peer's lower half, then notify
@@ -54,6 +62,8 @@ def check_endpoint(rank, world):
         # what the peer wrote is ITS buffer after its own reads; recompute that
         psegs = [(half + 1000 * i + (i % 3), 5000 * i + (i % 5), 777 + 16 * i) for i in range(200)]
         psegs.append((half + (1 << 20), 1 << 20, 1 << 20))
+        psegs += [(half + (2 << 20) + 65536 * ((7 * i) % 40), (2 << 20) + 65536 * i, 65536) for i in range(20)]
+        psegs += [(half + 4096, 4096, 200 << 10), (half + 16, 1 << 19, 48)]
         pbuf = peer_orig.clone()
         for roff, loff, ln in psegs:
             pbuf[loff:loff + ln] = orig[roff:roff + ln]
