@@ -302,3 +302,33 @@ def test_peer_agent_over_rdma_links():
         print("ok")
     """)
     assert "ok" in out
+
+
+def test_obs_counts_each_operation_once_with_four_queue_pairs():
+    """Accounting is per user operation, not per queue pair or work request (the reference pins this in
+    tests/python/test_obs_multi_qp.py): bytes completed equal bytes submitted, nothing stays pending."""
+    out = run_child("""
+        a, b = pair(num_qp=4)
+        n = 8 << 20
+        src = buf(n, 1); dst = buf(n)
+        a.register_memory_region("src", ctypes.addressof(src), 0, n)
+        b.register_memory_region("dst", ctypes.addressof(dst), 0, n)
+        link(a, b)
+        ha, hb = a.get_mr_handle("src"), a.get_remote_mr_handle("dst")
+        total = 0   # a fresh process: every counter starts at zero
+        for k in range(10):
+            assert a.write([(ha, hb, 0, 0, 1 << 20), (ha, hb, 1 << 20, 1 << 20, 4096)]).wait(5000) == 0
+            total += (1 << 20) + 4096
+        assert a.read([(ha, hb, 0, 0, 2 << 20)]).wait(5000) == 0
+        snap = C.obs_snapshot()
+        nic = [x for x in snap["nics"] if x["nic"] == "rdma_lo0"][0]
+        w, r = nic["by_op"]["write"], nic["by_op"]["read"]
+        assert w["batch"] == 10 and w["assign"] == 20 and w["errors"] == 0 and w["pending"] == 0, w
+        assert w["completed_bytes"] == total and w["submitted_bytes"] == total, w
+        assert r["batch"] == 1 and r["completed_bytes"] == 2 << 20, r
+        assert snap["summary"]["pending_ops"] == 0 and nic["pending_ops"] == 0, snap["summary"]
+        assert w["post_wr"] == 10 * 5 and w["post_bytes"] == total, w      # 4 stripes + 1 small piece per write, counted apart
+        a.shutdown(); b.shutdown()
+        print("ok")
+    """, env_extra={"DLSLIME_OBS": "1"})
+    assert "ok" in out
