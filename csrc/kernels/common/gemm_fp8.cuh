@@ -9,14 +9,15 @@
 // loop. Two-level accumulation: a K block (128 bytes = one swizzle row = one pipeline stage) is FOUR
 // tcgen05.mma.kind::f8f6f4 (K = 32 each) into a fresh TMEM partial; eight "promotion" warps read the
 // partial (tcgen05.ld), multiply by sa * sb and add into fp32 registers, while the tensor core already
-// fills the other partial (two partials of 128 x 256 fp32 = all 512 TMEM columns). One thread owns one
-// row and 128 of the 256 columns, so it carries 128 accumulators; at the end of the tile it converts and
-// stores its 256 contiguous output bytes. Ten warps put three on one scheduler partition, which caps a
-// thread at 168 registers: the partial is therefore read 32 columns at a time (64 at a time spills into the
-// inner loop and halves the speed; overlapping two 32-column reads was measured 5 % slower than not).
+// fills the other partial. The promotion is the critical path: a TMEM read costs a few hundred cycles and a
+// thread's reads of one partial are dependent steps, so the tile is 128 x 192 and TWELVE warps share a
+// partial: one thread owns one row and 64 columns (two 32-column reads and 64 FMAs per K block, 64
+// accumulators), which keeps 14 warps under the 128-register limit of four warps per scheduler partition.
+// (Measured on 8192^3 with 128 x 256 tiles and eight warps of 128 columns each: 0.62 ms, the tensor pipe
+// 39 % busy; 64-column reads spilled and halved the speed; overlapping two reads was 5 % slower.)
 //
-// Roles per CTA (320 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps 2..9
-// promotion + epilogue (warp w reads TMEM lane quadrant w % 4, column half (w - 2) / 4). Every wait is
+// Roles per CTA (448 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps 2..13
+// promotion + epilogue (warp w reads TMEM lane quadrant w % 4, column slice (w - 2) / 4). Every wait is
 // bounded and reports through the status page, as in the bf16 kernels. The all-gather roles of
 // gemm_tc.cuh carry over: shard-major tiles, own shard read in place, tiles gated on arrival counters, one
 // push warp that sends fp8 payload AND scales (half the NVLink bytes of the bf16 form).
@@ -28,10 +29,13 @@ namespace slime {
 namespace gemm {
 
 constexpr int kF8BK       = 128;  // fp8 elements (= bytes) per K block
-constexpr int kF8BN       = 256;
-constexpr int kF8Stages   = 4;
-constexpr int kF8Threads  = 320;
-constexpr int kF8PromoThreads = 256;
+constexpr int kF8BN         = 192;  // tile width: three 64-column slices per TMEM lane quadrant
+constexpr int kF8Cols       = 64;   // columns per promotion thread
+constexpr int kF8PartStride = 256;  // TMEM columns between the two partials
+constexpr int kF8Stages     = 5;
+constexpr int kF8PromoWarps = 4 * (kF8BN / kF8Cols);
+constexpr int kF8Threads    = (2 + kF8PromoWarps) * 32;
+constexpr int kF8PromoThreads = kF8PromoWarps * 32;
 
 struct F8Args {
     int M, N, K;
@@ -292,7 +296,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t tmem_d = tmem_base + part * kF8BN;
+                    const uint32_t tmem_d = tmem_base + part * kF8PartStride;
                     const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
                     const uint32_t sb = sa + S::kABytes;
                     const uint64_t da = make_kmajor_sw128_desc(sa);
@@ -314,7 +318,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             if (!ok) *fail_slot = 1;
         }
     }
-    else if (AG && warp >= 10) {
+    else if (AG && warp >= 2 + kF8PromoWarps) {
         if (f.ag.ag_src != nullptr && lane == 0) {
             if (!ag_push_bulk_f8(f, ag_bufs, ag_bar, S::kAgBufs, blockIdx.x, gridDim.x, st, lim)) *fail_slot = 1;
         }
@@ -322,7 +326,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
     else {
         // ------------------------------ promotion + epilogue ------------------------------
         const int quad = warp & 3;
-        const int half = (warp - 2) >> 2;  // which 128 of the 256 tile columns
+        const int grp  = (warp - 2) >> 2;  // which 64-column slice of the tile
         const int srow = kblocks;          // scales per row
         F8Walker  walk(f);
         int       row0, nt;
@@ -349,12 +353,12 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                     }
                 }
             }
-            const int    nblk   = nt * (kF8BN / 128) + half;
+            const int    nblk   = (nt * kF8BN + grp * kF8Cols) / 128;  // a 64-column slice never straddles a 128-wide scale block
             const int    nblk_c = nblk < (f.N + 127) / 128 ? nblk : (f.N + 127) / 128 - 1;
             const float* sb_row = f.sb + static_cast<long long>(nblk_c) * srow;
-            float acc[128];
+            float acc[kF8Cols];
 #pragma unroll
-            for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+            for (int i = 0; i < kF8Cols; ++i) acc[i] = 0.0f;
             float s_next = sa_row[0] * sb_row[0];
             for (int kb = 0; kb < kblocks; ++kb) {
                 const float s = s_next;
@@ -364,9 +368,9 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + part * kF8BN + half * 128;
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + part * kF8PartStride + grp * kF8Cols;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < kF8Cols / 32; ++c) {
                     uint32_t v[32];
                     tmem_ld_32x32b_x32(taddr + c * 32, v);
                     tmem_ld_wait();
@@ -381,12 +385,12 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 }
             }
             if (!ok) break;
-            const int col0 = nt * kF8BN + half * 128;
+            const int col0 = nt * kF8BN + grp * kF8Cols;
             if (valid) {
                 __nv_bfloat16* crow_ptr = f.C + static_cast<long long>(row) * f.ldc + col0;
                 const int      cols     = f.N - col0;  // a multiple of 8 (N % 32 == 0)
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
+                for (int i = 0; i < kF8Cols / 8; ++i) {
                     if (i * 8 < cols) {
                         uint4 o = make_uint4(pack_bf16(acc[8 * i], acc[8 * i + 1]), pack_bf16(acc[8 * i + 2], acc[8 * i + 3]),
                                              pack_bf16(acc[8 * i + 4], acc[8 * i + 5]), pack_bf16(acc[8 * i + 6], acc[8 * i + 7]));
