@@ -65,7 +65,9 @@ static void bind_future(py::module_& m, const char* name)
         .def("wait", [](const Fut& f, double timeout) { return f.wait(timeout < 0 ? -1 : static_cast<int64_t>(timeout * 1000)); },
              py::arg("timeout") = -1.0, py::call_guard<py::gil_scoped_release>(),
              "Block until the operation completed; returns the status (0 ok, 402 timeout, 403 failed).")
-        .def("done", &Fut::done);
+        .def("done", &Fut::done)
+        .def("wait_on_stream", &Fut::wait_on_stream,
+             "Make the stream given at submission wait on the device for this operation (stream-ordered signals only).");
 }
 
 PYBIND11_MODULE(_slime_c, m)
@@ -142,7 +144,18 @@ PYBIND11_MODULE(_slime_c, m)
         .def("is_gpu_ready", &DeviceSignal::is_gpu_ready)
         .def("get_comm_done_mask", &DeviceSignal::get_comm_done_mask)
         .def("force_complete", &DeviceSignal::force_complete)
+        .def("bind_stream", [](DeviceSignal& s, uintptr_t stream) { s.bind_stream(reinterpret_cast<void*>(stream)); })
+        .def("wait_comm_done_on_stream", &DeviceSignal::wait_comm_done_on_stream, py::arg("mask") = 1)
         .def("reset_all", &DeviceSignal::reset_all);
+    // Addresses of four C functions (see StreamHooks); the kernel library's loader passes its own.
+    m.def("install_stream_hooks", [](uintptr_t alloc_words, uintptr_t free_words, uintptr_t record_value, uintptr_t wait_mask) {
+        StreamHooks& h = stream_hooks();
+        h.alloc_words  = reinterpret_cast<decltype(h.alloc_words)>(alloc_words);
+        h.free_words   = reinterpret_cast<decltype(h.free_words)>(free_words);
+        h.record_value = reinterpret_cast<decltype(h.record_value)>(record_value);
+        h.wait_mask    = reinterpret_cast<decltype(h.wait_mask)>(wait_mask);
+    });
+    m.def("stream_hooks_installed", [] { return stream_hooks().installed(); });
     m.def("create_signal", [](bool bypass) { return create_signal(bypass); }, py::arg("bypass") = true);
 
     bind_future<OpFuture>(m, "SlimeSendFuture");
@@ -150,11 +163,13 @@ PYBIND11_MODULE(_slime_c, m)
     py::class_<ReadWriteFuture, std::shared_ptr<ReadWriteFuture>>(m, "SlimeReadWriteFuture")
         .def("wait", [](const ReadWriteFuture& f, double timeout) { return f.wait(timeout < 0 ? -1 : static_cast<int64_t>(timeout * 1000)); },
              py::arg("timeout") = -1.0, py::call_guard<py::gil_scoped_release>())
-        .def("done", &ReadWriteFuture::done);
+        .def("done", &ReadWriteFuture::done)
+        .def("wait_on_stream", &ReadWriteFuture::wait_on_stream);
     py::class_<ImmRecvFuture, std::shared_ptr<ImmRecvFuture>>(m, "SlimeImmRecvFuture")
         .def("wait", [](const ImmRecvFuture& f, double timeout) { return f.wait(timeout < 0 ? -1 : static_cast<int64_t>(timeout * 1000)); },
              py::arg("timeout") = -1.0, py::call_guard<py::gil_scoped_release>())
         .def("done", &ImmRecvFuture::done)
+        .def("wait_on_stream", &ImmRecvFuture::wait_on_stream)
         .def("imm_data", &ImmRecvFuture::imm_data)
         .def("time_trace_enabled", &ImmRecvFuture::time_trace_enabled)
         .def("time_trace_start_ns", &ImmRecvFuture::time_trace_start_ns)

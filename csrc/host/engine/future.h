@@ -13,6 +13,7 @@
 #include <stdexcept>
 #include <string>
 
+#include "core/env.h"
 #include "engine/assignment.h"
 #include "engine/signal.h"
 
@@ -40,7 +41,7 @@ struct EndpointOpState {
 inline std::shared_ptr<EndpointOpState> make_op_state(uint32_t mask, OpCode op)
 {
     auto st           = std::make_shared<EndpointOpState>();
-    st->signal        = create_signal();
+    st->signal        = create_signal(engine_env().bypass_device_signal != 0);
     st->expected_mask = mask;
     st->opcode        = op;
     return st;
@@ -64,6 +65,9 @@ public:
     {
         return (st_->signal->get_comm_done_mask() & st_->expected_mask) == st_->expected_mask;
     }
+    // Makes the stream the operation was submitted with wait (bounded, on the device) for its completion; a no-op for
+    // host-only signals.
+    void wait_on_stream() const { st_->signal->wait_comm_done_on_stream(st_->expected_mask); }
     const std::shared_ptr<EndpointOpState>& state() const { return st_; }
 
 protected:

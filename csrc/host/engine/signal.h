@@ -16,6 +16,7 @@
 #include <functional>
 #include <memory>
 #include <mutex>
+#include <vector>
 
 #include "core/ring.h"
 
@@ -38,14 +39,18 @@ public:
     virtual void reset_all()                                        = 0;
 };
 
-// Hooks that let a CUDA-aware layer order transfers against a stream without linking CUDA here.
+// Hooks that let a CUDA-aware layer order transfers against a stream without linking CUDA here. They are plain C
+// function pointers (the kernel library exports matching functions); words are 64-bit and live in pinned host
+// memory that the device can address.
 struct StreamHooks {
-    // enqueue "write 1 to *flag" on the stream (buffer is ready once it executes)
-    std::function<void(void* stream, std::atomic<uint32_t>* flag)> record_ready;
-    // make the stream wait until (*done & mask) == mask
-    std::function<void(void* stream, std::atomic<uint32_t>* done, uint32_t mask)> wait_done;
+    int (*alloc_words)(unsigned long long n_words, void** host, void** dev)                         = nullptr;
+    int (*free_words)(void* host)                                                                   = nullptr;
+    // enqueue on `stream`: *word = value (release at system scope): "the buffer is ready once this has run"
+    int (*record_value)(void* stream, void* dev_word, unsigned long long value)                     = nullptr;
+    // enqueue on `stream`: wait (bounded) until (*word & mask) == mask
+    int (*wait_mask)(void* stream, void* dev_word, unsigned long long mask, unsigned long long limit_ns) = nullptr;
+    bool installed() const { return alloc_words && free_words && record_value && wait_mask; }
 };
-
 inline StreamHooks& stream_hooks()
 {
     static StreamHooks hooks;
@@ -55,14 +60,7 @@ inline StreamHooks& stream_hooks()
 class HostSignal final: public DeviceSignal {
 public:
     void init() override { reset_all(); }
-    void record_gpu_ready() override
-    {
-        if (stream_ != nullptr && stream_hooks().record_ready) {
-            stream_hooks().record_ready(stream_, &gpu_ready_);
-            return;
-        }
-        gpu_ready_.store(1, std::memory_order_release);
-    }
+    void record_gpu_ready() override { gpu_ready_.store(1, std::memory_order_release); }
     bool     is_gpu_ready() const override { return gpu_ready_.load(std::memory_order_acquire) != 0; }
     uint32_t get_comm_done_mask() const override { return done_.load(std::memory_order_acquire); }
     void     set_comm_done(int lane) override
@@ -71,10 +69,7 @@ public:
         notify();
     }
     void bind_stream(void* stream) override { stream_ = stream; }
-    void wait_comm_done_on_stream(uint32_t mask) override
-    {
-        if (stream_ != nullptr && stream_hooks().wait_done) stream_hooks().wait_done(stream_, &done_, mask);
-    }
+    void wait_comm_done_on_stream(uint32_t) override {}  // no device-visible words: use MappedSignal for stream ordering
     bool wait_comm_done_cpu(uint32_t mask, int64_t timeout_ms = -1) override
     {
         auto satisfied = [&] { return forced_.load(std::memory_order_acquire) || (done_.load(std::memory_order_acquire) & mask) == mask; };
@@ -116,8 +111,119 @@ private:
     std::condition_variable cv_;
 };
 
-inline std::shared_ptr<DeviceSignal> create_signal(bool /*bypass*/ = true)
+// Pool of device-addressable words (two per signal), allocated from the hooks in chunks and recycled.
+class MappedWordPool {
+public:
+    struct Pair {
+        std::atomic<unsigned long long>* host = nullptr;  // [2]
+        void*                            dev  = nullptr;  // device address of host[0]
+    };
+    static MappedWordPool& get()
+    {
+        static MappedWordPool* p = new MappedWordPool();  // pinned memory is returned to the driver at process exit
+        return *p;
+    }
+    bool acquire(Pair& out)
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        if (free_.empty()) {
+            constexpr unsigned long long kPairs = 128;
+            void *h = nullptr, *d = nullptr;
+            if (!stream_hooks().installed() || stream_hooks().alloc_words(2 * kPairs, &h, &d) != 0) return false;
+            for (unsigned long long i = 0; i < kPairs; ++i)
+                free_.push_back(Pair{reinterpret_cast<std::atomic<unsigned long long>*>(h) + 2 * i, static_cast<char*>(d) + 16 * i});
+        }
+        out = free_.back();
+        free_.pop_back();
+        return true;
+    }
+    void release(const Pair& p)
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        free_.push_back(p);
+    }
+
+private:
+    std::mutex        mu_;
+    std::vector<Pair> free_;
+};
+
+// DeviceSignal whose two words the GPU can read and write: "ready" is set by a one-thread kernel in stream order
+// (so the transfer engine posts only after the producer kernels on that stream have finished), "done" can be waited
+// for by a bounded one-thread kernel in stream order (so consumer kernels queue behind the transfer without a host
+// round trip). The reference does this with cuStreamWriteValue32 / cuStreamWaitValue32
+// (dlslime/csrc/device/cuda/cuda_signal.h:40-118 in the reference); kernels give the wait a time limit.
+class MappedSignal final: public DeviceSignal {
+public:
+    explicit MappedSignal(const MappedWordPool::Pair& w): w_(w) { reset_all(); }
+    ~MappedSignal() override { MappedWordPool::get().release(w_); }
+    void init() override { reset_all(); }
+    void record_gpu_ready() override
+    {
+        if (stream_ != nullptr && stream_hooks().record_value(stream_, w_.dev, 1ull) == 0) return;
+        w_.host[0].store(1, std::memory_order_release);
+    }
+    bool     is_gpu_ready() const override { return w_.host[0].load(std::memory_order_acquire) != 0; }
+    uint32_t get_comm_done_mask() const override { return static_cast<uint32_t>(w_.host[1].load(std::memory_order_acquire)); }
+    void     set_comm_done(int lane) override
+    {
+        w_.host[1].fetch_or(1ull << lane, std::memory_order_acq_rel);
+        notify();
+    }
+    void bind_stream(void* stream) override { stream_ = stream; }
+    void wait_comm_done_on_stream(uint32_t mask) override
+    {
+        if (stream_ != nullptr) stream_hooks().wait_mask(stream_, static_cast<char*>(w_.dev) + 8, mask, 0ull);
+    }
+    bool wait_comm_done_cpu(uint32_t mask, int64_t timeout_ms = -1) override
+    {
+        auto satisfied = [&] { return forced_.load(std::memory_order_acquire) || (get_comm_done_mask() & mask) == mask; };
+        for (int i = 0; i < 2000; ++i) {
+            if (satisfied()) return true;
+            cpu_pause();
+        }
+        std::unique_lock<std::mutex> g(mu_);
+        if (timeout_ms < 0) {
+            cv_.wait(g, satisfied);
+            return true;
+        }
+        return cv_.wait_for(g, std::chrono::milliseconds(timeout_ms), satisfied);
+    }
+    void force_complete() override
+    {
+        forced_.store(true, std::memory_order_release);
+        // a kernel that waits for "done" in stream order must not be left to its time limit
+        w_.host[1].store(~0ull, std::memory_order_release);
+        notify();
+    }
+    void reset_all() override
+    {
+        w_.host[0].store(0, std::memory_order_relaxed);
+        w_.host[1].store(0, std::memory_order_relaxed);
+        forced_.store(false, std::memory_order_release);
+    }
+
+private:
+    void notify()
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        cv_.notify_all();
+    }
+    MappedWordPool::Pair    w_;
+    std::atomic<bool>       forced_{false};
+    void*                   stream_ = nullptr;
+    std::mutex              mu_;
+    std::condition_variable cv_;
+};
+
+// bypass = true: host-only signal (buffers are taken to be ready when the call is made). bypass = false: a
+// stream-ordered signal when a CUDA layer installed its hooks, else the host-only one.
+inline std::shared_ptr<DeviceSignal> create_signal(bool bypass = true)
 {
+    if (!bypass && stream_hooks().installed()) {
+        MappedWordPool::Pair w;
+        if (MappedWordPool::get().acquire(w)) return std::make_shared<MappedSignal>(w);
+    }
     auto s = std::make_shared<HostSignal>();
     s->init();
     return s;

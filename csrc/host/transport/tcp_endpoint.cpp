@@ -168,9 +168,13 @@ int TcpEndpoint::connect(const Json& remote_info)
 // ------------------------------------------------------------------------------------------------
 // submission
 // ------------------------------------------------------------------------------------------------
-std::shared_ptr<ReadWriteFuture> TcpEndpoint::submit_one_sided(OpCode opcode, const std::vector<assign_tuple_t>& assign, int32_t imm)
+std::shared_ptr<ReadWriteFuture> TcpEndpoint::submit_one_sided(OpCode opcode, const std::vector<assign_tuple_t>& assign, int32_t imm,
+                                                               void* stream)
 {
     auto st = make_op_state(1, opcode);
+    // with stream-ordered signals the sender thread posts only once the stream has reached this point
+    if (stream != nullptr && !engine_env().bypass_device_signal) st->signal->bind_stream(stream);
+    st->signal->record_gpu_ready();
     uint64_t bytes = 0;
     for (const auto& a : assign) bytes += std::get<4>(a);
     st->bytes   = bytes;
@@ -195,17 +199,17 @@ std::shared_ptr<ReadWriteFuture> TcpEndpoint::submit_one_sided(OpCode opcode, co
     return fut;
 }
 
-std::shared_ptr<ReadWriteFuture> TcpEndpoint::read(const std::vector<assign_tuple_t>& assign, void*)
+std::shared_ptr<ReadWriteFuture> TcpEndpoint::read(const std::vector<assign_tuple_t>& assign, void* stream)
 {
-    return submit_one_sided(OpCode::READ, assign, 0);
+    return submit_one_sided(OpCode::READ, assign, 0, stream);
 }
-std::shared_ptr<ReadWriteFuture> TcpEndpoint::write(const std::vector<assign_tuple_t>& assign, void*)
+std::shared_ptr<ReadWriteFuture> TcpEndpoint::write(const std::vector<assign_tuple_t>& assign, void* stream)
 {
-    return submit_one_sided(OpCode::WRITE, assign, 0);
+    return submit_one_sided(OpCode::WRITE, assign, 0, stream);
 }
-std::shared_ptr<ReadWriteFuture> TcpEndpoint::write_with_imm(const std::vector<assign_tuple_t>& assign, int32_t imm, void*)
+std::shared_ptr<ReadWriteFuture> TcpEndpoint::write_with_imm(const std::vector<assign_tuple_t>& assign, int32_t imm, void* stream)
 {
-    return submit_one_sided(OpCode::WRITE_WITH_IMM, assign, imm);
+    return submit_one_sided(OpCode::WRITE_WITH_IMM, assign, imm, stream);
 }
 
 std::shared_ptr<ImmRecvFuture> TcpEndpoint::imm_recv(void*)
@@ -233,10 +237,12 @@ std::shared_ptr<ImmRecvFuture> TcpEndpoint::imm_recv(void*)
     return fut;
 }
 
-std::shared_ptr<SendFuture> TcpEndpoint::send(const chunk_tuple_t& chunk, void*)
+std::shared_ptr<SendFuture> TcpEndpoint::send(const chunk_tuple_t& chunk, void* stream)
 {
     auto st  = make_op_state(1, OpCode::SEND);
     auto fut = std::make_shared<SendFuture>(st);
+    if (stream != nullptr && !engine_env().bypass_device_signal) st->signal->bind_stream(stream);
+    st->signal->record_gpu_ready();
     if (!connected_.load() || stopping_.load()) {
         complete(st, FAILED);
         return fut;
@@ -370,6 +376,12 @@ void TcpEndpoint::sender_loop()
             if (stopping_.load()) return;
             op = std::move(submit_q_.front());
             submit_q_.pop_front();
+        }
+        // head of line: operations leave in submission order, so a buffer that is not ready yet holds back what follows
+        while (!op.state->signal->is_gpu_ready() && !stopping_.load()) std::this_thread::sleep_for(std::chrono::microseconds(20));
+        if (stopping_.load()) {
+            complete(op.state, FAILED);
+            return;
         }
         if (op.opcode == OpCode::READ && op.assign.empty()) {
             complete(op.state, SUCCESS);

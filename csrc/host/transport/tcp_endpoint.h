@@ -77,7 +77,7 @@ private:
         std::shared_ptr<EndpointOpState> state;
     };
 
-    std::shared_ptr<ReadWriteFuture> submit_one_sided(OpCode op, const std::vector<assign_tuple_t>& assign, int32_t imm);
+    std::shared_ptr<ReadWriteFuture> submit_one_sided(OpCode op, const std::vector<assign_tuple_t>& assign, int32_t imm, void* stream);
     void sender_loop();
     void receiver_loop();
     void acceptor_loop();

@@ -30,6 +30,8 @@ int slime_signal_flag_kernel(void* flag, unsigned long long value, int add, void
 // ---- symmetric heap (symm_heap.cu) ----------------------------------------
 // cudaMalloc-backed region with a CUDA IPC handle (64 bytes) that other
 // processes on the node can map. Returns the device pointer in *ptr.
+int slime_hook_record_value(void* stream, void* dev_word, unsigned long long value);
+int slime_hook_wait_mask(void* stream, void* dev_word, unsigned long long mask, unsigned long long limit_ns);
 int slime_symm_alloc(unsigned long long bytes, void** ptr, unsigned char* ipc_handle_out64);
 int slime_symm_free(void* ptr);
 int slime_ipc_get_handle(const void* ptr, unsigned char* ipc_handle_out64, unsigned long long* offset_out,

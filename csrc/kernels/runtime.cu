@@ -16,6 +16,16 @@ __global__ void wait_flag_kernel(const unsigned long long* flag, unsigned long l
     wait_flag_ge(flag, target, st, 100, 0, limit_ns ? limit_ns : kDefaultWaitNs);
 }
 
+__global__ void wait_mask_kernel(const unsigned long long* word, unsigned long long mask, unsigned long long limit_ns)
+{
+    const unsigned long long lim = limit_ns ? limit_ns : kDefaultWaitNs;
+    const unsigned long long t0  = globaltimer_ns();
+    while ((ld_acquire_sys(word) & mask) != mask) {
+        if (globaltimer_ns() - t0 > lim) return;  // bounded: the host sees the operation's own status
+        __nanosleep(100);
+    }
+}
+
 __global__ void signal_flag_kernel(unsigned long long* flag, unsigned long long value, int add)
 {
     if (add)
@@ -88,6 +98,22 @@ int slime_wait_flag_kernel(const void* flag, unsigned long long target, unsigned
 int slime_signal_flag_kernel(void* flag, unsigned long long value, int add, void* stream)
 {
     signal_flag_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned long long*>(flag), value, add);
+    SLIME_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+// Stream hooks of the host runtime's stream-ordered signals (see csrc/host/engine/signal.h): word allocation is
+// slime_host_flags_alloc / slime_host_flags_free above.
+int slime_hook_record_value(void* stream, void* dev_word, unsigned long long value)
+{
+    signal_flag_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned long long*>(dev_word), value, 0);
+    SLIME_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+int slime_hook_wait_mask(void* stream, void* dev_word, unsigned long long mask, unsigned long long limit_ns)
+{
+    wait_mask_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned long long*>(dev_word), mask, limit_ns);
     SLIME_CUDA_OK(cudaGetLastError());
     return 0;
 }

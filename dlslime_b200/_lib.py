@@ -81,7 +81,20 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
             fn.argtypes = argtypes
             fn.restype = c_int
         _LIB = lib
+        _install_stream_hooks(lib)
     return _LIB
+
+
+def _install_stream_hooks(lib) -> None:
+    """Give the host runtime the addresses of the four functions behind its stream-ordered signals."""
+    try:
+        from . import _slime_c
+
+        addr = lambda name: ctypes.cast(getattr(lib, name), ctypes.c_void_p).value  # noqa: E731
+        _slime_c.install_stream_hooks(addr("slime_host_flags_alloc"), addr("slime_host_flags_free"),
+                                      addr("slime_hook_record_value"), addr("slime_hook_wait_mask"))
+    except Exception:  # the host module is optional for pure kernel users
+        pass
 
 
 def declare(name: str, argtypes) -> None:

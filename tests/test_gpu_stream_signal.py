@@ -1,0 +1,49 @@
+"""Stream-ordered signals with the real hooks: a transfer submitted with a CUDA stream starts only after the kernels
+already queued on that stream, and a stream can wait on the device for a transfer."""
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_transfer_is_ordered_after_the_stream_and_before_its_waiters():
+    body = textwrap.dedent("""
+        import ctypes, time, torch
+        from dlslime_b200 import _lib, _slime_c as C
+        _lib.load()
+        assert C.stream_hooks_installed()
+        n = 1 << 20
+        src = torch.zeros(n, dtype=torch.uint8).pin_memory()
+        dst = torch.zeros(n, dtype=torch.uint8).pin_memory()
+        dev = torch.full((n,), 7, dtype=torch.uint8, device="cuda")
+        a, b = C.TcpEndpoint(), C.TcpEndpoint()
+        a.register_memory_region("src", src.data_ptr(), 0, n)
+        b.register_memory_region("dst", dst.data_ptr(), 0, n)
+        ia, ib = a.endpoint_info(), b.endpoint_info()
+        assert a.connect(ib) == 0 and b.connect(ia) == 0
+        for name, info in ib["mr_info"].items():
+            a.register_remote_memory_region(name, info)
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            torch.cuda._sleep(400_000_000)            # ~0.2 s of device time in front of the producer copy
+            src.copy_(dev, non_blocking=True)         # the producer: fills the staging buffer on the stream
+            f = a.write([(a.get_mr_handle("src"), a.get_remote_mr_handle("dst"), 0, 0, n)], stream=s.cuda_stream)
+            assert f.wait(0.02) == 402, "the transfer did not wait for the stream"
+            f.wait_on_stream()                        # consumers queued on the stream see the transferred bytes
+            back = torch.empty(n, dtype=torch.uint8, device="cuda")
+            back.copy_(dst, non_blocking=True)
+        assert f.wait(20) == 0
+        s.synchronize()
+        assert bool((dst == 7).all()), "the transfer read the staging buffer before the producer had filled it"
+        assert bool((back == 7).all()), "the consumer on the stream ran before the transfer had completed"
+        a.shutdown(); b.shutdown()
+        print("ok")
+    """)
+    env = dict(os.environ, PYTHONPATH=REPO, SLIME_BYPASS_DEVICE_SIGNAL="0")
+    r = subprocess.run([sys.executable, "-c", body], env=env, capture_output=True, text=True, timeout=200)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
