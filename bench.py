@@ -189,6 +189,11 @@ def run_ours(args, rank, world, local):
     T = T_MODE[args.mode]
     cfg = MoEConfig(num_experts=E, topk=TOPK, hidden=HIDDEN, intermediate=INTER)
     layer = ExpertParallelMoE(cfg, max_tokens=T, seed=0)
+    tbo = None
+    if args.overlap and args.mode == "normal":
+        from dlslime_b200.models.moe import TwoBatchOverlapMoE
+
+        tbo = TwoBatchOverlapMoE(cfg, max_tokens=T, weights=(layer.w_gate_up, layer.w_down))
     n_in = min(4, max(1, args.steps))
     host_x, host_lg = make_inputs(T, rank, n_in)
     dev_x = [h.cuda() for h in host_x]
@@ -201,9 +206,11 @@ def run_ours(args, rank, world, local):
     # Decode-size steps are launch-bound: the whole layer is replayed from one CUDA graph on fixed buffers.
     graph = layer.capture(x_stage, lg_stage, out) if args.mode == "ll" and not args.no_graph else None
 
+    fwd = tbo.forward if tbo is not None else layer.forward
+
     def run_layer(x, lg):
         if graph is None:
-            layer.forward(x, lg, out=out)
+            fwd(x, lg, out=out)
         else:
             if x is not x_stage:
                 x_stage.copy_(x, non_blocking=True)
@@ -251,7 +258,7 @@ def run_ours(args, rank, world, local):
                 self.primed = True
             main.wait_event(self.in_ready[b])
             main.wait_event(self.out_done[b])  # the output slot was copied out two steps ago
-            layer.forward(self.xs[b], self.lgs[b], out=self.outs[b])
+            fwd(self.xs[b], self.lgs[b], out=self.outs[b])
             self.computed[b].record(main)
             self.prefetch(i + 1)
             with torch.cuda.stream(self.s_out):
@@ -291,6 +298,8 @@ def run_ours(args, rank, world, local):
         clocks = sampler.stop() if rank == 0 else None
         ms = ev0.elapsed_time(ev1) / args.steps
         layer.buf.status.check()
+        if tbo is not None:
+            tbo.check()
         return max_over_ranks(ms, world), clocks
 
     ms_dev, clocks = timed(step_device)
@@ -324,7 +333,7 @@ def run_ours(args, rank, world, local):
     return {
         "ms_dev": ms_dev, "ms_e2e": ms_e2e, "ms_e2e_serial": ms_e2e_serial, "e2e_pipelined": pipe is not None, "clocks": clocks, "breakdown_us": breakdown, "T": T,
         "h2d": host_x[0].numel() * 2 + host_lg[0].numel() * 4, "d2h": host_out.numel() * 2,
-        "launches": 6 * args.steps, "cuda_graph": graph is not None, "weights_gb": weights_gb, "nvlink_bytes_per_rank": nvlink_bytes,
+        "launches": (12 if tbo is not None else 6) * args.steps, "cuda_graph": graph is not None, "overlap": tbo is not None, "weights_gb": weights_gb, "nvlink_bytes_per_rank": nvlink_bytes,
     }
 
 
@@ -347,6 +356,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--mode", choices=["ll", "normal"], default="normal")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--overlap", action="store_true",
+                    help="normal mode: split the step into two half-batches on two streams (communication of one half under the GEMMs of the other)")
     ap.add_argument("--no-graph", action="store_true", help="ll mode: launch the kernels one by one instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -374,7 +385,7 @@ def main():
         "nvlink_gbs_per_rank": round(res["nvlink_bytes_per_rank"] / (res["ms_dev"] * 1e-3) / 1e9, 2),
         "config": {
             "model": "DeepSeek-V3-shaped MoE layer: 256 experts, top-8, hidden 7168, intermediate 2048",
-            "mode": args.mode, "cuda_graph": bool(res.get("cuda_graph")), "tokens_per_rank": T, "global_batch": world * T, "seq_len": 1,
+            "mode": args.mode, "cuda_graph": bool(res.get("cuda_graph")), "two_batch_overlap": bool(res.get("overlap")), "tokens_per_rank": T, "global_batch": world * T, "seq_len": 1,
             "parallelism": f"ep{world}", "experts_per_rank": E // world,
             "l2": f"inputs larger than L2: {res['weights_gb']:.1f} GB of expert weights per rank are streamed every step",
         },

@@ -56,13 +56,16 @@ class ExpertParallelMoE:
     """One rank's shard of the MoE layer."""
 
     def __init__(self, cfg: MoEConfig, max_tokens: int, *, group=None, seed: int = 0, buffer: EpBuffer | None = None,
-                 recv_cap: int | None = None):
+                 recv_cap: int | None = None, weights=None, recv_grid_rows: int | None = None):
         self.cfg = cfg
         self.buf = buffer or EpBuffer(cfg.num_experts, cfg.topk, cfg.hidden, max_tokens, group=group, recv_cap=recv_cap)
         self.rank, self.world = self.buf.rank, self.buf.world
         dev = self.buf.device
         epr = self.buf.experts_per_rank
-        self.w_gate_up, self.w_down = init_expert_weights(cfg, range(self.rank * epr, (self.rank + 1) * epr), dev, seed)
+        if weights is None:
+            weights = init_expert_weights(cfg, range(self.rank * epr, (self.rank + 1) * epr), dev, seed)
+        self.w_gate_up, self.w_down = weights
+        self.recv_grid_rows = recv_grid_rows  # sizes the grid of the receive kernel (None: by the expected row count)
         cap = self.buf.recv_cap
         self.xd = torch.empty((cap, cfg.hidden), dtype=torch.bfloat16, device=dev)
         self.h = torch.empty((cap, cfg.intermediate), dtype=torch.bfloat16, device=dev)
@@ -78,7 +81,8 @@ class ExpertParallelMoE:
 
     def step_recv(self, T, epoch):
         c = self.cfg
-        self.buf.recv_dequant(self.xd, epoch, expected_rows=min(self.buf.recv_cap, max(1, 2 * T * c.topk)))
+        rows = self.recv_grid_rows or min(self.buf.recv_cap, max(1, 2 * T * c.topk))
+        self.buf.recv_dequant(self.xd, epoch, expected_rows=rows)
 
     def step_gate_up(self):
         gemm.grouped_gemm_bf16(self.xd, self.w_gate_up, self.buf.group_offsets, out=self.h, epilogue=gemm.EPI_SWIGLU)
@@ -128,6 +132,64 @@ class ExpertParallelMoE:
         with torch.cuda.graph(graph):
             self.forward(x, logits, out)
         return graph
+
+
+class TwoBatchOverlapMoE:
+    """The same layer with the step split into two half-batches on two streams, so that the communication phases
+    of one half (dispatch, receive, combine: NVLink- and HBM-bound) run while the tensor cores work on the other
+    half's expert GEMMs.
+
+    The halves are two :class:`ExpertParallelMoE` instances that share the expert weights and own their
+    symmetric buffers and step counters, so no protocol state is shared and the two chains never wait on each other;
+    every kernel still waits only on kernels that the other RANKS issued earlier in the same chain. The spinning
+    receive kernel is launched with a grid that leaves half of every SM's thread slots free, so kernels of the
+    other chain can always start beside it.
+    """
+
+    def __init__(self, cfg: MoEConfig, max_tokens: int, *, group=None, seed: int = 0, weights=None):
+        half = (max_tokens + 1) // 2
+        self.cfg, self.max_tokens, self.half = cfg, max_tokens, half
+        self.a = ExpertParallelMoE(cfg, half, group=group, seed=seed, weights=weights, recv_grid_rows=160)
+        self.b = ExpertParallelMoE(cfg, half, group=group, weights=(self.a.w_gate_up, self.a.w_down), recv_grid_rows=160)
+        self.rank, self.world = self.a.rank, self.a.world
+        self.buf = self.a.buf  # status page and geometry for callers that look at the single-batch layer's buffer
+        self.w_gate_up, self.w_down = self.a.w_gate_up, self.a.w_down
+        self.sa, self.sb = torch.cuda.Stream(), torch.cuda.Stream()
+        self._fork, self._ja, self._jb = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty_like(x)
+        t0 = (T + 1) // 2
+        parts = [(self.a, self.sa, slice(0, t0)), (self.b, self.sb, slice(t0, T))]
+        cur = torch.cuda.current_stream()
+        self._fork.record(cur)
+        for _, s, _ in parts:
+            s.wait_event(self._fork)
+        # issue order = the order in which every rank's kernels appear: both dispatches first, then the expert phases
+        for layer, s, sl in parts:
+            with torch.cuda.stream(s):
+                n = sl.stop - sl.start
+                layer.step_route(logits[sl], n, None)
+                layer.step_dispatch(x[sl], None)
+        for layer, s, sl in parts:
+            with torch.cuda.stream(s):
+                layer.step_experts(sl.stop - sl.start, None)
+        for layer, s, sl in parts:
+            with torch.cuda.stream(s):
+                layer.step_combine(out[sl], sl.stop - sl.start, None)
+        self._ja.record(self.sa)
+        self._jb.record(self.sb)
+        cur.wait_event(self._ja)
+        cur.wait_event(self._jb)
+        return out
+
+    __call__ = forward
+
+    def check(self) -> None:
+        self.a.buf.status.check()
+        self.b.buf.status.check()
 
 
 def emulated_forward(layers: list[ExpertParallelMoE], xs, logits):

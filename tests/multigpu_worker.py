@@ -114,6 +114,28 @@ def check_moe(rank, world):
     dist.barrier()
 
 
+def check_moe_tbo(rank, world):
+    """Two half-batches on two streams: same results as the fp32 oracle, for token counts that split unevenly."""
+    from dlslime_b200.models.moe import MoEConfig, TwoBatchOverlapMoE, init_expert_weights, ref_moe_forward
+
+    cfg = MoEConfig(num_experts=32, topk=4, hidden=1024, intermediate=256)
+    layer = TwoBatchOverlapMoE(cfg, max_tokens=256, seed=7)
+    w13, w2 = init_expert_weights(cfg, range(cfg.num_experts), "cuda", seed=7)
+    for step in range(4):
+        T = [200, 1, 256, 33, 64, 128, 17, 255][(rank + step) % 8]
+        gen = torch.Generator(device="cuda").manual_seed(2000 * step + rank)
+        x = torch.randn((T, cfg.hidden), generator=gen, device="cuda").to(torch.bfloat16)
+        lg = torch.randn((T, cfg.num_experts), generator=gen, device="cuda")
+        out = layer(x, lg)
+        torch.cuda.synchronize()
+        layer.check()
+        ref, idx, w = ref_moe_forward(cfg, x, lg, w13, w2)
+        err = (out.float() - ref.float()).abs()
+        tol = ref.float().abs() * 2 ** -6 + ref.float().abs().mean() * 2 ** -5
+        assert (err <= tol).all(), f"tbo rank {rank} step {step}: max err {err.max().item()}"
+    dist.barrier()
+
+
 def check_ag_gemm(rank, world):
     from dlslime_b200.ops.ag_gemm import AllGatherGemm
 
@@ -200,7 +222,7 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    which = sys.argv[1:] or ["endpoint", "allgather", "moe", "ag_gemm", "ag_gemm_fp8", "kv"]
+    which = sys.argv[1:] or ["endpoint", "allgather", "moe", "moe_tbo", "ag_gemm", "ag_gemm_fp8", "kv"]
     for name in which:
         globals()[f"check_{name}"](rank, world)
         if rank == 0:

@@ -99,3 +99,24 @@ def test_wait_times_out_instead_of_hanging():
     with pytest.raises(KernelTimeout):
         default_status().check()
     default_status().check()  # the page is cleared after reporting
+
+
+@pytest.mark.parametrize("tokens", [1, 2, 77, 256])
+def test_two_batch_overlap_single_rank(tokens):
+    """The two-stream, two-half-batch form of the layer against the fp32 oracle on one rank."""
+    from dlslime_b200.models.moe import MoEConfig, TwoBatchOverlapMoE, init_expert_weights, ref_moe_forward
+
+    cfg = MoEConfig(num_experts=16, topk=4, hidden=1024, intermediate=256)
+    layer = TwoBatchOverlapMoE(cfg, max_tokens=256, seed=3)
+    w13, w2 = init_expert_weights(cfg, range(cfg.num_experts), "cuda", seed=3)
+    for step in range(2):
+        gen = torch.Generator(device="cuda").manual_seed(31 * tokens + step)
+        x = torch.randn((tokens, cfg.hidden), generator=gen, device="cuda").to(torch.bfloat16)
+        lg = torch.randn((tokens, cfg.num_experts), generator=gen, device="cuda")
+        out = layer(x, lg)
+        torch.cuda.synchronize()
+        layer.check()
+        ref, _, _ = ref_moe_forward(cfg, x, lg, w13, w2)
+        err = (out.float() - ref.float()).abs()
+        tol = ref.float().abs() * 2 ** -6 + ref.float().abs().mean() * 2 ** -5
+        assert (err <= tol).all(), f"step {step}: max err {err.max().item()}"
