@@ -9,14 +9,17 @@
 // loop. Two-level accumulation: a K block (128 bytes = one swizzle row = one pipeline stage) is FOUR
 // tcgen05.mma.kind::f8f6f4 (K = 32 each) into a fresh TMEM partial; eight "promotion" warps read the
 // partial (tcgen05.ld), multiply by sa * sb and add into fp32 registers, while the tensor core already
-// fills the other partial. The promotion is the critical path: a TMEM read costs a few hundred cycles and a
-// thread's reads of one partial are dependent steps, so the tile is 128 x 192 and TWELVE warps share a
-// partial: one thread owns one row and 64 columns (two 32-column reads and 64 FMAs per K block, 64
-// accumulators), which keeps 14 warps under the 128-register limit of four warps per scheduler partition.
-// (Measured on 8192^3 with 128 x 256 tiles and eight warps of 128 columns each: 0.62 ms, the tensor pipe
-// 39 % busy; 64-column reads spilled and halved the speed; overlapping two reads was 5 % slower.)
+// fills the other partial (two partials of 128 x 256 fp32 = all 512 TMEM columns). One thread owns one row and
+// 128 of the 256 columns (four 32-column reads and 128 FMAs per K block, 128 accumulators); at the end of the tile
+// it converts and stores its 256 contiguous output bytes.
 //
-// Roles per CTA (448 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps 2..13
+// The promotion is the limit, and it is the volume read back from TMEM, not the latency of a read: the tensor
+// pipe is 39 % busy (8192^3 in 0.62 ms = 1769 TFLOP/s). Measured alternatives, all slower: 64-column reads (spill at
+// the 168-register cap of ten warps: 1.20 ms), two overlapped 32-column reads (0.65 ms), 128 x 192 tiles with twelve
+// warps of 64 columns each, no spills (0.69 ms). Doing the scaling in the tensor core (kind::mxf8f6f4 with UE8M0
+// scale factors in TMEM) is what removes this read; it needs power-of-two scales.
+//
+// Roles per CTA (320 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps 2..9
 // promotion + epilogue (warp w reads TMEM lane quadrant w % 4, column slice (w - 2) / 4). Every wait is
 // bounded and reports through the status page, as in the bf16 kernels. The all-gather roles of
 // gemm_tc.cuh carry over: shard-major tiles, own shard read in place, tiles gated on arrival counters, one
@@ -29,10 +32,10 @@ namespace slime {
 namespace gemm {
 
 constexpr int kF8BK       = 128;  // fp8 elements (= bytes) per K block
-constexpr int kF8BN         = 192;  // tile width: three 64-column slices per TMEM lane quadrant
-constexpr int kF8Cols       = 64;   // columns per promotion thread
+constexpr int kF8BN         = 256;  // tile width: two 128-column slices per TMEM lane quadrant
+constexpr int kF8Cols       = 128;  // columns per promotion thread
 constexpr int kF8PartStride = 256;  // TMEM columns between the two partials
-constexpr int kF8Stages     = 5;
+constexpr int kF8Stages     = 4;
 constexpr int kF8PromoWarps = 4 * (kF8BN / kF8Cols);
 constexpr int kF8Threads    = (2 + kF8PromoWarps) * 32;
 constexpr int kF8PromoThreads = kF8PromoWarps * 32;
