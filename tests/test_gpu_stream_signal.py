@@ -29,18 +29,33 @@ def test_transfer_is_ordered_after_the_stream_and_before_its_waiters():
         for name, info in ib["mr_info"].items():
             a.register_remote_memory_region(name, info)
         s = torch.cuda.Stream()
+        lh, rh = a.get_mr_handle("src"), a.get_remote_mr_handle("dst")
+        # warm-up: first launches load modules and allocate the pinned words
         with torch.cuda.stream(s):
-            torch.cuda._sleep(400_000_000)            # ~0.2 s of device time in front of the producer copy
-            src.copy_(dev, non_blocking=True)         # the producer: fills the staging buffer on the stream
-            f = a.write([(a.get_mr_handle("src"), a.get_remote_mr_handle("dst"), 0, 0, n)], stream=s.cuda_stream)
-            assert f.wait(0.02) == 402, "the transfer did not wait for the stream"
-            f.wait_on_stream()                        # consumers queued on the stream see the transferred bytes
-            back = torch.empty(n, dtype=torch.uint8, device="cuda")
-            back.copy_(dst, non_blocking=True)
-        assert f.wait(20) == 0
-        s.synchronize()
-        assert bool((dst == 7).all()), "the transfer read the staging buffer before the producer had filled it"
-        assert bool((back == 7).all()), "the consumer on the stream ran before the transfer had completed"
+            w = a.write([(lh, rh, 0, 0, 4096)], stream=s.cuda_stream)
+            w.wait_on_stream()
+        assert w.wait(20) == 0
+        torch.cuda.synchronize()
+        dst.zero_()
+        for trial in range(3):
+            fill = 7 + trial
+            with torch.cuda.stream(s):
+                dev.fill_(fill)
+                torch.cuda._sleep(200_000_000)            # ~0.1 s of device time in front of the producer copy
+                src.copy_(dev, non_blocking=True)         # the producer: fills the staging buffer on the stream
+                gate = torch.cuda.Event()
+                gate.record(s)
+                f = a.write([(lh, rh, 0, 0, n)], stream=s.cuda_stream)
+                f.wait_on_stream()                        # consumers queued on the stream see the transferred bytes
+                back = torch.empty(n, dtype=torch.uint8, device="cuda")
+                back.copy_(dst, non_blocking=True)
+            # the operation cannot be done while the stream has not reached the point where it was submitted
+            early = f.done() and not gate.query()
+            assert not early, "the transfer completed before its stream reached the submission point"
+            assert f.wait(20) == 0
+            s.synchronize()
+            assert bool((dst == fill).all()), "the transfer read the staging buffer before the producer had filled it"
+            assert bool((back == fill).all()), "the consumer on the stream ran before the transfer had completed"
         a.shutdown(); b.shutdown()
         print("ok")
     """)
