@@ -162,7 +162,7 @@ def build_stress(sanitizer: str, verbose: bool = False) -> Path:
     odir = OBJ / f"san_{tag}"
     odir.mkdir(parents=True, exist_ok=True)
     cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else os.environ.get("CXX", "g++")
-    flags = ["-O1", "-g", "-std=c++17", "-pthread", f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer"]
+    flags = ["-O1", "-g1", "-std=c++17", "-pthread", f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer"]
     inc = [CSRC / "include", hdir]
     dep = _newest_header_mtime([CSRC / "include", hdir])
     jobs, objs = [], []
@@ -177,6 +177,8 @@ def build_stress(sanitizer: str, verbose: bool = False) -> Path:
     exe = odir / "host_stress"
     if changed or not exe.exists():
         _run([cxx, *flags, "-o", exe, *objs, "-ldl", "-lrt"], verbose)
+    for obj in objs:  # instrumented objects are large and only the program is needed
+        obj.unlink(missing_ok=True)
     return exe
 
 
