@@ -129,9 +129,11 @@ __global__ void __launch_bounds__(kThreads) p2p_scatter_gather_kernel(CopyArgs a
 // The same batch through the bulk-copy engine, for batches whose addresses and lengths are all multiples of 16 bytes.
 // One thread per CTA drives a ring of shared-memory buffers: a 64 KiB unit is fetched with up to eight 8 KiB
 // global -> shared bulk loads that are all in flight together (loads from peer memory included), and every chunk
-// is handed on with a shared -> global bulk store as soon as it has landed. The engine keeps tens of KB per CTA
-// in flight, which is what a read from peer memory needs to cover the NVLink round trip; 16-byte loads issued by
-// threads stall at a few hundred GB/s.
+// is handed on with a shared -> global bulk store as soon as it has landed. Measured between two GPUs it moves
+// data exactly as fast as the 256-thread load/store kernel (contiguous 768 / 707 GB/s read / write, 4096 scattered
+// 64 KiB pieces 264 / 668 GB/s): the scattered read is limited by the remote side (every piece touches another
+// page of a 4 GiB region), not by how the copy is issued. What the engine buys is occupancy: one warp per CTA
+// instead of eight, so a transfer that runs beside compute kernels takes almost no issue slots from them.
 constexpr int kBulkBufs  = 8;
 constexpr int kBulkChunk = 8192;
 

@@ -42,7 +42,7 @@ def check_endpoint(rank, world):
         torch.cuda.synchronize()
         assert torch.equal(buf, expect), "endpoint read mismatch"
         # aligned batch (the bulk-copy-engine path): 40 scattered 64 KiB pieces, one 200 KiB piece, one 48-byte piece
-        segs = [("buffer", "buffer", half + (2 << 20) + 65536 * ((7 * i) % 40), (2 << 20) + 65536 * i, 65536) for i in range(20)]
+        segs = [("buffer", "buffer", half + (1 << 20) + 65536 * ((7 * i) % 40), (2 << 20) + 65536 * i, 65536) for i in range(20)]
         segs += [("buffer", "buffer", half + 4096, 4096, 200 << 10), ("buffer", "buffer", half + 16, 1 << 19, 48)]
         assert ep.read(segs).wait() == 0
         for _, _, roff, loff, ln in segs:
@@ -62,7 +62,7 @@ def check_endpoint(rank, world):
         # what the peer wrote is ITS buffer after its own reads; recompute that
         psegs = [(half + 1000 * i + (i % 3), 5000 * i + (i % 5), 777 + 16 * i) for i in range(200)]
         psegs.append((half + (1 << 20), 1 << 20, 1 << 20))
-        psegs += [(half + (2 << 20) + 65536 * ((7 * i) % 40), (2 << 20) + 65536 * i, 65536) for i in range(20)]
+        psegs += [(half + (1 << 20) + 65536 * ((7 * i) % 40), (2 << 20) + 65536 * i, 65536) for i in range(20)]
         psegs += [(half + 4096, 4096, 200 << 10), (half + 16, 1 << 19, 48)]
         pbuf = peer_orig.clone()
         for roff, loff, ln in psegs:
