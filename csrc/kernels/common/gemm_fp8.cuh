@@ -124,7 +124,7 @@ __device__ __forceinline__ bool ag_push_bulk_f8(const F8Args& f, uint8_t* bufs, 
         uint8_t*  sdst = reinterpret_cast<uint8_t*>(f.ag_dst_scales[p]) + (static_cast<unsigned long long>(a.ag_rank) * slices + sl) * sslice;
         for (int c = 0; c < chunks; ++c) {
             const int b = n_st % nb;
-            if (!mbar_wait(&bars[b], (n_st / nb) & 1, st, 12, b, lim)) return false;
+            if (!mbar_wait_relaxed(&bars[b], (n_st / nb) & 1, st, 12, b, lim)) return false;
             uint32_t bytes;
             chunk_src(sl, c, bytes);
             uint8_t* d = c < pchunks ? dst + static_cast<unsigned long long>(c) * kAgChunkBytes

@@ -255,7 +255,7 @@ __device__ __forceinline__ bool ag_push_bulk(const Args& a, uint8_t* bufs, uint6
         uint8_t*  dst = reinterpret_cast<uint8_t*>(a.ag_dst[p]) + (static_cast<unsigned long long>(a.ag_rank) * slices + sl) * slice_bytes;
         for (int c = 0; c < chunks; ++c) {
             const int b = n_st % nb;
-            if (!mbar_wait(&bars[b], (n_st / nb) & 1, st, 12, b, lim)) return false;
+            if (!mbar_wait_relaxed(&bars[b], (n_st / nb) & 1, st, 12, b, lim)) return false;
             bulk_store_s2g(dst + static_cast<unsigned long long>(c) * kAgChunkBytes, bufs + b * kAgChunkBytes, chunk_bytes(c));
             tma_store_commit();
             ++n_st;

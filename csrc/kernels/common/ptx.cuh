@@ -250,6 +250,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Kernel
     return true;
 }
 
+// The same wait for a thread that is not on the critical path (a copy warp beside compute warps): it backs off
+// between polls so that its spinning does not take issue slots from the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, KernelStatus* st, unsigned int where,
+                                                  unsigned int aux, unsigned long long limit_ns = kDefaultWaitNs)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned int             it = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(128);
+        if ((++it & 0x3f) == 0 && globaltimer_ns() - t0 > limit_ns) {
+            report_status(st, K_TIMEOUT, where, aux, parity, it);
+            return false;
+        }
+    }
+    return true;
+}
+
 // ---------------------------------------------------------------------------
 // TMA (tiled, 2D). Loads complete on an mbarrier; stores use bulk groups.
 // The x coordinate times the element size must be a multiple of 16 bytes.

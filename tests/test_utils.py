@@ -1,0 +1,55 @@
+"""Trace merging, NVTX ranges without CUDA, and the DRAM pool's back-pressure."""
+import threading
+import time
+
+import pytest
+
+from dlslime_b200.ops.offload import DRAMMemoryPool
+from dlslime_b200.utils.nvtx import nvtx_annotate, nvtx_range
+from dlslime_b200.utils.profiler import dist_print, merge_traces
+
+
+def test_merge_traces_remaps_pids_per_rank_and_labels_processes():
+    t0 = {"traceEvents": [{"ph": "M", "name": "process_name", "pid": 7, "args": {"name": "python"}},
+                          {"ph": "X", "pid": 7, "tid": 1, "name": "kernel_a", "ts": 1, "dur": 2}]}
+    t1 = {"traceEvents": [{"ph": "X", "pid": 7, "tid": 1, "name": "kernel_b", "ts": 1, "dur": 2},
+                          {"ph": "X", "pid": "gpu0", "tid": 3, "name": "kernel_c", "ts": 3, "dur": 1}]}
+    m = merge_traces([t0, t1], names=["prefill", "decode"])
+    ev = m["traceEvents"]
+    by_name = {e["name"]: e for e in ev if e.get("ph") == "X"}
+    assert by_name["kernel_a"]["pid"] == 7 and by_name["kernel_b"]["pid"] == 1_000_007
+    assert 1_000_000 <= by_name["kernel_c"]["pid"] < 2_000_000
+    labels = {e["pid"]: e["args"]["name"] for e in ev if e.get("ph") == "M" and e["name"] == "process_name"}
+    assert labels[7] == "prefill: python" and labels[1_000_007] == "decode" and labels[by_name["kernel_c"]["pid"]] == "decode"
+    # inputs are not modified
+    assert t1["traceEvents"][0]["pid"] == 7
+
+
+def test_nvtx_helpers_are_noops_without_cuda(capsys):
+    calls = []
+
+    @nvtx_annotate("labelled")
+    def f(x):
+        calls.append(x)
+        return x + 1
+
+    with nvtx_range("outer"):
+        assert f(1) == 2
+    assert calls == [1] and f.__name__ == "f"
+    dist_print("hello", ranks=None)
+    assert "[rank 0] hello" in capsys.readouterr().out
+
+
+def test_dram_pool_blocks_when_full_and_wakes_on_release():
+    pool = DRAMMemoryPool(slot_bytes=1024, num_slots=2)
+    a, b = pool.acquire(), pool.acquire()
+    assert {a, b} == {0, 1} and pool.slot(a).numel() == 1024
+    with pytest.raises(TimeoutError):
+        pool.acquire(timeout=0.05)
+    got = []
+    t = threading.Thread(target=lambda: got.append(pool.acquire(timeout=5)))
+    t.start()
+    time.sleep(0.05)
+    pool.release(a)
+    t.join(5)
+    assert got == [a]
