@@ -5,6 +5,7 @@
     python bench/profile_case.py gemm_pair   # the same product on CTA pairs (cta_group::2), 3 launches
     python bench/profile_case.py gemm_fp8    # the same shape in block-scaled fp8 (e4m3), 3 launches
     python bench/profile_case.py grouped     # grouped SwiGLU gate/up + down GEMM, 8 experts x 512 rows, 2 launches each
+    python bench/profile_case.py grouped_stream  # the same GEMMs with 16 experts x 128 rows: weight streaming, HBM-bound
     python bench/profile_case.py moe_step    # one single-GPU MoE layer step (T=1024, 32 experts of the 7168/2048 shape)
     python bench/profile_case.py quant       # fp8 1x128 quantise + dequantise of 16384 x 7168
     python bench/profile_case.py copy        # 1024 x 64 KiB segment batch through the NVLink endpoint (local peer)
@@ -66,6 +67,22 @@ def grouped_case():
         gemm.grouped_gemm_bf16(h, w2, offs, out=y)
 
 
+def grouped_stream_case():
+    """The weight-streaming regime of the expert GEMMs (few rows per expert, as on one GPU with 256 experts)."""
+    from dlslime_b200.ops import gemm
+
+    g, rows, k, inter = 16, 128, 7168, 2048
+    offs = torch.arange(0, g + 1, dtype=torch.int32, device="cuda") * rows
+    x = torch.randn(g * rows, k, device="cuda").to(torch.bfloat16)
+    w13 = (torch.randn(g, 2 * inter, k, device="cuda") * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(g, k, inter, device="cuda") * 0.02).to(torch.bfloat16)
+    h = torch.empty(g * rows, inter, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty(g * rows, k, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):
+        gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU)
+        gemm.grouped_gemm_bf16(h, w2, offs, out=y)
+
+
 def moe_case():
     from dlslime_b200.models.moe import ExpertParallelMoE, MoEConfig
 
@@ -104,6 +121,6 @@ def copy_case():
 
 
 if __name__ == "__main__":
-    {"gemm": gemm_case, "gemm_pair": gemm_pair_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
+    {"gemm": gemm_case, "gemm_pair": gemm_pair_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "grouped_stream": grouped_stream_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
     torch.cuda.synchronize()
     print("done", sys.argv[1])
