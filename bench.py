@@ -333,7 +333,7 @@ def run_ours(args, rank, world, local):
     return {
         "ms_dev": ms_dev, "ms_e2e": ms_e2e, "ms_e2e_serial": ms_e2e_serial, "e2e_pipelined": pipe is not None, "clocks": clocks, "breakdown_us": breakdown, "T": T,
         "h2d": host_x[0].numel() * 2 + host_lg[0].numel() * 4, "d2h": host_out.numel() * 2,
-        "launches": (12 if tbo is not None else 6) * args.steps, "cuda_graph": graph is not None, "overlap": tbo is not None, "weights_gb": weights_gb, "nvlink_bytes_per_rank": nvlink_bytes,
+        "launches": (18 if tbo is not None else 6) * args.steps, "cuda_graph": graph is not None, "overlap": tbo is not None, "weights_gb": weights_gb, "nvlink_bytes_per_rank": nvlink_bytes,
     }
 
 

@@ -97,6 +97,7 @@ int slime_ep_recv_dequant(const void* cfg_bytes, const int* group_offsets, void*
 int slime_ep_combine_push(const void* cfg_bytes, const void* y, long long ldy, const int* group_offsets,
                           int expected_rows, void* status, void* stream);
 int slime_ep_signal(const void* cfg_bytes, int which, unsigned long long epoch, void* stream);
+int slime_ep_wait(const void* cfg_bytes, int which, unsigned long long epoch, void* status, void* stream);
 int slime_ep_combine_reduce(const void* cfg_bytes, int T, const int* topk_idx, const float* topk_w, void* out,
                             long long ldo, unsigned long long epoch, int do_signal, void* status, void* stream);
 int slime_ep_barrier(const void* cfg_bytes, unsigned long long epoch, void* status, void* stream);

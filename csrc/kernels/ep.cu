@@ -410,6 +410,15 @@ __global__ void __launch_bounds__(256) ep_combine_reduce_kernel(EpConfig cfg, in
     }
 }
 
+// One small block that waits until every rank's flag reached the step's epoch. Launched in front of a large kernel
+// so that the large kernel itself never spins: when two chains of kernels share a GPU (two-batch overlap), a grid of
+// spinning blocks can otherwise keep the other chain's signalling block from ever being scheduled.
+__global__ void ep_wait_kernel(EpConfig cfg, unsigned long long off, unsigned long long epoch, KernelStatus* st)
+{
+    epoch = resolve_epoch(cfg, epoch);
+    wait_all_ranks(cfg, off, epoch, st, 55);
+}
+
 __global__ void ep_barrier_kernel(EpConfig cfg, unsigned long long epoch, KernelStatus* st)
 {
     if (threadIdx.x < cfg.world) {
@@ -519,6 +528,17 @@ int slime_ep_signal(const void* cfg_bytes, int which, unsigned long long epoch, 
     if (check_cfg(cfg)) return -1;
     const unsigned long long off = which == 0 ? cfg.off_dispatch_done : which == 1 ? cfg.off_combine_done : cfg.off_barrier;
     ep_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(cfg, off, epoch);
+    SLIME_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+int slime_ep_wait(const void* cfg_bytes, int which, unsigned long long epoch, void* status, void* stream)
+{
+    EpConfig cfg;
+    memcpy(&cfg, cfg_bytes, sizeof(cfg));
+    if (check_cfg(cfg)) return -1;
+    const unsigned long long off = which == 0 ? cfg.off_dispatch_done : which == 1 ? cfg.off_combine_done : cfg.off_barrier;
+    ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(cfg, off, epoch, static_cast<KernelStatus*>(status));
     SLIME_CUDA_OK(cudaGetLastError());
     return 0;
 }

@@ -56,7 +56,7 @@ class ExpertParallelMoE:
     """One rank's shard of the MoE layer."""
 
     def __init__(self, cfg: MoEConfig, max_tokens: int, *, group=None, seed: int = 0, buffer: EpBuffer | None = None,
-                 recv_cap: int | None = None, weights=None, recv_grid_rows: int | None = None):
+                 recv_cap: int | None = None, weights=None, recv_grid_rows: int | None = None, thin_waits: bool = False):
         self.cfg = cfg
         self.buf = buffer or EpBuffer(cfg.num_experts, cfg.topk, cfg.hidden, max_tokens, group=group, recv_cap=recv_cap)
         self.rank, self.world = self.buf.rank, self.buf.world
@@ -66,6 +66,9 @@ class ExpertParallelMoE:
             weights = init_expert_weights(cfg, range(self.rank * epr, (self.rank + 1) * epr), dev, seed)
         self.w_gate_up, self.w_down = weights
         self.recv_grid_rows = recv_grid_rows  # sizes the grid of the receive kernel (None: by the expected row count)
+        # thin_waits: every wait for other ranks is a one-block kernel in front of the large kernel, which then starts
+        # with its flags already set and never spins (needed when two chains of kernels share the GPU)
+        self.thin_waits = thin_waits
         cap = self.buf.recv_cap
         self.xd = torch.empty((cap, cfg.hidden), dtype=torch.bfloat16, device=dev)
         self.h = torch.empty((cap, cfg.intermediate), dtype=torch.bfloat16, device=dev)
@@ -82,6 +85,8 @@ class ExpertParallelMoE:
     def step_recv(self, T, epoch):
         c = self.cfg
         rows = self.recv_grid_rows or min(self.buf.recv_cap, max(1, 2 * T * c.topk))
+        if self.thin_waits:
+            self.buf.wait(0, epoch)
         self.buf.recv_dequant(self.xd, epoch, expected_rows=rows)
 
     def step_gate_up(self):
@@ -99,6 +104,10 @@ class ExpertParallelMoE:
         self.step_down()
 
     def step_combine(self, out, T, epoch, do_signal=True):
+        if self.thin_waits and do_signal:
+            self.buf.signal(1, epoch)
+            self.buf.wait(1, epoch)
+            do_signal = False
         self.buf.combine_reduce(out, T, epoch, do_signal=do_signal)
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -140,17 +149,17 @@ class TwoBatchOverlapMoE:
     half's expert GEMMs.
 
     The halves are two :class:`ExpertParallelMoE` instances that share the expert weights and own their
-    symmetric buffers and step counters, so no protocol state is shared and the two chains never wait on each other;
-    every kernel still waits only on kernels that the other RANKS issued earlier in the same chain. The spinning
-    receive kernel is launched with a grid that leaves half of every SM's thread slots free, so kernels of the
-    other chain can always start beside it.
+    symmetric buffers and step counters, so no protocol state is shared and the two chains never wait on each other.
+    Waits for other ranks are one-block kernels in front of the large kernels (``thin_waits``): a large grid that spins
+    could fill the GPU while the block that has to signal for the OTHER chain cannot be scheduled, on two ranks in
+    opposite order, and then neither would ever be released (seen as 1 s timeouts on two GPUs at full size).
     """
 
     def __init__(self, cfg: MoEConfig, max_tokens: int, *, group=None, seed: int = 0, weights=None):
         half = (max_tokens + 1) // 2
         self.cfg, self.max_tokens, self.half = cfg, max_tokens, half
-        self.a = ExpertParallelMoE(cfg, half, group=group, seed=seed, weights=weights, recv_grid_rows=160)
-        self.b = ExpertParallelMoE(cfg, half, group=group, weights=(self.a.w_gate_up, self.a.w_down), recv_grid_rows=160)
+        self.a = ExpertParallelMoE(cfg, half, group=group, seed=seed, weights=weights, thin_waits=True)
+        self.b = ExpertParallelMoE(cfg, half, group=group, weights=(self.a.w_gate_up, self.a.w_down), thin_waits=True)
         self.rank, self.world = self.a.rank, self.a.world
         self.buf = self.a.buf  # status page and geometry for callers that look at the single-batch layer's buffer
         self.w_gate_up, self.w_down = self.a.w_gate_up, self.a.w_down

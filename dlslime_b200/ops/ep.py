@@ -212,6 +212,11 @@ class EpBuffer:
         cfg, e = self._mode(epoch)
         _lib.call("slime_ep_signal", cfg, which, e, stream_ptr())
 
+    def wait(self, which: int, epoch: int | None = None) -> None:
+        """One small block that waits for every rank's flag (0 dispatch done, 1 combine done) of this step."""
+        cfg, e = self._mode(epoch)
+        _lib.call("slime_ep_wait", cfg, which, e, self.status.dev_ptr, stream_ptr())
+
     def combine_reduce(self, out: torch.Tensor, T: int, epoch: int | None = None, do_signal: bool = True) -> None:
         cfg, e = self._mode(epoch)
         _lib.call("slime_ep_combine_reduce", cfg, T, ptr(self.topk_idx), ptr(self.topk_w), ptr(out), out.stride(0),
@@ -230,5 +235,6 @@ _lib.declare("slime_ep_dispatch", [_ct.c_char_p, _v, _ll, _i, _v, _v, _v, _v, _u
 _lib.declare("slime_ep_recv_dequant", [_ct.c_char_p, _v, _v, _ll, _i, _ull, _v, _v])
 _lib.declare("slime_ep_combine_push", [_ct.c_char_p, _v, _ll, _v, _i, _v, _v])
 _lib.declare("slime_ep_signal", [_ct.c_char_p, _i, _ull, _v])
+_lib.declare("slime_ep_wait", [_ct.c_char_p, _i, _ull, _v, _v])
 _lib.declare("slime_ep_combine_reduce", [_ct.c_char_p, _i, _v, _v, _v, _ll, _ull, _i, _v, _v])
 _lib.declare("slime_ep_barrier", [_ct.c_char_p, _ull, _v, _v])
