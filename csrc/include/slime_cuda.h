@@ -64,6 +64,9 @@ int slime_ag_gemm_fp8(int mode, const void* xq_local, const float* sx_local, con
                       const void* Bq, const float* sb, void* C, int rows_local, int N, int K, long long ldb, long long ldc, int rank,
                       int world, const unsigned long long* dst8, const unsigned long long* sdst8, const unsigned long long* flags8,
                       unsigned long long step, int push_blocks, void* status, void* stream);
+int slime_grouped_gemm_fp8a(const void* Aq, const float* a_scale, const void* B, void* C, const int* group_offsets, int num_groups,
+                            int M_cap, int N, int K, long long lda_bytes, long long ldb, long long ldc, int epilogue, void* status,
+                            void* stream);
 int slime_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                           long long ldc, const void* a_ready, int a_ready_rows, unsigned long long a_ready_target,
                           int m_tile_rotate, void* status, void* stream);

@@ -16,6 +16,7 @@
 // drains, frees its TMEM and returns.
 #pragma once
 
+#include "fp8.cuh"
 #include "ptx.cuh"
 
 namespace slime {
@@ -62,6 +63,8 @@ struct Args {
     int                       ag_local_direct; // tiles of the own shard read ag_src through the third tensor map and wait for nothing
     unsigned long long        ag_dst[8];       // address of the gathered A on every rank
     unsigned long long        ag_flags[8];     // address of the arrival counters (u64 per 128 rows) on every rank
+    // A operand as e4m3 with 1x128 scales (kernels instantiated with A8): the tile is expanded to bf16 in shared memory
+    const float*              a_scale;         // [M_total, K / 128]
     KernelStatus*             status;
     unsigned long long        wait_ns;
 };
@@ -70,14 +73,15 @@ constexpr int kAgChunkBytes = 4096;  // staging buffer of the in-kernel all-gath
 constexpr int kAgMaxBufs    = 6;
 constexpr int kSmemLimit    = 227 * 1024;
 
-template<int BN, int STAGES, bool AG = false>
+template<int BN, int STAGES, bool AG = false, bool A8 = false>
 struct Smem {
     static constexpr int kABytes     = kBM * kBK * 2;
     static constexpr int kBBytes     = BN * kBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kBarBytes   = (2 * STAGES + 4 + kAgMaxBufs) * 8 + 16;
+    static constexpr int kRawBytes   = A8 ? kBM * kBK : 0;  // e4m3 A tile of a stage as it arrives, before expansion
+    static constexpr int kBarBytes   = (3 * STAGES + 4 + kAgMaxBufs) * 8 + 16;
     static constexpr int kEpiBytes   = 128 * kEpiRowPitch;  // one padded 128-byte slot per tile row
-    static constexpr int kBase       = STAGES * kStageBytes + kEpiBytes + kBarBytes + 1024;  // + alignment slack
+    static constexpr int kBase       = STAGES * (kStageBytes + kRawBytes) + kEpiBytes + kBarBytes + 1024;  // + alignment slack
     // the push stages its chunks in whatever shared memory the tile ring leaves free
     static constexpr int kAgBufs = !AG ? 0 : ((kSmemLimit - kBase - 128) / kAgChunkBytes > kAgMaxBufs ? kAgMaxBufs : (kSmemLimit - kBase - 128) / kAgChunkBytes);
     static constexpr int kTotal  = kBase + (AG ? kAgBufs * kAgChunkBytes + 128 : 0);
@@ -289,19 +293,29 @@ static __global__ void __launch_bounds__(256) ag_push_only_kernel(const Args arg
     ag_push_units(args, threadIdx.x, blockDim.x, 1, blockIdx.x, gridDim.x);
 }
 
-template<int BN, int STAGES, int EPI, bool AG = false>
-__global__ void __launch_bounds__(kThreads + (AG ? kAgThreads : 0), 1)
+constexpr int kCvtThreads = 128;  // A8 kernels: four more warps expand the e4m3 A tile of every stage to bf16
+
+// A8 = true: tmA describes A as e4m3 bytes [M_total, K] (box 128 rows x 64 bytes, no swizzle) and args.a_scale its 1x128
+// scales. The producer lands the raw tile in a staging area; four converter warps (one thread per tile row) multiply
+// by the row's scale, round to bf16 exactly as the stand-alone dequantisation kernel does, and write the tile in the
+// 128-byte-swizzled K-major layout the MMA descriptor expects; the "full" barrier of the stage then needs the B bytes
+// AND the converters' arrival. This removes the dequantisation pass over the received rows and halves the A traffic.
+template<int BN, int STAGES, int EPI, bool AG = false, bool A8 = false>
+__global__ void __launch_bounds__(kThreads + (AG ? kAgThreads : 0) + (A8 ? kCvtThreads : 0), 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmAL, const Args args)
 {
-    using S = Smem<BN, STAGES, AG>;
+    static_assert(!(AG && A8), "the all-gather form takes bf16 activations");
+    using S = Smem<BN, STAGES, AG, A8>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
-    uint8_t*  epi_smem   = smem + STAGES * S::kStageBytes;
+    uint8_t*  raw_smem   = smem + STAGES * S::kStageBytes;             // [STAGES][kRawBytes] (A8 only)
+    uint8_t*  epi_smem   = raw_smem + STAGES * S::kRawBytes;
     uint64_t* full_bar   = reinterpret_cast<uint64_t*>(epi_smem + S::kEpiBytes);
     uint64_t* empty_bar  = full_bar + STAGES;
-    uint64_t* tfull_bar  = empty_bar + STAGES;  // [2] accumulator ready
+    uint64_t* raw_bar    = empty_bar + STAGES;  // [STAGES] raw A tile landed (A8 only)
+    uint64_t* tfull_bar  = raw_bar + STAGES;    // [2] accumulator ready
     uint64_t* tempty_bar = tfull_bar + 2;       // [2] accumulator drained
     uint64_t* ag_bar     = tempty_bar + 2;      // [kAgMaxBufs] push chunk loaded
     uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(ag_bar + kAgMaxBufs);
@@ -321,8 +335,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (threadIdx.x == 0) {
         *fail_slot = 0;
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], 1);
+            mbar_init(&full_bar[s], A8 ? 1 + kCvtThreads : 1);  // the producer (B bytes) and, for A8, every converter thread
             mbar_init(&empty_bar[s], 1);
+            mbar_init(&raw_bar[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&tfull_bar[s], 1);
@@ -389,8 +404,15 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     }
                     uint8_t* sa = smem + stage * S::kStageBytes;
                     uint8_t* sb = sa + S::kABytes;
-                    mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
-                    tma_load_2d(sa, mapA, &full_bar[stage], kb * kBK, arow);
+                    if (A8) {
+                        mbar_arrive_expect_tx(&raw_bar[stage], S::kRawBytes);
+                        tma_load_2d(raw_smem + stage * S::kRawBytes, mapA, &raw_bar[stage], kb * kBK, arow);
+                        mbar_arrive_expect_tx(&full_bar[stage], S::kBBytes);
+                    }
+                    else {
+                        mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
+                        tma_load_2d(sa, mapA, &full_bar[stage], kb * kBK, arow);
+                    }
                     tma_load_2d(sb, &tmB, &full_bar[stage], kb * kBK, yb0);
                     tma_load_2d(sb + S::kBBytes / 2, &tmB, &full_bar[stage], kb * kBK, yb1);
                     if (++stage == STAGES) {
@@ -450,6 +472,45 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
             if (!ok) *fail_slot = 1;
         }
+    }
+    else if (A8 && warp >= 6) {
+        // ------------------------------ e4m3 -> bf16 expansion of the A tile ------
+        const int  r = threadIdx.x - kThreads;  // tile row of this thread
+        TileWalker walk(args, kBNOut);
+        TileCoord  tc;
+        int        stage = 0;
+        uint32_t   phase = 0;
+        bool       ok    = true;
+        const int  srow  = args.K / 128;
+        while (ok && walk.next(tc)) {
+            int grow = tc.row0 + r;  // rows past the end of A read zeros from the TMA fill; their scale must only be addressable
+            if (grow >= args.M_total) grow = args.M_total - 1;
+            const float* sc_row = args.a_scale + static_cast<long long>(grow) * srow;
+            float        sc     = sc_row[0];
+            for (int kb = 0; kb < kblocks; ++kb) {
+                if ((kb & 1) == 0) sc = sc_row[kb >> 1];  // one scale per 128 elements = two K blocks
+                if (!mbar_wait(&raw_bar[stage], phase, st, 5, stage, lim)) {
+                    ok = false;
+                    break;
+                }
+                const uint8_t* raw = raw_smem + stage * S::kRawBytes + r * kBK;  // 64 bytes per row, unswizzled
+                uint8_t*       dst = smem + stage * S::kStageBytes + r * 128;    // 128 bytes per row, 16-byte chunks XOR-swizzled
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint2 q = *reinterpret_cast<const uint2*>(raw + c * 8);
+                    float       v[8];
+                    dequant_fp8x8(q, sc, v);
+                    *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = pack_bf16x8(v);
+                }
+                fence_proxy_async_smem();  // the tensor core reads this through the async proxy
+                mbar_arrive(&full_bar[stage]);
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+        }
+        if (!ok) *fail_slot = 1;
     }
     else if (AG && warp >= 6) {
         // ------------------------------ all-gather push ---------------------------

@@ -88,6 +88,28 @@ int launch_ag(const void* A, const void* B, const void* A_local, const Args& arg
     }
 }
 
+// Grouped GEMM whose A operand is e4m3 with 1x128 scales, expanded to bf16 inside the kernel (three stages: the raw
+// tile needs room next to the bf16 one).
+template<int EPI>
+int launch_a8(const void* Aq, const void* B, const Args& args, long long lda_bytes, long long ldb, cudaStream_t stream)
+{
+    constexpr int kStagesA8 = 3;
+    using S = Smem<kBN, kStagesA8, false, true>;
+    CUtensorMap tmA, tmB;
+    const unsigned long long rowsB_total = static_cast<unsigned long long>(args.rowsB) * args.num_groups;
+    if (make_tmap_2d(&tmA, Aq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, args.M_total, args.K, lda_bytes, kBM, kBK)) return -1;
+    if (make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rowsB_total, args.K, ldb, kBN / 2, kBK)) return -1;
+    auto kern = gemm_bf16_tc_kernel<kBN, kStagesA8, EPI, false, true>;
+    static bool configured = false;
+    if (!configured) {
+        SLIME_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+        configured = true;
+    }
+    kern<<<sm_count(), kThreads + kCvtThreads, S::kTotal, stream>>>(tmA, tmB, tmA, args);
+    SLIME_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
 // CTA-pair kernels: 256-row tiles on clusters of two CTAs (one-group GEMMs only).
 int pick_bn_pair(int M, int N)
 {
@@ -305,6 +327,38 @@ int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* gr
         default:
             return fail("grouped gemm: unknown epilogue %d", epilogue);
     }
+}
+
+// The grouped GEMM with A as received from the dispatch: e4m3 rows Aq [M_cap, K] (lda in bytes) and their 1x128 scales
+// a_scale [M_cap, K/128]. epilogue: kEpiStore or kEpiSwiGLU.
+int slime_grouped_gemm_fp8a(const void* Aq, const float* a_scale, const void* B, void* C, const int* group_offsets, int num_groups,
+                            int M_cap, int N, int K, long long lda_bytes, long long ldb, long long ldc, int epilogue, void* status,
+                            void* stream)
+{
+    if (check_common(M_cap, N, K, 8, ldb)) return -1;
+    if (K % 128 != 0 || lda_bytes % 16 != 0) return fail("fp8-A grouped gemm: K must be a multiple of 128 and lda of 16 bytes");
+    if (num_groups <= 0 || group_offsets == nullptr || a_scale == nullptr) return fail("fp8-A grouped gemm: need group offsets and scales");
+    Args a{};
+    a.M_total       = M_cap;
+    a.N             = N;
+    a.K             = K;
+    a.num_groups    = num_groups;
+    a.group_offsets = group_offsets;
+    a.C             = static_cast<__nv_bfloat16*>(C);
+    a.ldc           = ldc;
+    a.a_scale       = a_scale;
+    a.status        = static_cast<KernelStatus*>(status);
+    cudaStream_t s  = static_cast<cudaStream_t>(stream);
+    if (epilogue == kEpiStore) {
+        a.rowsB = N;
+        return launch_a8<kEpiStore>(Aq, B, a, lda_bytes, ldb, s);
+    }
+    if (epilogue == kEpiSwiGLU) {
+        if (N % (kBN / 2) != 0) return fail("fp8-A grouped gemm: SwiGLU needs N to be a multiple of %d", kBN / 2);
+        a.rowsB = 2 * N;
+        return launch_a8<kEpiSwiGLU>(Aq, B, a, lda_bytes, ldb, s);
+    }
+    return fail("fp8-A grouped gemm: unknown epilogue %d", epilogue);
 }
 
 }  // extern "C"

@@ -40,6 +40,8 @@ _SIGNATURES = {
     "slime_gemm_bf16_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p],
     "slime_gemm_fp8_blockscaled": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
                                    c_longlong, c_void_p, c_void_p],
+    "slime_grouped_gemm_fp8a": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong,
+                                c_longlong, c_int, c_void_p, c_void_p],
     "slime_gemm_bf16_gated": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                               c_void_p, c_int, c_ulonglong, c_int, c_void_p, c_void_p],
     "slime_grouped_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong,

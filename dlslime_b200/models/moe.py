@@ -56,7 +56,8 @@ class ExpertParallelMoE:
     """One rank's shard of the MoE layer."""
 
     def __init__(self, cfg: MoEConfig, max_tokens: int, *, group=None, seed: int = 0, buffer: EpBuffer | None = None,
-                 recv_cap: int | None = None, weights=None, recv_grid_rows: int | None = None, thin_waits: bool = False):
+                 recv_cap: int | None = None, weights=None, recv_grid_rows: int | None = None, thin_waits: bool = False,
+                 fuse_dequant: bool = False):
         self.cfg = cfg
         self.buf = buffer or EpBuffer(cfg.num_experts, cfg.topk, cfg.hidden, max_tokens, group=group, recv_cap=recv_cap)
         self.rank, self.world = self.buf.rank, self.buf.world
@@ -69,6 +70,9 @@ class ExpertParallelMoE:
         # thin_waits: every wait for other ranks is a one-block kernel in front of the large kernel, which then starts
         # with its flags already set and never spins (needed when two chains of kernels share the GPU)
         self.thin_waits = thin_waits
+        # fuse_dequant: the gate/up GEMM reads the received e4m3 rows and their scales directly and expands them in
+        # shared memory (bit-identical to the separate pass, which is then only a one-block wait for the rows)
+        self.fuse_dequant = fuse_dequant
         cap = self.buf.recv_cap
         self.xd = torch.empty((cap, cfg.hidden), dtype=torch.bfloat16, device=dev)
         self.h = torch.empty((cap, cfg.intermediate), dtype=torch.bfloat16, device=dev)
@@ -84,12 +88,19 @@ class ExpertParallelMoE:
 
     def step_recv(self, T, epoch):
         c = self.cfg
+        if self.fuse_dequant:
+            self.buf.wait(0, epoch)
+            return
         rows = self.recv_grid_rows or min(self.buf.recv_cap, max(1, 2 * T * c.topk))
         if self.thin_waits:
             self.buf.wait(0, epoch)
         self.buf.recv_dequant(self.xd, epoch, expected_rows=rows)
 
     def step_gate_up(self):
+        if self.fuse_dequant:
+            gemm.grouped_gemm_fp8a(self.buf.recv_x, self.buf.recv_scale, self.w_gate_up, self.buf.group_offsets, out=self.h,
+                                   epilogue=gemm.EPI_SWIGLU)
+            return
         gemm.grouped_gemm_bf16(self.xd, self.w_gate_up, self.buf.group_offsets, out=self.h, epilogue=gemm.EPI_SWIGLU)
 
     def step_down(self):

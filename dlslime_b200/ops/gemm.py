@@ -77,6 +77,27 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
     return out
 
 
+def grouped_gemm_fp8a(aq: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor,
+                      out: torch.Tensor | None = None, epilogue: int = EPI_STORE) -> torch.Tensor:
+    """The grouped GEMM with the activations still in their wire format: ``aq [M_cap, K]`` e4m3 and ``a_scale
+    [M_cap, K/128]`` (1x128 scales), bf16 weights ``b [G, N or 2N, K]``. The kernel expands every A tile to bf16 in
+    shared memory with the same rounding as :func:`dlslime_b200.ops.quant.fp8_dequant_1x128`, so the result is
+    bit-identical to dequantising first and calling :func:`grouped_gemm_bf16`, without the pass over the rows."""
+    require_cuda(aq, a_scale, b, group_offsets)
+    assert aq.dtype == torch.float8_e4m3fn and b.dtype == torch.bfloat16 and group_offsets.dtype == torch.int32
+    assert aq.stride(1) == 1 and b.is_contiguous() and b.dim() == 3 and a_scale.dtype == torch.float32 and a_scale.is_contiguous()
+    assert epilogue in (EPI_STORE, EPI_SWIGLU)
+    g, rows_b, k = b.shape
+    m_cap = aq.shape[0]
+    n = rows_b // 2 if epilogue == EPI_SWIGLU else rows_b
+    assert group_offsets.numel() == g + 1 and aq.shape[1] == k and k % 128 == 0 and a_scale.shape == (m_cap, k // 128)
+    if out is None:
+        out = torch.empty((m_cap, n), dtype=torch.bfloat16, device=aq.device)
+    _lib.call("slime_grouped_gemm_fp8a", ptr(aq), ptr(a_scale), ptr(b), ptr(out), ptr(group_offsets), g, m_cap, n, k,
+              aq.stride(0), k, out.stride(0), epilogue, default_status().dev_ptr, stream_ptr())
+    return out
+
+
 def gemm_fp8_blockscaled(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.Tensor,
                          out: torch.Tensor | None = None) -> torch.Tensor:
     """``out[M, N]`` (bf16) ``= dequant(aq, sa) @ dequant(bq, sb).T`` on the fp8 tensor cores.

@@ -120,3 +120,19 @@ def test_two_batch_overlap_single_rank(tokens):
         err = (out.float() - ref.float()).abs()
         tol = ref.float().abs() * 2 ** -6 + ref.float().abs().mean() * 2 ** -5
         assert (err <= tol).all(), f"step {step}: max err {err.max().item()}"
+
+
+def test_moe_layer_with_fused_dequant_matches_the_two_pass_layer():
+    from dlslime_b200.models.moe import ExpertParallelMoE, MoEConfig
+
+    cfg = MoEConfig(num_experts=16, topk=4, hidden=1024, intermediate=256)
+    plain = ExpertParallelMoE(cfg, max_tokens=256, seed=5)
+    fused = ExpertParallelMoE(cfg, max_tokens=256, weights=(plain.w_gate_up, plain.w_down), fuse_dequant=True)
+    for tokens in (1, 77, 256):
+        gen = torch.Generator(device="cuda").manual_seed(tokens)
+        x = torch.randn((tokens, cfg.hidden), generator=gen, device="cuda").to(torch.bfloat16)
+        lg = torch.randn((tokens, cfg.num_experts), generator=gen, device="cuda")
+        a, b = plain(x, lg), fused(x, lg)
+        torch.cuda.synchronize()
+        plain.buf.status.check()
+        assert torch.equal(a, b), (a.float() - b.float()).abs().max().item()

@@ -143,3 +143,29 @@ def test_gemm_fp8_blockscaled(m, n, k):
     full = a.float() @ w.float().t()
     rel = (out.float() - full).norm() / full.norm()
     assert rel < 0.08, rel.item()
+
+
+def test_grouped_gemm_with_fp8_activations_is_bit_identical_to_dequant_then_gemm():
+    """The gate/up GEMM fed with e4m3 rows and 1x128 scales (expanded in shared memory) against the two-pass path."""
+    from dlslime_b200.ops import gemm, quant
+    from dlslime_b200.ops._common import default_status
+
+    torch.manual_seed(11)
+    sizes = [0, 5, 128, 131, 300, 1, 0, 64]
+    g, k, inter = len(sizes), 1024, 256
+    offs = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device="cuda")
+    total = sum(sizes)
+    x = (torch.randn(total + 37, k, device="cuda") * torch.rand(total + 37, 1, device="cuda") * 3).to(torch.bfloat16)
+    xq, xs = quant.fp8_quant_1x128(x)
+    xd = quant.fp8_dequant_1x128(xq, xs)
+    w13 = (torch.randn(g, 2 * inter, k, device="cuda") * 0.05).to(torch.bfloat16)
+    w = (torch.randn(g, inter, k, device="cuda") * 0.05).to(torch.bfloat16)
+    for weights, epi in ((w13, gemm.EPI_SWIGLU), (w, gemm.EPI_STORE)):
+        ref = torch.zeros((total + 37, inter), device="cuda", dtype=torch.bfloat16)
+        out = torch.zeros_like(ref)
+        gemm.grouped_gemm_bf16(xd, weights, offs, out=ref, epilogue=epi)
+        gemm.grouped_gemm_fp8a(xq, xs, weights, offs, out=out, epilogue=epi)
+        torch.cuda.synchronize()
+        default_status().check()
+        assert torch.equal(out[:total], ref[:total]), (out[:total].float() - ref[:total].float()).abs().max().item()
+        assert bool((out[total:] == 0).all())
