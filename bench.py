@@ -188,7 +188,7 @@ def run_ours(args, rank, world, local):
 
     T = T_MODE[args.mode]
     cfg = MoEConfig(num_experts=E, topk=TOPK, hidden=HIDDEN, intermediate=INTER)
-    layer = ExpertParallelMoE(cfg, max_tokens=T, seed=0)
+    layer = ExpertParallelMoE(cfg, max_tokens=T, seed=0, fuse_dequant=args.fuse_dequant)
     tbo = None
     if args.overlap and args.mode == "normal":
         from dlslime_b200.models.moe import TwoBatchOverlapMoE
@@ -333,7 +333,8 @@ def run_ours(args, rank, world, local):
     return {
         "ms_dev": ms_dev, "ms_e2e": ms_e2e, "ms_e2e_serial": ms_e2e_serial, "e2e_pipelined": pipe is not None, "clocks": clocks, "breakdown_us": breakdown, "T": T,
         "h2d": host_x[0].numel() * 2 + host_lg[0].numel() * 4, "d2h": host_out.numel() * 2,
-        "launches": (18 if tbo is not None else 6) * args.steps, "cuda_graph": graph is not None, "overlap": tbo is not None, "weights_gb": weights_gb, "nvlink_bytes_per_rank": nvlink_bytes,
+        "launches": (18 if tbo is not None else 6) * args.steps, "cuda_graph": graph is not None, "overlap": tbo is not None,
+        "dequant": "in the gate/up GEMM's A-tile loader" if args.fuse_dequant else "separate pass", "weights_gb": weights_gb, "nvlink_bytes_per_rank": nvlink_bytes,
     }
 
 
@@ -356,6 +357,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--mode", choices=["ll", "normal"], default="normal")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--fuse-dequant", action="store_true",
+                    help="expand the received e4m3 rows to bf16 inside the gate/up GEMM instead of in a separate pass (measured slower)")
     ap.add_argument("--overlap", action="store_true",
                     help="normal mode: split the step into two half-batches on two streams (communication of one half under the GEMMs of the other)")
     ap.add_argument("--no-graph", action="store_true", help="ll mode: launch the kernels one by one instead of replaying a CUDA graph")
@@ -385,7 +388,7 @@ def main():
         "nvlink_gbs_per_rank": round(res["nvlink_bytes_per_rank"] / (res["ms_dev"] * 1e-3) / 1e9, 2),
         "config": {
             "model": "DeepSeek-V3-shaped MoE layer: 256 experts, top-8, hidden 7168, intermediate 2048",
-            "mode": args.mode, "cuda_graph": bool(res.get("cuda_graph")), "two_batch_overlap": bool(res.get("overlap")), "tokens_per_rank": T, "global_batch": world * T, "seq_len": 1,
+            "mode": args.mode, "cuda_graph": bool(res.get("cuda_graph")), "two_batch_overlap": bool(res.get("overlap")), "dequant": res.get("dequant"), "tokens_per_rank": T, "global_batch": world * T, "seq_len": 1,
             "parallelism": f"ep{world}", "experts_per_rank": E // world,
             "l2": f"inputs larger than L2: {res['weights_gb']:.1f} GB of expert weights per rank are streamed every step",
         },

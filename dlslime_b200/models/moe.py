@@ -71,7 +71,9 @@ class ExpertParallelMoE:
         # with its flags already set and never spins (needed when two chains of kernels share the GPU)
         self.thin_waits = thin_waits
         # fuse_dequant: the gate/up GEMM reads the received e4m3 rows and their scales directly and expands them in
-        # shared memory (bit-identical to the separate pass, which is then only a one-block wait for the rows)
+        # shared memory (bit-identical to the separate pass, which is then only a one-block wait for the rows). Off by
+        # default: with the raw tile next to the bf16 one the ring is 3 stages deep instead of 4 and the expansion sits
+        # between the load and the MMA; measured on one GPU the gate/up GEMM takes 3.76 ms instead of 2.73 + 0.13 ms.
         self.fuse_dequant = fuse_dequant
         cap = self.buf.recv_cap
         self.xd = torch.empty((cap, cfg.hidden), dtype=torch.bfloat16, device=dev)
