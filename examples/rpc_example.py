@@ -4,8 +4,8 @@
     python examples/rpc_example.py                        # starts a control plane in this process
     python examples/rpc_example.py --ctrl http://host:3000  # or uses a running `nanoctrl start`
 
-Same flow as the reference's examples/python/rpc_example.py: a service class with @method-decorated methods,
-`serve` on the worker, `proxy` on the driver, futures with .wait().
+The pattern of the reference's examples/python/rpc_example.py (a class with @method-decorated methods, `serve` on the
+worker, `proxy` on the driver, futures with .wait()), on a small block directory with pickled and raw methods.
 """
 import argparse
 import os
@@ -19,18 +19,28 @@ from dlslime_b200.nanoctrl import start_local_nanoctrl  # noqa: E402
 from dlslime_b200.rpc import method, proxy, serve  # noqa: E402
 
 
-class CalcService:
-    @method
-    def add(self, a: int, b: int) -> int:
-        return a + b
+class BlockIndex:
+    """A toy block directory: which worker holds which KV block, served over SlimeRPC."""
+
+    def __init__(self):
+        self.blocks = {}
 
     @method
-    def mul(self, a: float, b: float) -> float:
-        return a * b
+    def publish(self, block_id: int, owner: str, nbytes: int) -> int:
+        self.blocks[block_id] = (owner, nbytes)
+        return len(self.blocks)
 
     @method
-    def echo(self, msg: str) -> str:
-        return f"echo: {msg}"
+    def lookup(self, block_id: int):
+        return self.blocks.get(block_id)
+
+    @method
+    def total_bytes(self) -> int:
+        return sum(n for _, n in self.blocks.values())
+
+    @method(raw=True)
+    def checksum(self, payload: bytes) -> bytes:
+        return sum(payload).to_bytes(8, "little")
 
 
 def main(ctrl_url):
@@ -45,15 +55,16 @@ def main(ctrl_url):
         driver.connect_to("worker:0").wait(10)
         worker.connect_to("driver:0").wait(10)
         print("Connected.")
-        t = threading.Thread(target=serve, args=(worker, CalcService(), "driver:0"), kwargs={"stop_event": stop}, daemon=True)
+        t = threading.Thread(target=serve, args=(worker, BlockIndex(), "driver:0"), kwargs={"stop_event": stop}, daemon=True)
         t.start()
-        w = proxy(driver, "worker:0", CalcService)
-        assert w.add(1, 2).wait() == 3
-        assert abs(w.mul(3.14, 2.0).wait() - 6.28) < 1e-6
-        assert w.echo("hello").wait() == "echo: hello"
-        results = [w.add(i, i * 10).wait() for i in range(5)]
-        assert results == [0, 11, 22, 33, 44]
-        print(f"add / mul / echo / batch add = {results}: all calls returned")
+        w = proxy(driver, "worker:0", BlockIndex)
+        assert w.publish(7, "prefill:3", 1 << 20).wait() == 1
+        futures = [w.publish(100 + i, f"prefill:{i % 4}", 4096 * (i + 1)) for i in range(8)]   # eight calls in flight
+        assert [f.wait() for f in futures][-1] == 9
+        assert w.lookup(7).wait() == ("prefill:3", 1 << 20) and w.lookup(999).wait() is None
+        assert w.total_bytes().wait() == (1 << 20) + 4096 * 36
+        assert int.from_bytes(w.checksum(bytes(range(200))).wait(), "little") == sum(range(200))
+        print("publish / lookup / total_bytes / raw checksum: all calls returned")
         w.close()
     finally:
         stop.set()
