@@ -332,3 +332,49 @@ def test_obs_counts_each_operation_once_with_four_queue_pairs():
         print("ok")
     """, env_extra={"DLSLIME_OBS": "1"})
     assert "ok" in out
+
+
+def test_slimerpc_over_rdma_links():
+    """SlimeRPC (slot mailbox written with write_with_imm, immediates as slot ids) between two agents connected over
+    RoCE-typed links with two queue pairs: calls, a burst of calls in flight, a large reply that is chunked, a remote exception."""
+    out = run_child("""
+        from dlslime_b200.nanoctrl import start_local_nanoctrl
+        from dlslime_b200.peer_agent import PeerAgent
+        from dlslime_b200.rpc import method, proxy, serve
+        from dlslime_b200.rpc.errors import RemoteRpcError
+
+        class Svc:
+            @method
+            def add(self, a, b):
+                return a + b
+            @method
+            def blob(self, n):
+                return bytes(i % 251 for i in range(n))
+            @method
+            def boom(self):
+                raise ValueError("no such block")
+
+        ctrl = start_local_nanoctrl()
+        w = PeerAgent(ctrl.url, alias="w", scope="rr", device="rdma_lo0", link_type="RoCE")
+        d = PeerAgent(ctrl.url, alias="d", scope="rr", device="rdma_lo2", link_type="RoCE")
+        stop = threading.Event()
+        try:
+            d.connect_to("w", local_device="rdma_lo2", peer_device="rdma_lo0", qp_num=2).wait(10)
+            w.connect_to("d", local_device="rdma_lo0", peer_device="rdma_lo2", qp_num=2).wait(10)
+            threading.Thread(target=serve, args=(w, Svc(), "d"), kwargs={"stop_event": stop}, daemon=True).start()
+            p = proxy(d, "w", Svc)
+            assert p.add(2, 3).wait(10) == 5
+            futs = [p.add(i, i) for i in range(32)]
+            assert [f.wait(10) for f in futs] == [2 * i for i in range(32)]
+            big = p.blob(600_000).wait(20)
+            assert len(big) == 600_000 and big[:5] == bytes([0, 1, 2, 3, 4]) and big[-1] == (599_999 % 251)
+            try:
+                p.boom().wait(10); raise SystemExit("must raise")
+            except RemoteRpcError as e:
+                assert "no such block" in str(e)
+            p.close()
+        finally:
+            stop.set(); d.shutdown(); w.shutdown(); ctrl.stop()
+        print("ok")
+    """, timeout=180)
+    assert "ok" in out
