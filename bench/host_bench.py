@@ -5,6 +5,8 @@
     python bench/host_bench.py sendrecv  [--transport tcp|rdma] [--sizes ...]
     python bench/host_bench.py rpc       [--sizes 64,4096,65536,1048576] [--iters 500]
     python bench/host_bench.py cache     [--length 16777216] [--iters 20]
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 bench/host_bench.py torch [--sizes ...]
+                                         # send / recv through torch.distributed with backend "dlslime"
 
 `--transport rdma` uses the verbs provider the host offers; `SLIME_RDMA_PROVIDER=loopback` selects the software RC
 fabric (which measures the engine's own overhead: striping, credits, completion routing, not a wire). One JSON line per
@@ -168,9 +170,32 @@ def cmd_cache(args):
         ctrl.stop()
 
 
+def cmd_torch(args):
+    import torch
+    import torch.distributed as dist
+
+    import dlslime_b200.torch_backend  # noqa: F401  (registers the backend)
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("dlslime")
+    rank = dist.get_rank()
+    for size in [int(s) for s in args.sizes.split(",")]:
+        t = torch.zeros(size, dtype=torch.uint8)
+        for _ in range(5):
+            dist.send(t, 1) if rank == 0 else dist.recv(t, 0)
+        t0 = time.perf_counter()
+        for _ in range(args.iters):
+            dist.send(t, 1) if rank == 0 else dist.recv(t, 0)
+        dt = time.perf_counter() - t0
+        if rank == 1:
+            print(json.dumps({"bench": "torch_dist_sendrecv", "backend": "dlslime", "bytes": size, "us_per_msg": round(dt / args.iters * 1e6, 1),
+                              "mb_s": round(size * args.iters / dt / 1e6, 1)}), flush=True)
+    os._exit(0)
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("cmd", choices=["io", "sendrecv", "rpc", "cache"])
+    ap.add_argument("cmd", choices=["io", "sendrecv", "rpc", "cache", "torch"])
     ap.add_argument("--transport", default="tcp", choices=["tcp", "rdma"])
     ap.add_argument("--sizes", default="4096,65536,1048576,16777216")
     ap.add_argument("--batch", type=int, default=1)
@@ -178,4 +203,4 @@ if __name__ == "__main__":
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--length", type=int, default=16 << 20)
     a = ap.parse_args()
-    {"io": cmd_io, "sendrecv": cmd_sendrecv, "rpc": cmd_rpc, "cache": cmd_cache}[a.cmd](a)
+    {"io": cmd_io, "sendrecv": cmd_sendrecv, "rpc": cmd_rpc, "cache": cmd_cache, "torch": cmd_torch}[a.cmd](a)
