@@ -56,7 +56,7 @@ class ExpertParallelMoE:
     """One rank's shard of the MoE layer."""
 
     def __init__(self, cfg: MoEConfig, max_tokens: int, *, group=None, seed: int = 0, buffer: EpBuffer | None = None,
-                 recv_cap: int | None = None, weights=None, recv_grid_rows: int | None = None, thin_waits: bool = False,
+                 recv_cap: int | None = None, weights=None, thin_waits: bool = False,
                  fuse_dequant: bool = False):
         self.cfg = cfg
         self.buf = buffer or EpBuffer(cfg.num_experts, cfg.topk, cfg.hidden, max_tokens, group=group, recv_cap=recv_cap)
@@ -66,7 +66,6 @@ class ExpertParallelMoE:
         if weights is None:
             weights = init_expert_weights(cfg, range(self.rank * epr, (self.rank + 1) * epr), dev, seed)
         self.w_gate_up, self.w_down = weights
-        self.recv_grid_rows = recv_grid_rows  # sizes the grid of the receive kernel (None: by the expected row count)
         # thin_waits: every wait for other ranks is a one-block kernel in front of the large kernel, which then starts
         # with its flags already set and never spins (needed when two chains of kernels share the GPU)
         self.thin_waits = thin_waits
@@ -93,7 +92,7 @@ class ExpertParallelMoE:
         if self.fuse_dequant:
             self.buf.wait(0, epoch)
             return
-        rows = self.recv_grid_rows or min(self.buf.recv_cap, max(1, 2 * T * c.topk))
+        rows = min(self.buf.recv_cap, max(1, 2 * T * c.topk))
         if self.thin_waits:
             self.buf.wait(0, epoch)
         self.buf.recv_dequant(self.xd, epoch, expected_rows=rows)
