@@ -9,6 +9,8 @@
     python bench/profile_case.py moe_step    # one single-GPU MoE layer step (T=1024, 32 experts of the 7168/2048 shape)
     python bench/profile_case.py quant       # fp8 1x128 quantise + dequantise of 16384 x 7168
     python bench/profile_case.py copy        # 1024 x 64 KiB segment batch through the NVLink endpoint (local peer)
+    python bench/profile_case.py kv          # paged KV pack + unpack, 4096 pages of 64 tokens x 512 B rows (K and V)
+    python bench/profile_case.py allgather   # all-gather push of 1024 x 7168 bf16 to 4 emulated ranks on one GPU
 
 Each case holds well under 4 GB on the device and exits by itself in seconds.
 """
@@ -120,7 +122,37 @@ def copy_case():
     b.close()
 
 
+def kv_case():
+    from dlslime_b200.ops import kv
+
+    page, row, pages = 64, 256, 4096  # two KV heads of 128 per rank, as a TP4 shard of an 8-KV-head model
+    tokens = page * pages
+    src = torch.randn(2, tokens, row, device="cuda").to(torch.bfloat16)
+    paged = torch.zeros(2, pages, page, row, device="cuda", dtype=torch.bfloat16)
+    back = torch.empty_like(src)
+    tok_off, blk, ntok = kv.build_page_tasks([tokens], page, torch.randperm(pages).tolist())
+    for _ in range(2):
+        kv.kv_pack(src, paged, tok_off, blk, ntok)
+        kv.kv_unpack(paged, back, tok_off, blk, ntok)
+    torch.cuda.synchronize()
+    assert torch.equal(back, src)
+
+
+def allgather_case():
+    from dlslime_b200.ops.allgather import AllGatherLLBuffer
+
+    world, bs, hidden = 4, 1024, 7168
+    group = AllGatherLLBuffer.emulated_group(world, bs, hidden, torch.bfloat16)
+    xs = [torch.randn(bs, hidden, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    for _ in range(2):
+        hooks = [g.all_gather_ll_hook(x) for g, x in zip(group, xs)]
+        outs = [h() for h in hooks]
+    torch.cuda.synchronize()
+    group[0].status.check()
+    assert torch.equal(outs[0], torch.cat(xs, dim=0))
+
+
 if __name__ == "__main__":
-    {"gemm": gemm_case, "gemm_pair": gemm_pair_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "grouped_stream": grouped_stream_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
+    {"kv": kv_case, "allgather": allgather_case, "gemm": gemm_case, "gemm_pair": gemm_pair_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "grouped_stream": grouped_stream_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
     torch.cuda.synchronize()
     print("done", sys.argv[1])

@@ -12,9 +12,18 @@ namespace slime {
 constexpr float kFp8Max      = 448.0f;
 constexpr float kFp8AmaxFloor = 1e-4f;
 
-__device__ __forceinline__ float fp8_scale_from_amax(float amax)
+// Block scaling: with c = max(amax, floor), scale = c / 448 is what the consumer multiplies by and
+// inv = 448 / c is what the producer multiplies by. Both are IEEE divisions, done once per block, so
+// that the per-element work is one multiply and the result can be restated bit for bit on the host.
+struct Fp8Scale {
+    float scale;
+    float inv;
+};
+
+__device__ __forceinline__ Fp8Scale fp8_scale_from_amax(float amax)
 {
-    return __fdiv_rn(fmaxf(amax, kFp8AmaxFloor), kFp8Max);
+    const float c = fmaxf(amax, kFp8AmaxFloor);
+    return {__fdiv_rn(c, kFp8Max), __fdiv_rn(kFp8Max, c)};
 }
 
 __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* v)
@@ -37,14 +46,14 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float* v)
     return out;
 }
 
-// q[i] = rne_sat(v[i] / scale), eight values packed little-endian.
-__device__ __forceinline__ uint2 quant_fp8x8(const float* v, float scale)
+// q[i] = rne_sat(v[i] * inv), eight values packed little-endian.
+__device__ __forceinline__ uint2 quant_fp8x8(const float* v, float inv)
 {
     uint32_t w[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const float2 a = make_float2(__fdiv_rn(v[4 * h + 0], scale), __fdiv_rn(v[4 * h + 1], scale));
-        const float2 b = make_float2(__fdiv_rn(v[4 * h + 2], scale), __fdiv_rn(v[4 * h + 3], scale));
+        const float2 a = make_float2(__fmul_rn(v[4 * h + 0], inv), __fmul_rn(v[4 * h + 1], inv));
+        const float2 b = make_float2(__fmul_rn(v[4 * h + 2], inv), __fmul_rn(v[4 * h + 3], inv));
         const uint32_t lo = __nv_cvt_float2_to_fp8x2(a, __NV_SATFINITE, __NV_E4M3);
         const uint32_t hi = __nv_cvt_float2_to_fp8x2(b, __NV_SATFINITE, __NV_E4M3);
         w[h]              = lo | (hi << 16);

@@ -250,8 +250,9 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpConfig cfg, const __
             for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
 #pragma unroll
             for (int o = 4; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 8));
-            const float scale = fp8_scale_from_amax(amax);
-            const uint2 q0 = quant_fp8x8(v, scale), q1 = quant_fp8x8(v + 8, scale);
+            const Fp8Scale fs    = fp8_scale_from_amax(amax);
+            const float    scale = fs.scale;
+            const uint2 q0 = quant_fp8x8(v, fs.inv), q1 = quant_fp8x8(v + 8, fs.inv);
             const uint4 q  = make_uint4(q0.x, q0.y, q1.x, q1.y);
             for (int k = 0; k < K; ++k) {
                 const int e = topk_idx[t * K + k];

@@ -1,8 +1,8 @@
 // Block-scaled fp8 e4m3 quantisation and dequantisation.
 //   1x128   : one fp32 scale per 128 consecutive elements of a row (activations)
 //   128x128 : one fp32 scale per 128x128 tile (weights)
-// scale = max(amax, 1e-4) / 448, q = rne_sat(x / scale). Vector kernels, bound by
-// HBM bandwidth: 16-byte loads, 8-byte fp8 stores, amax by shuffles.
+// With c = max(amax, 1e-4): scale = c / 448, q = rne_sat(x * (448 / c)). Vector kernels, bound by
+// HBM bandwidth: 16-byte loads, 8-byte fp8 stores, amax by shuffles, one multiply per element.
 #include "common/fp8.cuh"
 #include "common/host_utils.h"
 #include "slime_cuda.h"
@@ -11,43 +11,88 @@ using namespace slime;
 
 namespace {
 
-// 16 threads cover one 128-element group (8 bf16 each).
+// 16 lanes cover one 128-element group (8 bf16 each); a warp covers 2 * kGroupsPerLane consecutive groups
+// and issues all of its loads before it uses any of them. kContig: both matrices are dense (pitch == cols), so a
+// group's offset is its index times 128 and no row / column split (a 64-bit division) is needed.
+constexpr int kGroupsPerLane = 2;
+
+template<bool kContig>
+__device__ __forceinline__ void group_offsets(long long gid, int groups_per_row, long long ld_a, long long ld_b,
+                                              long long& off_a, long long& off_b)
+{
+    if (kContig) {
+        off_a = off_b = gid * 128;
+    }
+    else {
+        const long long row = gid / groups_per_row;
+        const long long col = (gid - row * groups_per_row) * 128;
+        off_a               = row * ld_a + col;
+        off_b               = row * ld_b + col;
+    }
+}
+
+template<bool kContig>
 __global__ void __launch_bounds__(256) quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                                                          float* __restrict__ scales, long long n_groups,
                                                          int groups_per_row, long long ldx, long long ldq)
 {
-    const long long gid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
-    const int       sub = threadIdx.x & 15;
-    if (gid >= n_groups) return;  // whole 16-lane segments leave together
-    const long long row = gid / groups_per_row;
-    const int       grp = static_cast<int>(gid - row * groups_per_row);
-    const uint4     raw = *reinterpret_cast<const uint4*>(x + row * ldx + grp * 128 + sub * 8);
-    float           v[8];
-    unpack_bf16x8(raw, v);
-    float amax = 0.f;
+    const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int       half = (threadIdx.x >> 4) & 1, sub = threadIdx.x & 15;
+    long long       gid[kGroupsPerLane], ox[kGroupsPerLane], oq[kGroupsPerLane];
+    uint4           raw[kGroupsPerLane];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    for (int j = 0; j < kGroupsPerLane; ++j) {
+        gid[j] = warp * (2 * kGroupsPerLane) + 2 * j + half;
+        raw[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (gid[j] < n_groups) {
+            group_offsets<kContig>(gid[j], groups_per_row, ldx, ldq, ox[j], oq[j]);
+            raw[j] = *reinterpret_cast<const uint4*>(x + ox[j] + sub * 8);
+        }
+    }
 #pragma unroll
-    for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 16));
-    const float scale = fp8_scale_from_amax(amax);
-    *reinterpret_cast<uint2*>(q + row * ldq + grp * 128 + sub * 8) = quant_fp8x8(v, scale);
-    if (sub == 0) scales[gid] = scale;
+    for (int j = 0; j < kGroupsPerLane; ++j) {
+        float v[8];
+        unpack_bf16x8(raw[j], v);
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+        for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 16));  // all 32 lanes take part
+        if (gid[j] < n_groups) {
+            const Fp8Scale fs = fp8_scale_from_amax(amax);
+            *reinterpret_cast<uint2*>(q + oq[j] + sub * 8) = quant_fp8x8(v, fs.inv);
+            if (sub == 0) scales[gid[j]] = fs.scale;
+        }
+    }
 }
 
+template<bool kContig>
 __global__ void __launch_bounds__(256) dequant_1x128_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scales,
                                                            __nv_bfloat16* __restrict__ y, long long n_groups,
                                                            int groups_per_row, long long ldq, long long ldy)
 {
-    const long long gid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
-    const int       sub = threadIdx.x & 15;
-    if (gid >= n_groups) return;
-    const long long row   = gid / groups_per_row;
-    const int       grp   = static_cast<int>(gid - row * groups_per_row);
-    const uint2     raw   = *reinterpret_cast<const uint2*>(q + row * ldq + grp * 128 + sub * 8);
-    const float     scale = scales[gid];
-    float           v[8];
-    dequant_fp8x8(raw, scale, v);
-    *reinterpret_cast<uint4*>(y + row * ldy + grp * 128 + sub * 8) = pack_bf16x8(v);
+    const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int       half = (threadIdx.x >> 4) & 1, sub = threadIdx.x & 15;
+    long long       gid[kGroupsPerLane], oq[kGroupsPerLane], oy[kGroupsPerLane];
+    uint2           raw[kGroupsPerLane];
+    float           scale[kGroupsPerLane];
+#pragma unroll
+    for (int j = 0; j < kGroupsPerLane; ++j) {
+        gid[j] = warp * (2 * kGroupsPerLane) + 2 * j + half;
+        if (gid[j] < n_groups) {
+            group_offsets<kContig>(gid[j], groups_per_row, ldq, ldy, oq[j], oy[j]);
+            raw[j]   = *reinterpret_cast<const uint2*>(q + oq[j] + sub * 8);
+            scale[j] = scales[gid[j]];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kGroupsPerLane; ++j) {
+        if (gid[j] < n_groups) {
+            float v[8];
+            dequant_fp8x8(raw[j], scale[j], v);
+            *reinterpret_cast<uint4*>(y + oy[j] + sub * 8) = pack_bf16x8(v);
+        }
+    }
 }
 
 // One CTA (256 threads) per 128x128 tile: thread t handles row t/2, 64 columns.
@@ -83,13 +128,13 @@ __global__ void __launch_bounds__(256) quant_128x128_kernel(const __nv_bfloat16*
     amax = warp_max[0];
 #pragma unroll
     for (int i = 1; i < 8; ++i) amax = fmaxf(amax, warp_max[i]);
-    const float scale = fp8_scale_from_amax(amax);
-    if (threadIdx.x == 0) scales[static_cast<long long>(tile_r) * gridDim.x + tile_c] = scale;
+    const Fp8Scale fs = fp8_scale_from_amax(amax);
+    if (threadIdx.x == 0) scales[static_cast<long long>(tile_r) * gridDim.x + tile_c] = fs.scale;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int c = c0 + i * 8;
         if (in && c < cols)
-            *reinterpret_cast<uint2*>(q + static_cast<long long>(r) * ldq + c) = quant_fp8x8(v + i * 8, scale);
+            *reinterpret_cast<uint2*>(q + static_cast<long long>(r) * ldq + c) = quant_fp8x8(v + i * 8, fs.inv);
     }
 }
 
@@ -104,8 +149,11 @@ int slime_fp8_quant_1x128(const void* x, void* q, float* scales, long long rows,
     if (ldx % 8 != 0 || ldq % 8 != 0) return fail("fp8 quant: row pitches must be multiples of 8 elements");
     if (rows <= 0) return 0;
     const long long n_groups = rows * (cols / 128);
-    const long long blocks   = (n_groups * 16 + 255) / 256;
-    quant_1x128_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    const long long per_block = 256 / 16 * kGroupsPerLane;
+    const long long blocks    = (n_groups + per_block - 1) / per_block;
+    if (blocks > 0x7fffffffLL) return fail("fp8 quant: %lld groups exceed one launch", n_groups);
+    auto kernel = (ldx == cols && ldq == cols) ? quant_1x128_kernel<true> : quant_1x128_kernel<false>;
+    kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scales, n_groups, cols / 128, ldx, ldq);
     SLIME_CUDA_OK(cudaGetLastError());
     return 0;
@@ -118,8 +166,11 @@ int slime_fp8_dequant_1x128(const void* q, const float* scales, void* y, long lo
     if (ldy % 8 != 0 || ldq % 8 != 0) return fail("fp8 dequant: row pitches must be multiples of 8 elements");
     if (rows <= 0) return 0;
     const long long n_groups = rows * (cols / 128);
-    const long long blocks   = (n_groups * 16 + 255) / 256;
-    dequant_1x128_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    const long long per_block = 256 / 16 * kGroupsPerLane;
+    const long long blocks    = (n_groups + per_block - 1) / per_block;
+    if (blocks > 0x7fffffffLL) return fail("fp8 dequant: %lld groups exceed one launch", n_groups);
+    auto kernel = (ldq == cols && ldy == cols) ? dequant_1x128_kernel<true> : dequant_1x128_kernel<false>;
+    kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint8_t*>(q), scales, static_cast<__nv_bfloat16*>(y), n_groups, cols / 128, ldq, ldy);
     SLIME_CUDA_OK(cudaGetLastError());
     return 0;

@@ -1,6 +1,7 @@
 """Block-scaled fp8 e4m3 quantisation (1x128 activations, 128x128 weights).
 
-scale = max(amax, 1e-4) / 448 in fp32; q = round-to-nearest-even, saturating.
+With c = max(amax, 1e-4) in fp32: scale = c / 448 and q = rne_sat(x * (448 / c)), i.e. two IEEE divisions
+per block and one multiply per element; round-to-nearest-even, saturating.
 The kernels are ``csrc/kernels/fp8_quant.cu``; the PyTorch functions below
 restate the same arithmetic in fp32 and are the oracle the tests compare against.
 """
@@ -59,8 +60,10 @@ def fp8_quant_128x128(w: torch.Tensor):
 def ref_quant_1x128(x: torch.Tensor):
     xf = x.float().reshape(x.shape[0], -1, 128)
     amax = xf.abs().amax(dim=-1).clamp_min(AMAX_FLOOR)
-    scale = amax / torch.full_like(amax, FP8_MAX)  # tensor / tensor: IEEE division, not a reciprocal multiply
-    q = (xf / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    # tensor / tensor: IEEE divisions, once per group; elements are then multiplied, exactly as the kernels do
+    scale = amax / torch.full_like(amax, FP8_MAX)
+    inv = torch.full_like(amax, FP8_MAX) / amax
+    q = (xf * inv.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     return q.reshape(x.shape), scale
 
 
@@ -77,5 +80,6 @@ def ref_quant_128x128(w: torch.Tensor):
     blocks = wf.reshape(pr // 128, 128, pc // 128, 128)
     amax = blocks.abs().amax(dim=(1, 3)).clamp_min(AMAX_FLOOR)
     scale = amax / torch.full_like(amax, FP8_MAX)
-    q = (blocks / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    inv = torch.full_like(amax, FP8_MAX) / amax
+    q = (blocks * inv[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     return q.reshape(pr, pc)[:rows, :cols].contiguous(), scale
