@@ -320,13 +320,16 @@ __global__ void __launch_bounds__(256) ep_recv_dequant_kernel(EpConfig cfg, cons
     const float*    sc   = at<float>(cfg, cfg.rank, cfg.off_scale);
     for (long long gid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4; gid < n;
          gid += (static_cast<long long>(gridDim.x) * blockDim.x) >> 4) {
-        const int       sub = threadIdx.x & 15;
-        const long long row = gid / gpr;
-        const int       grp = static_cast<int>(gid - row * gpr);
-        const uint2     raw = *reinterpret_cast<const uint2*>(q + row * cfg.hidden + grp * 128 + sub * 8);
-        float           v[8];
+        const int sub = threadIdx.x & 15;
+        long long oq = gid * 128, oy = gid * 128;  // dense output: a group's offset is its index times 128
+        if (ldy != cfg.hidden) {
+            const long long row = gid / gpr;
+            oy                  = row * ldy + (gid - row * gpr) * 128;
+        }
+        const uint2 raw = *reinterpret_cast<const uint2*>(q + oq + sub * 8);
+        float       v[8];
         dequant_fp8x8(raw, sc[gid], v);
-        *reinterpret_cast<uint4*>(y + row * ldy + grp * 128 + sub * 8) = pack_bf16x8(v);
+        *reinterpret_cast<uint4*>(y + oy + sub * 8) = pack_bf16x8(v);
     }
 }
 
@@ -383,28 +386,34 @@ __global__ void __launch_bounds__(256) ep_combine_reduce_kernel(EpConfig cfg, in
     if (!wait_all_ranks(cfg, cfg.off_combine_done, epoch, st, 50)) return;
     const int       H = cfg.hidden, K = cfg.topk;
     const int       chunks = H / 256;
-    const long long units  = static_cast<long long>(T) * chunks;
-    const int       warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned int units = static_cast<unsigned int>(T) * static_cast<unsigned int>(chunks);
+    const int          warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const __nv_bfloat16* buf = at<__nv_bfloat16>(cfg, cfg.rank, cfg.off_combine);
-    for (long long u = static_cast<long long>(blockIdx.x) * 8 + warp; u < units; u += static_cast<long long>(gridDim.x) * 8) {
-        const int t = static_cast<int>(u / chunks);
-        const int c = static_cast<int>(u - static_cast<long long>(t) * chunks);
-        float     acc[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (unsigned int u = blockIdx.x * 8u + warp; u < units; u += gridDim.x * 8u) {
+        const int t = static_cast<int>(u / static_cast<unsigned int>(chunks));
+        const int c = static_cast<int>(u - static_cast<unsigned int>(t) * static_cast<unsigned int>(chunks));
+        // The row pieces are fetched whether or not their slot is in use (the slot exists in the buffer either way), so
+        // that the eight loads do not wait for the index loads; an unused slot is skipped when the sum is formed.
         uint4 part[kMaxTopk];
+        int   idx[kMaxTopk];
+        float wgt[kMaxTopk];
 #pragma unroll
         for (int k = 0; k < kMaxTopk; ++k)
-            if (k < K && topk_idx[t * K + k] >= 0)
+            if (k < K) {
                 part[k] = *reinterpret_cast<const uint4*>(buf + (static_cast<long long>(t) * K + k) * H + c * 256 + lane * 8);
+                idx[k]  = topk_idx[t * K + k];
+                wgt[k]  = topk_w[t * K + k];
+            }
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 #pragma unroll
         for (int k = 0; k < kMaxTopk; ++k) {
-            if (k < K && topk_idx[t * K + k] >= 0) {
-                const float w = topk_w[t * K + k];
-                float       v[8];
+            if (k < K && idx[k] >= 0) {
+                float v[8];
                 unpack_bf16x8(part[k], v);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[i] = fmaf(w, v[i], acc[i]);
+                for (int i = 0; i < 8; ++i) acc[i] = fmaf(wgt[k], v[i], acc[i]);
             }
         }
         *reinterpret_cast<uint4*>(out + t * ldo + c * 256 + lane * 8) = pack_bf16x8(acc);
