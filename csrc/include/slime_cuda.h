@@ -120,6 +120,13 @@ unsigned long long slime_nvlink_ep_remote_addr(void* ep, int handle);
 int slime_nvlink_ep_transfer(void* ep, const unsigned long long* tuples, int n, int is_write, void* signal,
                              unsigned long long signal_value, int signal_add, int max_blocks, void* stream);
 
+// One contiguous piece with scalar arguments: a copy-engine (DMA) copy in stream order, then the completion word.
+// slime_nvlink_ep_transfer takes the same route by itself for up to four pieces that are one piece or all >= 4 MiB
+// (SLIME_NVLINK_NO_COPY_ENGINE in the environment keeps every batch on the kernels).
+int slime_nvlink_ep_copy1(void* ep, long long local_handle, long long remote_handle, unsigned long long remote_offset,
+                          unsigned long long local_offset, unsigned long long length, int is_write, void* signal,
+                          unsigned long long signal_value, void* stream);
+
 // ---- low-latency all-gather (allgather.cu) -----------------------------------
 int slime_ag_config_size(void);
 int slime_ag_push(const void* cfg_bytes, const void* src, unsigned long long bytes, unsigned long long stride_bytes,

@@ -388,6 +388,58 @@ unsigned long long slime_nvlink_ep_remote_addr(void* h, int handle)
     return ep->remote[handle].addr;
 }
 
+// Few, large pieces are a job for the copy engines: no SM is occupied, nothing is staged, and for one contiguous
+// region a DMA copy is a few percent faster than any kernel (it has no tail and no launch-shaped ramp). The kernels
+// take over where the copy engines lose: many pieces, each of which would cost one host call and one DMA set-up.
+constexpr int                kCopyEngineMaxSegs  = 4;
+constexpr unsigned long long kCopyEngineMinBytes = 4ull << 20;
+
+static bool copy_engine_enabled()
+{
+    static const bool off = std::getenv("SLIME_NVLINK_NO_COPY_ENGINE") != nullptr;
+    return !off;
+}
+
+// Checks one assignment against its regions and resolves it to device addresses (ep->mu held by the caller).
+static int resolve_segment(Endpoint* ep, int index, long long lh, long long rh, unsigned long long roff,
+                           unsigned long long loff, unsigned long long len, int is_write, unsigned long long* dst,
+                           unsigned long long* src)
+{
+    if (lh < 0 || lh >= static_cast<long long>(ep->local.size()) || !ep->local[lh].alive)
+        return fail("nvlink endpoint: assignment %d names unknown local region %lld", index, lh);
+    if (rh < 0 || rh >= static_cast<long long>(ep->remote.size()) || !ep->remote[rh].alive)
+        return fail("nvlink endpoint: assignment %d names unknown remote region %lld", index, rh);
+    const Region& L = ep->local[lh];
+    const Region& R = ep->remote[rh];
+    if (loff + len > L.length || roff + len > R.length)
+        return fail("nvlink endpoint: assignment %d exceeds a region (local %llu+%llu of %llu, remote %llu+%llu of %llu)", index,
+                    loff, len, L.length, roff, len, R.length);
+    *dst = is_write ? R.addr + roff : L.addr + loff;
+    *src = is_write ? L.addr + loff : R.addr + roff;
+    return 0;
+}
+
+// One contiguous piece, arguments as scalars (no table to build on the caller's side): a DMA copy in stream order,
+// followed by the completion word if one is asked for.
+int slime_nvlink_ep_copy1(void* h, long long local_handle, long long remote_handle, unsigned long long remote_offset,
+                          unsigned long long local_offset, unsigned long long length, int is_write, void* signal,
+                          unsigned long long signal_value, void* stream_v)
+{
+    Endpoint*          ep     = static_cast<Endpoint*>(h);
+    cudaStream_t       stream = static_cast<cudaStream_t>(stream_v);
+    unsigned long long dst = 0, src = 0;
+    {
+        std::lock_guard<std::mutex> g(ep->mu);
+        if (resolve_segment(ep, 0, local_handle, remote_handle, remote_offset, local_offset, length, is_write, &dst, &src))
+            return -1;
+    }
+    if (length)
+        SLIME_CUDA_OK(cudaMemcpyAsync(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src), length,
+                                      cudaMemcpyDeviceToDevice, stream));
+    if (signal) return slime_signal_flag_kernel(signal, signal_value, 0, stream_v);
+    return 0;
+}
+
 // One batched transfer. tuples = n x {local_handle, remote_handle, remote_offset, local_offset, length}
 // (the assignment tuple order of the endpoint API). is_write: local -> remote, else remote -> local.
 // signal (optional) receives signal_value (store, or add when signal_add) after the last byte.
@@ -397,9 +449,31 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
     Endpoint*    ep     = static_cast<Endpoint*>(h);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     if (n < 0) return fail("nvlink endpoint: negative batch size");
+    if (n == 0 && signal == nullptr) return 0;
+    if (n >= 1 && n <= kCopyEngineMaxSegs && copy_engine_enabled()) {
+        bool large = true;
+        for (int i = 0; i < n; ++i) large = large && (n == 1 || tuples[5ull * i + 4] >= kCopyEngineMinBytes);
+        if (large) {
+            unsigned long long dst[kCopyEngineMaxSegs], src[kCopyEngineMaxSegs];
+            {
+                std::lock_guard<std::mutex> g(ep->mu);
+                for (int i = 0; i < n; ++i) {
+                    const unsigned long long* t = tuples + 5ull * i;
+                    if (resolve_segment(ep, i, static_cast<long long>(t[0]), static_cast<long long>(t[1]), t[2], t[3], t[4],
+                                        is_write, &dst[i], &src[i]))
+                        return -1;
+                }
+            }
+            for (int i = 0; i < n; ++i)
+                if (tuples[5ull * i + 4])
+                    SLIME_CUDA_OK(cudaMemcpyAsync(reinterpret_cast<void*>(dst[i]), reinterpret_cast<const void*>(src[i]),
+                                                  tuples[5ull * i + 4], cudaMemcpyDeviceToDevice, stream));
+            if (signal) return slime_signal_flag_kernel(signal, signal_value, signal_add, stream_v);
+            return 0;
+        }
+    }
     if (ensure_staging(ep)) return -1;
     int done = 0;
-    if (n == 0 && signal == nullptr) return 0;
     do {
         const int          batch = std::min(n - done, kStagingEntries);
         InlineBatch        inl{};
@@ -421,20 +495,11 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
             std::lock_guard<std::mutex> g(ep->mu);
             for (int i = 0; i < batch; ++i) {
                 const unsigned long long* t  = tuples + 5ull * (done + i);
-                const long long           lh = static_cast<long long>(t[0]), rh = static_cast<long long>(t[1]);
-                if (lh < 0 || lh >= static_cast<long long>(ep->local.size()) || !ep->local[lh].alive)
-                    return fail("nvlink endpoint: assignment %d names unknown local region %lld", done + i, lh);
-                if (rh < 0 || rh >= static_cast<long long>(ep->remote.size()) || !ep->remote[rh].alive)
-                    return fail("nvlink endpoint: assignment %d names unknown remote region %lld", done + i, rh);
-                const Region& L = ep->local[lh];
-                const Region& R = ep->remote[rh];
-                const unsigned long long roff = t[2], loff = t[3], len = t[4];
-                if (loff + len > L.length || roff + len > R.length)
-                    return fail("nvlink endpoint: assignment %d exceeds a region (local %llu+%llu of %llu, remote %llu+%llu of %llu)",
-                                done + i, loff, len, L.length, roff, len, R.length);
-                Segment& s   = seg_out[i];
-                s.dst        = is_write ? R.addr + roff : L.addr + loff;
-                s.src        = is_write ? L.addr + loff : R.addr + roff;
+                const unsigned long long  len = t[4];
+                Segment&                  s   = seg_out[i];
+                if (resolve_segment(ep, done + i, static_cast<long long>(t[0]), static_cast<long long>(t[1]), t[2], t[3], len,
+                                    is_write, &s.dst, &s.src))
+                    return -1;
                 s.len        = len;
                 if (((s.dst | s.src | len) & 15ull) != 0) all_aligned = false;
                 s.first_unit = units;

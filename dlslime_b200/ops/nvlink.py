@@ -38,6 +38,8 @@ _lib.declare("slime_nvlink_ep_local_info", [_v, _i, _ubp, _ullp, _ullp, _ullp])
 _lib.declare("slime_nvlink_ep_register_remote", [_v, _cp, _ubp, _ull, _ull, _ull, _i])
 _lib.declare("slime_nvlink_ep_handle", [_v, _cp, _i])
 _lib.declare("slime_nvlink_ep_transfer", [_v, _v, _i, _i, _v, _ull, _i, _i, _v])
+_ll = ctypes.c_longlong
+_lib.declare("slime_nvlink_ep_copy1", [_v, _ll, _ll, _ull, _ull, _ull, _i, _v, _ull, _v])
 
 IMM_RING = 1024  # immediate values a peer may have outstanding before the receiver consumes them
 
@@ -76,6 +78,7 @@ class NVLinkEndpoint:
         lib.slime_nvlink_ep_remote_addr.restype = ctypes.c_ulonglong
         lib.slime_nvlink_ep_remote_addr.argtypes = [_v, _i]
         self._h = lib.slime_nvlink_ep_create()
+        self._copy1 = lib.slime_nvlink_ep_copy1
         self._names: dict[int, str] = {}
         self._pid = os.getpid()
         self._uid = f"{self._pid}:{id(self):x}"
@@ -154,8 +157,22 @@ class NVLinkEndpoint:
         return arr
 
     def _transfer(self, assign, is_write: bool, stream, want_future: bool = True, max_blocks: int = 0):
-        arr = assign if isinstance(assign, np.ndarray) else self._resolve(assign)
         sp = stream_ptr() if stream is None else int(getattr(stream, "cuda_stream", stream))
+        if type(assign) is list and len(assign) == 1 and type(assign[0][0]) is int and max_blocks == 0:
+            # one contiguous piece by handle: scalar arguments, no table, a copy-engine copy
+            lh, rh, roff, loff, length = assign[0]
+            flag_dev, seq, fut = None, 0, None
+            if want_future:
+                i = self._next_flag
+                self._next_flag = (i + 1) % 256
+                seq = self._flag_seq[i] = self._flag_seq[i] + 1
+                flag_dev = self._flags_dev + 8 * i
+                fut = NVLinkFuture(self._flags_host, i, seq, sp)
+            if self._copy1(self._h, lh, rh, roff, loff, length, int(is_write), flag_dev, seq, sp) < 0:
+                msg = _lib.load().slime_last_error()
+                raise _lib.SlimeCudaError(f"slime_nvlink_ep_copy1: {msg.decode(errors='replace') if msg else 'unknown error'}")
+            return fut if fut is not None else NVLinkFuture(None, 0, 0, sp)
+        arr = assign if isinstance(assign, np.ndarray) else self._resolve(assign)
         if want_future:
             i = self._next_flag
             self._next_flag = (self._next_flag + 1) % 256

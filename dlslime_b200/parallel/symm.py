@@ -11,11 +11,18 @@ out-of-band channel can carry them as well, see ``export_info`` / ``connect``.
 ``SymmetricHeap.emulated(n)`` creates ``n`` regions on ONE device. That mode backs
 the single-GPU tests of multi-rank protocols: kernels are replayed rank by rank
 and every wait finds its flag already published.
+
+Guard bands (debugging aid, ``SLIME_HEAP_GUARD=1`` in the environment of EVERY rank, since
+offsets must stay identical across ranks): each reservation is followed by a 256-byte band
+filled with ``0xA5`` (one more band sits in front of the first reservation);
+``check_guards()`` lists the bands of this rank's region(s) that no longer hold the pattern, i.e.
+where a kernel of this or of another rank wrote outside its buffer.
 """
 
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Sequence
 
 import torch
@@ -41,13 +48,20 @@ def _align(x: int, a: int) -> int:
     return (x + a - 1) // a * a
 
 
+GUARD_BYTES = 256
+GUARD_BYTE = 0xA5
+_GUARD_SLACK = 64 << 10  # room for 256 bands on top of what the caller asked for
+
+
 class SymmetricHeap:
     """A region of ``nbytes`` on every rank plus the peer mappings."""
 
     def __init__(self, nbytes: int, group=None, _emulated_world: int = 0):
         import torch.distributed as dist
 
-        self.nbytes = _align(int(nbytes), 1 << 21)
+        self.guard = os.environ.get("SLIME_HEAP_GUARD", "0") not in ("", "0")
+        self.nbytes = _align(int(nbytes) + (_GUARD_SLACK if self.guard else 0), 1 << 21)
+        self._guards: list[int] = []
         self._owned: list[int] = []
         self._opened: list[int] = []
         self._cursor = 0
@@ -106,11 +120,35 @@ class SymmetricHeap:
     # -- carving --------------------------------------------------------------
     def reserve(self, nbytes: int, align: int = 256) -> int:
         """Reserve ``nbytes`` at the same offset on every rank; returns the offset."""
+        if self.guard and not self._guards:
+            self._place_guard(0)
+            self._cursor = GUARD_BYTES
         off = _align(self._cursor, align)
-        if off + nbytes > self.nbytes:
-            raise MemoryError(f"symmetric heap exhausted: need {off + nbytes}, have {self.nbytes}")
-        self._cursor = off + nbytes
+        end = off + nbytes
+        if self.guard:
+            end = _align(end, 16) + GUARD_BYTES
+        if end > self.nbytes:
+            raise MemoryError(f"symmetric heap exhausted: need {end}, have {self.nbytes}")
+        if self.guard:
+            self._place_guard(end - GUARD_BYTES)
+        self._cursor = end
         return off
+
+    def _place_guard(self, off: int) -> None:
+        self._guards.append(off)
+        for p in self._owned:
+            tensor_from_ptr(p + off, GUARD_BYTES).fill_(GUARD_BYTE)
+
+    def check_guards(self) -> list[tuple[int, int]]:
+        """``(region index, band offset)`` of every damaged guard band in the regions this process owns
+        (one region, or all of them for an emulated group). Synchronises the device."""
+        torch.cuda.synchronize()
+        bad = []
+        for i, p in enumerate(self._owned):
+            for off in self._guards:
+                if not bool((tensor_from_ptr(p + off, GUARD_BYTES) == GUARD_BYTE).all()):
+                    bad.append((i, off))
+        return bad
 
     def view(self, offset: int, shape, dtype: torch.dtype, rank: int | None = None) -> torch.Tensor:
         """Tensor view of ``[offset, offset + prod(shape) * itemsize)`` in rank ``rank``'s region."""
@@ -128,6 +166,9 @@ class SymmetricHeap:
         for p in self._owned:
             _lib.call("slime_memset_async", ctypes.c_void_p(p), 0, self.nbytes, None)
         torch.cuda.synchronize()
+        for p in self._owned:
+            for off in self._guards:
+                tensor_from_ptr(p + off, GUARD_BYTES).fill_(GUARD_BYTE)
 
     def close(self) -> None:
         torch.cuda.synchronize()

@@ -49,6 +49,16 @@ def check_endpoint(rank, world):
             expect[loff:loff + ln] = peer_orig[roff:roff + ln]
         torch.cuda.synchronize()
         assert torch.equal(buf, expect), "endpoint bulk read mismatch"
+        # one contiguous piece at odd offsets (the copy-engine route), by name and by handle
+        one = ("buffer", "buffer", half + 12345, (3 << 20) + 7, 1_000_001)
+        assert ep.read([one]).wait() == 0
+        lh, rh = ep.get_mr_handle("buffer"), ep.get_remote_mr_handle("buffer")
+        two = (lh, rh, half + 77, (3 << 20) - 4099, 4096)
+        assert ep.read([two]).wait() == 0
+        for _, _, roff, loff, ln in (one, two):
+            expect[loff:loff + ln] = peer_orig[roff:roff + ln]
+        torch.cuda.synchronize()
+        assert torch.equal(buf, expect), "endpoint single-piece read mismatch"
     dist.barrier()
     if rank < peer:
         # write with immediate data: push my lower half into the peer's lower half, then notify
@@ -64,6 +74,7 @@ def check_endpoint(rank, world):
         psegs.append((half + (1 << 20), 1 << 20, 1 << 20))
         psegs += [(half + (1 << 20) + 65536 * ((7 * i) % 40), (2 << 20) + 65536 * i, 65536) for i in range(20)]
         psegs += [(half + 4096, 4096, 200 << 10), (half + 16, 1 << 19, 48)]
+        psegs += [(half + 12345, (3 << 20) + 7, 1_000_001), (half + 77, (3 << 20) - 4099, 4096)]
         pbuf = peer_orig.clone()
         for roff, loff, ln in psegs:
             pbuf[loff:loff + ln] = orig[roff:roff + ln]
