@@ -7,6 +7,7 @@ Cases (shapes from the benchmark definition of this project):
   p2p        NVLink endpoint: contiguous read and write 8 B ... 1 GiB between rank pairs (r, r^1), and a batched
              scatter of 4096 x 64 KiB segments at permuted offsets; baseline = one cudaMemcpyAsync per segment
              (what the reference's NVLinkEndpoint.read does per assignment).
+  p2p_scatter  only the batched scatter of the p2p case.
   allgather  low-latency all-gather of [T, 7168] bf16, T in {1, 16, 128, 1024}; baseline = NCCL all_gather_into_tensor.
   ag_gemm_fp8  the same shape in e4m3 with 1x128 / 128x128 block scales (fp8 payload + scales cross NVLink)
   ag_gemm    per-rank [1024, 8192] bf16 gathered and multiplied by W[28672 / world, 8192]; fused kernel vs
@@ -65,7 +66,7 @@ def emit(rank, **kw):
 
 
 # ------------------------------------------------------------------------------------------ p2p
-def case_p2p(rank, world):
+def case_p2p(rank, world, contiguous=True):
     from dlslime_b200.ops.nvlink import NVLinkEndpoint
 
     peer = rank ^ 1
@@ -91,7 +92,7 @@ def case_p2p(rank, world):
     rbuf, lbuf = ep.get_remote_mr_handle("buf"), ep.get_mr_handle("buf")
     dist.barrier()
     active = rank < peer  # one direction per pair at a time
-    sizes = [8 << i for i in range(0, 28)]  # 8 B ... 1 GiB
+    sizes = [8 << i for i in range(0, 28)] if contiguous else []  # 8 B ... 1 GiB
     for op in ("read", "write"):
         for n in sizes:
             iters = 200 if n <= (1 << 20) else 20 if n <= (1 << 26) else 5
@@ -366,7 +367,7 @@ def main():
     os.environ.setdefault("MASTER_PORT", "29650")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local), rank=rank, world_size=world)
     for case in sys.argv[1:]:
-        {"p2p": case_p2p, "allgather": case_allgather, "ag_gemm": case_ag_gemm, "ag_gemm_fp8": case_ag_gemm_fp8, "kv": case_kv}[case](rank, world)
+        {"p2p": case_p2p, "p2p_scatter": lambda r, w: case_p2p(r, w, contiguous=False), "allgather": case_allgather, "ag_gemm": case_ag_gemm, "ag_gemm_fp8": case_ag_gemm_fp8, "kv": case_kv}[case](rank, world)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -500,12 +500,13 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
                 if (resolve_segment(ep, done + i, static_cast<long long>(t[0]), static_cast<long long>(t[1]), t[2], t[3], len,
                                     is_write, &s.dst, &s.src))
                     return -1;
-                s.len        = len;
+                s.len = len;
                 if (((s.dst | s.src | len) & 15ull) != 0) all_aligned = false;
-                s.first_unit = units;
-                units += (len + kUnitBytes - 1) / kUnitBytes;
-                if (len == 0) units += 0;
             }
+        }
+        for (int i = 0; i < batch; ++i) {
+            seg_out[i].first_unit = units;
+            units += (seg_out[i].len + kUnitBytes - 1) / kUnitBytes;
         }
         CopyArgs a{};
         a.n_seg   = batch;

@@ -42,8 +42,10 @@ def test_stray_write_is_reported(monkeypatch):
     b = heap.reserve(4096)
     assert a == GUARD_BYTES and b >= a + 1000 + GUARD_BYTES
     assert heap.check_guards() == []
-    # one element past the end of the first reservation, in the second rank's region (memory this heap owns)
-    heap.view(a, (1008,), torch.uint8, rank=1)[1007] = 0
+    # an overrun of the first reservation (rounded up to 16 bytes) by one byte, in the second rank's region;
+    # the byte belongs to this heap, so nothing outside it is touched
+    overrun = heap.view(a, (1009,), torch.uint8, rank=1)
+    overrun[1008] = 0
     bad = heap.check_guards()
     assert bad == [(1, heap._guards[1])]
     heap.close()
