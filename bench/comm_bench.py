@@ -9,6 +9,7 @@ Cases (shapes from the benchmark definition of this project):
              (what the reference's NVLinkEndpoint.read does per assignment).
   p2p_scatter  only the batched scatter of the p2p case.
   allgather  low-latency all-gather of [T, 7168] bf16, T in {1, 16, 128, 1024}; baseline = NCCL all_gather_into_tensor.
+  alltoall   low-latency all-to-all of [world * T, 7168] bf16, T in {1, 16, 128, 512}; baseline = NCCL all_to_all_single.
   ag_gemm_fp8  the same shape in e4m3 with 1x128 / 128x128 block scales (fp8 payload + scales cross NVLink)
   ag_gemm    per-rank [1024, 8192] bf16 gathered and multiplied by W[28672 / world, 8192]; fused kernel vs
              NCCL all-gather + torch.matmul (cuBLAS).
@@ -63,6 +64,25 @@ def timed(fn, iters, warmup=3, sync=None):
 def emit(rank, **kw):
     if rank == 0:
         print(json.dumps(kw), flush=True)
+
+
+# ------------------------------------------------------------------------------------------ all-to-all
+def case_alltoall(rank, world):
+    """Low-latency all-to-all of [world * T, 7168] bf16 (T rows to every rank) against NCCL all_to_all_single."""
+    from dlslime_b200.ops.alltoall import AllToAllLLBuffer
+
+    hidden = 7168
+    a2a = AllToAllLLBuffer(512, hidden, torch.bfloat16)
+    for T in (1, 16, 128, 512):
+        x = torch.randn(world * T, hidden, device="cuda").to(torch.bfloat16)
+        ref = torch.empty_like(x)
+        ms = max_ms(timed(lambda: a2a.all_to_all_ll(x), 200, sync=dist.barrier), world)
+        dist.barrier()
+        base = max_ms(timed(lambda: dist.all_to_all_single(ref, x), 200, sync=dist.barrier), world)
+        a2a.status.check()
+        nbytes = T * hidden * 2 * (world - 1)
+        emit(rank, case="ll_alltoall", T=T, world=world, us=round(ms * 1e3, 2), nccl_us=round(base * 1e3, 2), speedup=round(base / ms, 2),
+             send_gbs_per_rank=round(nbytes / ms / 1e6, 1), frac_of_nvlink=round(nbytes / ms / 1e6 / NVLINK_GBS, 3))
 
 
 # ------------------------------------------------------------------------------------------ p2p
@@ -367,7 +387,7 @@ def main():
     os.environ.setdefault("MASTER_PORT", "29650")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local), rank=rank, world_size=world)
     for case in sys.argv[1:]:
-        {"p2p": case_p2p, "p2p_scatter": lambda r, w: case_p2p(r, w, contiguous=False), "allgather": case_allgather, "ag_gemm": case_ag_gemm, "ag_gemm_fp8": case_ag_gemm_fp8, "kv": case_kv}[case](rank, world)
+        {"p2p": case_p2p, "p2p_scatter": lambda r, w: case_p2p(r, w, contiguous=False), "allgather": case_allgather, "alltoall": case_alltoall, "ag_gemm": case_ag_gemm, "ag_gemm_fp8": case_ag_gemm_fp8, "kv": case_kv}[case](rank, world)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -120,6 +120,12 @@ unsigned long long slime_nvlink_ep_remote_addr(void* ep, int handle);
 int slime_nvlink_ep_transfer(void* ep, const unsigned long long* tuples, int n, int is_write, void* signal,
                              unsigned long long signal_value, int signal_add, int max_blocks, void* stream);
 
+// ---- low-latency all-to-all (alltoall.cu): same configuration bytes as the all-gather -----------------------------
+int slime_a2a_push(const void* cfg_bytes, const void* src, unsigned long long row_bytes, int rows_total, int bs, int max_rows,
+                   int transpose, const int* offsets, const int* mask, unsigned long long step, unsigned int* block_counter,
+                   int do_wait, int max_blocks, void* status, void* stream);
+int slime_a2a_wait(const void* cfg_bytes, unsigned long long step, void* status, void* stream);
+
 // One contiguous piece with scalar arguments: a copy-engine (DMA) copy in stream order, then the completion word.
 // slime_nvlink_ep_transfer takes the same route by itself for up to four pieces that are one piece or all >= 4 MiB
 // (SLIME_NVLINK_NO_COPY_ENGINE in the environment keeps every batch on the kernels).

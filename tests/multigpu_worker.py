@@ -103,6 +103,38 @@ def check_allgather(rank, world):
     dist.barrier()
 
 
+def check_alltoall(rank, world):
+    from dlslime_b200.ops.alltoall import AllToAllLLBuffer
+
+    hidden, cap = 2048, 256
+    a2a = AllToAllLLBuffer(cap, hidden, torch.bfloat16)
+    for step, bs in enumerate([1, 16, 256, 16]):
+        x = torch.randn((world * bs, hidden), device="cuda").to(torch.bfloat16) + rank
+        ref = torch.empty_like(x)
+        dist.all_to_all_single(ref, x)
+        out = a2a.all_to_all_ll(x) if step % 2 == 0 else a2a.all_to_all_ll_hook(x)()
+        torch.cuda.synchronize()
+        a2a.status.check()
+        assert torch.equal(out, ref), f"all-to-all mismatch at bs={bs}"
+        out_t = a2a.all_to_all_ll(x, is_transpose=True)
+        torch.cuda.synchronize()
+        assert torch.equal(out_t, ref.view(world, bs, hidden).transpose(0, 1)), f"transposed all-to-all mismatch at bs={bs}"
+    # variable split: rank r sends (r + p) % 5 rows to rank p
+    sizes = [(rank + p) % 5 for p in range(world)]
+    offs = torch.tensor([sum(sizes[:p]) for p in range(world + 1)], dtype=torch.int32, device="cuda")
+    x = torch.randn((max(sum(sizes), 1), hidden), device="cuda").to(torch.bfloat16)[:sum(sizes)].contiguous()
+    recv_sizes = [(s + rank) % 5 for s in range(world)]
+    ref = torch.empty((sum(recv_sizes), hidden), dtype=torch.bfloat16, device="cuda")
+    dist.all_to_all_single(ref, x, output_split_sizes=recv_sizes, input_split_sizes=sizes)
+    data, counts = a2a.all_to_all_ll(x, offsets=offs)
+    torch.cuda.synchronize()
+    a2a.status.check()
+    assert counts.tolist() == recv_sizes, (counts.tolist(), recv_sizes)
+    got = torch.cat([data[s, :recv_sizes[s]] for s in range(world)], dim=0)
+    assert torch.equal(got, ref), "variable all-to-all mismatch"
+    dist.barrier()
+
+
 def check_moe(rank, world):
     from dlslime_b200.models.moe import ExpertParallelMoE, MoEConfig, init_expert_weights, ref_moe_forward
 
@@ -233,7 +265,7 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    which = sys.argv[1:] or ["endpoint", "allgather", "moe", "moe_tbo", "ag_gemm", "ag_gemm_fp8", "kv"]
+    which = sys.argv[1:] or ["endpoint", "allgather", "alltoall", "moe", "moe_tbo", "ag_gemm", "ag_gemm_fp8", "kv"]
     for name in which:
         globals()[f"check_{name}"](rank, world)
         if rank == 0:
