@@ -39,3 +39,22 @@ def get_cmake_dir() -> str:
     import os
 
     return os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc", "include")
+
+
+_LAZY_OPS = {
+    # names of the reference's collective buffers (bound in its `_slime_c` when the ops are built); they need CUDA,
+    # so they are imported on first use
+    "AllGatherInterLLBuffer": ("ops.allgather", "AllGatherLLBuffer"),
+    "AllGatherLLBuffer": ("ops.allgather", "AllGatherLLBuffer"),
+    "AllToAllIntraLLBuffer": ("ops.alltoall", "AllToAllLLBuffer"),
+    "AllToAllLLBuffer": ("ops.alltoall", "AllToAllLLBuffer"),
+}
+
+
+def __getattr__(name: str):
+    target = _LAZY_OPS.get(name)
+    if target is None:
+        raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+    import importlib
+
+    return getattr(importlib.import_module(f"{__name__}.{target[0]}"), target[1])

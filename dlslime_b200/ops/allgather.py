@@ -116,3 +116,7 @@ class AllGatherLLBuffer:
             return self._result(step, bs)
 
         return hook
+
+
+# name of the reference's class
+AllGatherInterLLBuffer = AllGatherLLBuffer

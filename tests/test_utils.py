@@ -53,3 +53,21 @@ def test_dram_pool_blocks_when_full_and_wakes_on_release():
     pool.release(a)
     t.join(5)
     assert got == [a]
+
+
+def test_collective_buffer_names_of_the_reference_resolve():
+    import dlslime_b200 as dlslime
+    from dlslime_b200.ops.allgather import AllGatherLLBuffer
+    from dlslime_b200.ops.alltoall import AllToAllLLBuffer
+
+    assert dlslime.AllGatherInterLLBuffer is AllGatherLLBuffer
+    assert dlslime.AllToAllIntraLLBuffer is AllToAllLLBuffer
+    for name in ("buffer_info", "connect_full_mesh", "get_local_buffer", "get_buffer_size_hint", "set_max_bs", "all_to_all_ll"):
+        assert callable(getattr(AllToAllLLBuffer, name))
+    for name in ("buffer_info", "connect_full_mesh", "all_gather_ll", "all_gather_ll_hook"):
+        assert callable(getattr(AllGatherLLBuffer, name))
+    assert AllToAllLLBuffer.get_buffer_size_hint(128, 7168, __import__("torch").bfloat16, 8) == 2 * 8 * 128 * 7168 * 2 + 4096
+    import pytest
+
+    with pytest.raises(AttributeError):
+        dlslime.no_such_name
