@@ -52,6 +52,7 @@ class AllToAllLLBuffer(AllGatherLLBuffer):
         if n * self.msg_size * self.itemsize > self.slot_bytes:
             raise ValueError(f"max_bs={n} needs more than the {self.slot_bytes}-byte slots this buffer was built with")
         self.max_bs = int(n)
+        self._views.clear()
 
     def _flags_view(self, step: int) -> torch.Tensor:
         off = self.off_flags + (step & 1) * self.world * 8
@@ -82,12 +83,20 @@ class AllToAllLLBuffer(AllGatherLLBuffer):
         return self.step, bs
 
     def _a2a_result(self, step: int, bs: int, is_transpose: bool, variable: bool):
-        off = self.off_data + (step & 1) * self.world * self.slot_bytes
+        half = step & 1
+        key = ("a2a", half, bs, is_transpose, variable)
+        v = self._views.get(key)
+        if v is None:  # building a tensor over raw memory is slow; the handful of shapes in use are kept
+            off = self.off_data + half * self.world * self.slot_bytes
+            if variable:
+                v = (self.heap.view(off, (self.world, self.max_bs, self.msg_size), self.dtype, rank=self.rank), self._flags_view(step))
+            else:
+                shape = (bs, self.world, self.msg_size) if is_transpose else (self.world * bs, self.msg_size)
+                v = self.heap.view(off, shape, self.dtype, rank=self.rank)
+            self._views[key] = v
         if variable:
-            data = self.heap.view(off, (self.world, self.max_bs, self.msg_size), self.dtype, rank=self.rank)
-            return data, (self._flags_view(step) & 0xFFFFFFFF).to(torch.int32)
-        shape = (bs, self.world, self.msg_size) if is_transpose else (self.world * bs, self.msg_size)
-        return self.heap.view(off, shape, self.dtype, rank=self.rank)
+            return v[0], (v[1] & 0xFFFFFFFF).to(torch.int32)
+        return v
 
     def all_to_all_ll(self, x: torch.Tensor, is_transpose: bool = False, mask: torch.Tensor | None = None,
                       offsets: torch.Tensor | None = None):

@@ -51,13 +51,19 @@ class NVLinkFuture:
     mapped host memory, so no stream synchronise is needed), or 402 after ``timeout``.
     """
 
-    def __init__(self, flags_host: int | None, index: int, target: int, stream):
+    def __init__(self, flags_host: int | None, index: int, target: int, stream, on_done=None):
         self._host, self._index, self._target, self._stream = flags_host, index, target, stream
+        self._on_done = on_done  # called once, the first time completion is observed (accounting)
 
     def done(self) -> bool:
         if self._host is None:
             return True
-        return ctypes.c_ulonglong.from_address(self._host + 8 * self._index).value >= self._target
+        if ctypes.c_ulonglong.from_address(self._host + 8 * self._index).value < self._target:
+            return False
+        if self._on_done is not None:
+            cb, self._on_done = self._on_done, None
+            cb()
+        return True
 
     def wait(self, timeout: float | None = 30.0) -> int:
         if self._host is None:
@@ -79,6 +85,14 @@ class NVLinkEndpoint:
         lib.slime_nvlink_ep_remote_addr.argtypes = [_v, _i]
         self._h = lib.slime_nvlink_ep_create()
         self._copy1 = lib.slime_nvlink_ep_copy1
+        # Accounting (DLSLIME_OBS=1): this endpoint is one link of kind "nvlink" in the process's counters, with the same
+        # submit / complete semantics per user operation as the RDMA links. Off: one `is None` test per transfer.
+        self._obs_link = None
+        from .. import _slime_c
+
+        if _slime_c.obs_enabled():
+            self._obs = _slime_c
+            self._obs_link = _slime_c.obs_register_link(f"nvlink:gpu{torch.cuda.current_device()}", "nvlink")
         self._names: dict[int, str] = {}
         self._pid = os.getpid()
         self._uid = f"{self._pid}:{id(self):x}"
@@ -156,7 +170,30 @@ class NVLinkEndpoint:
         arr = np.ascontiguousarray(np.asarray(assign, dtype=np.uint64).reshape(-1, 5))
         return arr
 
+    def _account(self, op: int, n: int, nbytes: int, fut: "NVLinkFuture") -> None:
+        """One submit now; the completion when the future first sees its word (at once if there is no word)."""
+        obs, link = self._obs, self._obs_link
+        obs.obs_record_submit(link, op, n, nbytes)
+        if fut._host is None:
+            obs.obs_record_complete(link, op, nbytes)
+        else:
+            fut._on_done = lambda: obs.obs_record_complete(link, op, nbytes)
+
+    @staticmethod
+    def _batch_size(assign) -> tuple[int, int]:
+        if isinstance(assign, np.ndarray):
+            return int(assign.shape[0]), int(assign.reshape(-1, 5)[:, 4].sum())
+        return len(assign), sum(int(a[4]) for a in assign)
+
     def _transfer(self, assign, is_write: bool, stream, want_future: bool = True, max_blocks: int = 0):
+        if self._obs_link is None:
+            return self._transfer_impl(assign, is_write, stream, want_future, max_blocks)
+        n, nbytes = self._batch_size(assign)
+        fut = self._transfer_impl(assign, is_write, stream, want_future, max_blocks)
+        self._account(int(is_write), n, nbytes, fut)  # op indices of the counters: 0 read, 1 write, 2 write_with_imm
+        return fut
+
+    def _transfer_impl(self, assign, is_write: bool, stream, want_future: bool = True, max_blocks: int = 0):
         sp = stream_ptr() if stream is None else int(getattr(stream, "cuda_stream", stream))
         if type(assign) is list and len(assign) == 1 and type(assign[0][0]) is int and max_blocks == 0:
             # one contiguous piece by handle: scalar arguments, no table, a copy-engine copy
@@ -194,7 +231,7 @@ class NVLinkEndpoint:
 
     def write_with_imm(self, assign, imm_data: int = 0, stream=None):
         """``write`` followed, in stream order, by delivery of ``imm_data`` to the peer's ``imm_recv``."""
-        fut = self._transfer(assign, True, stream, want_future=False)
+        fut = self._transfer_impl(assign, True, stream, want_future=False)
         sp = fut._stream
         n = self._imm_sent.get(self._peer_imm, 0)
         base = _lib.load().slime_nvlink_ep_remote_addr(self._h, self._peer_imm)
@@ -205,7 +242,10 @@ class NVLinkEndpoint:
         self._next_flag = (self._next_flag + 1) % 256
         self._flag_seq[i] += 1
         _lib.call("slime_signal_flag_kernel", self._flags_dev + 8 * i, self._flag_seq[i], 0, sp)
-        return NVLinkFuture(self._flags_host, i, self._flag_seq[i], sp)
+        out = NVLinkFuture(self._flags_host, i, self._flag_seq[i], sp)
+        if self._obs_link is not None:
+            self._account(2, *self._batch_size(assign), out)
+        return out
 
     def imm_recv(self, timeout: float = 30.0) -> tuple[int, int]:
         """Wait for the next immediate value from the connected peer. Returns (status, imm_data)."""

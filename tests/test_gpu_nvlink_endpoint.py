@@ -89,3 +89,41 @@ def test_write_with_imm_after_single_piece(pair):
     fut = ep.write_with_imm([(lh, rh, 64, 128, 4096)], imm_data=0xC0DE)
     assert fut.wait(10.0) == 0
     assert torch.equal(theirs, expect)
+
+
+def test_transfers_are_accounted_as_an_nvlink_link():
+    """With the counters on, an endpoint is one link of kind "nvlink": one submit per user operation, completed bytes
+    when the future first sees its word."""
+    from dlslime_b200 import _slime_c
+    from dlslime_b200.ops.nvlink import NVLinkEndpoint
+
+    _slime_c.obs_set_enabled_for_test(True)
+    _slime_c.obs_reset_for_test()
+    try:
+        size = 1 << 20
+        mine = torch.zeros(size, dtype=torch.uint8, device="cuda")
+        theirs = torch.randint(0, 255, (size,), dtype=torch.uint8, device="cuda")
+        a, b = NVLinkEndpoint(), NVLinkEndpoint()
+        a.register_memory_region(mine.data_ptr(), 0, size, "buf")
+        b.register_memory_region(theirs.data_ptr(), 0, size, "buf")
+        a.connect(b.endpoint_info())
+        lh, rh = a.get_mr_handle("buf"), a.get_remote_mr_handle("buf")
+        fut = a.read([(lh, rh, 4096 * i, 4096 * i, 1000 + i) for i in range(3)])
+        assert fut.wait(10.0) == 0
+        assert a.write([(lh, rh, 0, 0, 512)]).wait(10.0) == 0
+        assert a.write_with_imm([(lh, rh, 8192, 8192, 64)], imm_data=7).wait(10.0) == 0
+        a.read([(lh, rh, 0, 0, 256)], want_future=False)
+        torch.cuda.synchronize()
+        snap = _slime_c.obs_snapshot()
+        link = next(n for n in snap["nics"] if n["nic"] == f"nvlink:gpu{torch.cuda.current_device()}")
+        assert link["kind"] == "nvlink"
+        rd, wr, wi = link["by_op"]["read"], link["by_op"]["write"], link["by_op"]["write_with_imm"]
+        assert (rd["batch"], rd["assign"], rd["submitted_bytes"], rd["completed_bytes"]) == (2, 4, 3003 + 256, 3003 + 256)
+        assert (wr["batch"], wr["assign"], wr["completed_bytes"]) == (1, 1, 512)
+        assert (wi["batch"], wi["assign"], wi["completed_bytes"]) == (1, 1, 64)
+        assert link["pending_ops"] == 0 and snap["summary"]["pending_ops"] == 0
+        a.close()
+        b.close()
+    finally:
+        _slime_c.obs_reset_for_test()
+        _slime_c.obs_set_enabled_for_test(False)
