@@ -11,6 +11,7 @@
     python bench/profile_case.py copy        # 1024 x 64 KiB segment batch through the NVLink endpoint (local peer)
     python bench/profile_case.py kv          # paged KV pack + unpack, 4096 pages of 64 tokens x 512 B rows (K and V)
     python bench/profile_case.py allgather   # all-gather push of 1024 x 7168 bf16 to 4 emulated ranks on one GPU
+    python bench/profile_case.py alltoall    # all-to-all of 4 x 512 x 7168 bf16 among 4 emulated ranks on one GPU
 
 Each case holds well under 4 GB on the device and exits by itself in seconds.
 """
@@ -152,7 +153,21 @@ def allgather_case():
     assert torch.equal(outs[0], torch.cat(xs, dim=0))
 
 
+def alltoall_case():
+    from dlslime_b200.ops.alltoall import AllToAllLLBuffer
+
+    world, bs, hidden = 4, 512, 7168
+    group = AllToAllLLBuffer.emulated_group(world, bs, hidden, torch.bfloat16)
+    xs = [torch.randn(world * bs, hidden, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    for _ in range(2):
+        hooks = [g.all_to_all_ll_hook(x) for g, x in zip(group, xs)]
+        outs = [h() for h in hooks]
+    torch.cuda.synchronize()
+    group[0].status.check()
+    assert torch.equal(outs[1], torch.cat([x[bs:2 * bs] for x in xs], dim=0))
+
+
 if __name__ == "__main__":
-    {"kv": kv_case, "allgather": allgather_case, "gemm": gemm_case, "gemm_pair": gemm_pair_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "grouped_stream": grouped_stream_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
+    {"alltoall": alltoall_case, "kv": kv_case, "allgather": allgather_case, "gemm": gemm_case, "gemm_pair": gemm_pair_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "grouped_stream": grouped_stream_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
     torch.cuda.synchronize()
     print("done", sys.argv[1])

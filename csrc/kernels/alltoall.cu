@@ -70,22 +70,37 @@ __global__ void __launch_bounds__(256) a2a_push_kernel(A2aConfig cfg, A2aArgs a,
     for (int p = 0; p < cfg.world; ++p) total += s_rows[p];
     const unsigned int ppr   = static_cast<unsigned int>((vpr + 31) / 32);
     const unsigned int units = static_cast<unsigned int>(total) * ppr;
-    for (unsigned int u = blockIdx.x * 8u + warp; u < units; u += gridDim.x * 8u) {
-        const unsigned int w = u / ppr;
-        const int          v = static_cast<int>(u - w * ppr) * 32 + lane;
-        int                p = 0, b = static_cast<int>(w);
-        while (b >= s_rows[p]) b -= s_rows[p++];  // at most world - 1 steps
-        unsigned long long out_row;
-        if (a.offsets)
-            out_row = static_cast<unsigned long long>(cfg.rank) * a.max_rows + b;
-        else if (a.transpose)
-            out_row = static_cast<unsigned long long>(b) * cfg.world + cfg.rank;
-        else
-            out_row = static_cast<unsigned long long>(cfg.rank) * a.bs + b;
-        if (v < vpr) {
-            const uint4 x = a.src[static_cast<unsigned long long>(s_begin[p] + b) * vpr + v];
-            reinterpret_cast<uint4*>(cfg.peers[p] + base + out_row * a.row_bytes)[v] = x;
+    // four pieces per pass: all loads are issued before the first store, so that a warp has 2 KiB in flight
+    constexpr int      kPieces = 4;
+    const unsigned int stride  = gridDim.x * 8u;
+    for (unsigned int u0 = blockIdx.x * 8u + warp; u0 < units; u0 += stride * kPieces) {
+        uint4  x[kPieces];
+        uint4* to[kPieces];
+#pragma unroll
+        for (int j = 0; j < kPieces; ++j) {
+            const unsigned int u = u0 + j * stride;
+            to[j]                = nullptr;
+            if (u < units) {
+                const unsigned int w = u / ppr;
+                const int          v = static_cast<int>(u - w * ppr) * 32 + lane;
+                int                p = 0, b = static_cast<int>(w);
+                while (b >= s_rows[p]) b -= s_rows[p++];  // at most world - 1 steps
+                unsigned long long out_row;
+                if (a.offsets)
+                    out_row = static_cast<unsigned long long>(cfg.rank) * a.max_rows + b;
+                else if (a.transpose)
+                    out_row = static_cast<unsigned long long>(b) * cfg.world + cfg.rank;
+                else
+                    out_row = static_cast<unsigned long long>(cfg.rank) * a.bs + b;
+                if (v < vpr) {
+                    x[j]  = a.src[static_cast<unsigned long long>(s_begin[p] + b) * vpr + v];
+                    to[j] = reinterpret_cast<uint4*>(cfg.peers[p] + base + out_row * a.row_bytes) + v;
+                }
+            }
         }
+#pragma unroll
+        for (int j = 0; j < kPieces; ++j)
+            if (to[j]) *to[j] = x[j];
     }
     __shared__ bool is_last;
     __syncthreads();
