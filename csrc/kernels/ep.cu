@@ -54,7 +54,29 @@ struct EpConfig {
     // to *epoch_ptr (route passes 1 and stores the new value when its last CTA finishes, the kernels that
     // follow pass 0), so a whole step can be replayed from a CUDA graph with nothing changing on the host.
     unsigned long long epoch_ptr;
+    // Optional trace page (u64 [16][4], device memory; 0 = off). Rows 0..4 belong to the kernels that wait for other
+    // ranks {dispatch, receive, combine, wait, barrier}: {calls, start of the last call (globaltimer ns), time the last
+    // call waited, total time waited}. Rows 8..15: {rows pushed to peer p so far, calls}. Written by thread 0 of
+    // block 0 only; kernels of one buffer run in stream order, so there is nothing to synchronise.
+    unsigned long long trace_ptr;
 };
+
+enum TraceRow { kTraceDispatch = 0, kTraceReceive = 1, kTraceCombine = 2, kTraceWait = 3, kTraceBarrier = 4, kTracePeers = 8 };
+
+__device__ __forceinline__ bool tracing(const EpConfig& c)
+{
+    return c.trace_ptr != 0 && blockIdx.x == 0 && threadIdx.x == 0;
+}
+
+__device__ __forceinline__ void trace_waited(const EpConfig& c, int row, unsigned long long t0)
+{
+    unsigned long long*      r   = reinterpret_cast<unsigned long long*>(c.trace_ptr) + 4 * row;
+    const unsigned long long dt  = globaltimer_ns() - t0;
+    r[0] += 1;
+    r[1] = t0;
+    r[2] = dt;
+    r[3] += dt;
+}
 
 __device__ __forceinline__ unsigned long long resolve_epoch(const EpConfig& c, unsigned long long arg)
 {
@@ -190,6 +212,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpConfig cfg, const __
 
     epoch = resolve_epoch(cfg, epoch);
     if (threadIdx.x == 0) s_ok = 1;
+    const unsigned long long trace_t0 = tracing(cfg) ? globaltimer_ns() : 0;
     __syncthreads();
     // 1. wait for the W count rows of this epoch and derive the layout
     const unsigned long long* counts = at<unsigned long long>(cfg, cfg.rank, cfg.off_counts);
@@ -217,6 +240,16 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpConfig cfg, const __
         s_before[e] = before;
     }
     __syncthreads();
+    if (tracing(cfg)) {
+        trace_waited(cfg, kTraceDispatch, trace_t0);
+        unsigned long long* peers_row = reinterpret_cast<unsigned long long*>(cfg.trace_ptr) + 4 * kTracePeers;
+        for (int p = 0; p < W; ++p) {
+            unsigned long long rows = 0;
+            for (int e = p * El; e < (p + 1) * El; ++e) rows += counts[cfg.rank * E + e] & 0xffffffffull;
+            peers_row[4 * p] += rows;
+            peers_row[4 * p + 1] += 1;
+        }
+    }
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         const int    first = (e / El) * El;
         unsigned int off   = 0;
@@ -312,7 +345,9 @@ __global__ void __launch_bounds__(256) ep_recv_dequant_kernel(EpConfig cfg, cons
                                                              unsigned long long epoch, KernelStatus* st)
 {
     epoch = resolve_epoch(cfg, epoch);
+    const unsigned long long trace_t0 = tracing(cfg) ? globaltimer_ns() : 0;
     if (!wait_all_ranks(cfg, cfg.off_dispatch_done, epoch, st, 30)) return;
+    if (tracing(cfg)) trace_waited(cfg, kTraceReceive, trace_t0);
     const int       rows = group_offsets[cfg.experts_per_rank];
     const int       gpr  = cfg.hidden / 128;
     const long long n    = static_cast<long long>(rows) * gpr;
@@ -383,7 +418,9 @@ __global__ void __launch_bounds__(256) ep_combine_reduce_kernel(EpConfig cfg, in
         fence_acq_rel_sys();
         st_release_sys(at<unsigned long long>(cfg, threadIdx.x, cfg.off_combine_done) + cfg.rank, epoch);
     }
+    const unsigned long long trace_t0 = tracing(cfg) ? globaltimer_ns() : 0;
     if (!wait_all_ranks(cfg, cfg.off_combine_done, epoch, st, 50)) return;
+    if (tracing(cfg)) trace_waited(cfg, kTraceCombine, trace_t0);
     const int       H = cfg.hidden, K = cfg.topk;
     const int       chunks = H / 256;
     const unsigned int units = static_cast<unsigned int>(T) * static_cast<unsigned int>(chunks);
@@ -426,7 +463,9 @@ __global__ void __launch_bounds__(256) ep_combine_reduce_kernel(EpConfig cfg, in
 __global__ void ep_wait_kernel(EpConfig cfg, unsigned long long off, unsigned long long epoch, KernelStatus* st)
 {
     epoch = resolve_epoch(cfg, epoch);
+    const unsigned long long trace_t0 = tracing(cfg) ? globaltimer_ns() : 0;
     wait_all_ranks(cfg, off, epoch, st, 55);
+    if (tracing(cfg)) trace_waited(cfg, kTraceWait, trace_t0);
 }
 
 __global__ void ep_barrier_kernel(EpConfig cfg, unsigned long long epoch, KernelStatus* st)
@@ -435,7 +474,9 @@ __global__ void ep_barrier_kernel(EpConfig cfg, unsigned long long epoch, Kernel
         fence_acq_rel_sys();
         st_release_sys(at<unsigned long long>(cfg, threadIdx.x, cfg.off_barrier) + cfg.rank, epoch);
     }
+    const unsigned long long trace_t0 = tracing(cfg) ? globaltimer_ns() : 0;
     wait_all_ranks(cfg, cfg.off_barrier, epoch, st, 60);
+    if (tracing(cfg)) trace_waited(cfg, kTraceBarrier, trace_t0);
 }
 
 int check_cfg(const EpConfig& c)

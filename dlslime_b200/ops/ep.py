@@ -18,7 +18,7 @@ from .. import _lib
 from ..parallel.symm import SymmetricHeap
 from ._common import default_status, ptr, stream_ptr
 
-_CFG_FMT = "<8i8Q8QQQ"
+_CFG_FMT = "<8i8Q8QQQQ"
 
 
 @dataclass
@@ -105,6 +105,7 @@ class EpBuffer:
         self.group_offsets = torch.zeros(self.experts_per_rank + 1, dtype=torch.int32, device=dev)
         # Device-resident step counter for graph-replayable steps (methods called with epoch=None use it).
         self.epoch_dev = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.trace = None  # device trace page, see enable_device_trace
         self._cfg = self._pack_cfg()
         self._cfg_dev = self._pack_cfg(self.epoch_dev.data_ptr())
         self.status = default_status()
@@ -118,7 +119,33 @@ class EpBuffer:
             _CFG_FMT, self.rank, self.world, self.num_experts, self.experts_per_rank, self.topk, self.hidden,
             self.max_tokens, self.recv_cap,
             b + L.off_counts, b + L.off_dispatch_done, b + L.off_combine_done, b + L.off_barrier,
-            b + L.off_x, b + L.off_scale, b + L.off_info, b + L.off_combine, *peers, self.wait_ns, epoch_ptr)
+            b + L.off_x, b + L.off_scale, b + L.off_info, b + L.off_combine, *peers, self.wait_ns, epoch_ptr,
+            self.trace.data_ptr() if self.trace is not None else 0)
+
+    # -- device trace ---------------------------------------------------------------
+    _TRACE_KERNELS = ("dispatch", "receive", "combine", "wait", "barrier")
+
+    def enable_device_trace(self, on: bool = True) -> None:
+        """Let the kernels of this buffer that wait for other ranks record, in device memory, when they last started
+        and how long they waited (``globaltimer`` nanoseconds), and let dispatch count the rows it pushes to each
+        peer. Costs one predictable branch per kernel when off. A step captured in a CUDA graph before this call keeps
+        the setting it was captured with."""
+        self.trace = torch.zeros(64, dtype=torch.int64, device=self.epoch_dev.device) if on else None
+        self._cfg = self._pack_cfg()
+        self._cfg_dev = self._pack_cfg(self.epoch_dev.data_ptr())
+
+    def device_trace(self) -> dict:
+        """Snapshot of the trace page (synchronises the device): per kernel ``{calls, last_start_ns, last_wait_ns,
+        total_wait_ns}``, and per peer the rows and bytes (fp8 payload + scales + source word) dispatched so far."""
+        if self.trace is None:
+            raise RuntimeError("device trace is off; call enable_device_trace() first")
+        t = self.trace.cpu().view(16, 4).tolist()
+        row_bytes = self.hidden + self.hidden // 128 * 4 + 8
+        out = {name: dict(zip(("calls", "last_start_ns", "last_wait_ns", "total_wait_ns"), t[i]))
+               for i, name in enumerate(self._TRACE_KERNELS)}
+        out["peers"] = [{"rank": p, "rows": t[8 + p][0], "bytes": t[8 + p][0] * row_bytes, "steps": t[8 + p][1]}
+                        for p in range(self.world)]
+        return out
 
     @classmethod
     def emulated_group(cls, world: int, num_experts: int, topk: int, hidden: int, max_tokens: int,

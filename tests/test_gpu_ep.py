@@ -136,3 +136,34 @@ def test_moe_layer_with_fused_dequant_matches_the_two_pass_layer():
         torch.cuda.synchronize()
         plain.buf.status.check()
         assert torch.equal(a, b), (a.float() - b.float()).abs().max().item()
+
+
+def test_device_trace_counts_rows_and_waits():
+    """The optional trace page: rows pushed per peer add up to tokens x top-k, every waiting kernel reports its calls."""
+    from dlslime_b200.models.moe import ExpertParallelMoE, MoEConfig, emulated_forward
+    from dlslime_b200.ops.ep import EpBuffer
+
+    world, tokens = 2, [20, 7]
+    cfg = MoEConfig(num_experts=32, topk=4, hidden=1024, intermediate=256)
+    bufs = EpBuffer.emulated_group(world, cfg.num_experts, cfg.topk, cfg.hidden, max(tokens))
+    for b in bufs:
+        b.enable_device_trace()
+    layers = [ExpertParallelMoE(cfg, max(tokens), buffer=b, seed=3) for b in bufs]
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    steps = 3
+    for _ in range(steps):
+        xs = [torch.randn((t, cfg.hidden), generator=gen, device="cuda").to(torch.bfloat16) for t in tokens]
+        lgs = [torch.randn((t, cfg.num_experts), generator=gen, device="cuda") for t in tokens]
+        emulated_forward(layers, xs, lgs)
+    torch.cuda.synchronize()
+    for r, b in enumerate(bufs):
+        tr = b.device_trace()
+        assert sum(p["rows"] for p in tr["peers"]) == steps * tokens[r] * cfg.topk
+        assert all(p["steps"] == steps for p in tr["peers"])
+        assert tr["peers"][0]["bytes"] == tr["peers"][0]["rows"] * (1024 + 8 * 4 + 8)
+        for k in ("dispatch", "receive", "combine"):
+            assert tr[k]["calls"] == steps and tr[k]["last_start_ns"] > 0
+            assert 0 <= tr[k]["last_wait_ns"] <= tr[k]["total_wait_ns"] < 10**9
+    bufs[0].enable_device_trace(False)
+    with pytest.raises(RuntimeError):
+        bufs[0].device_trace()
