@@ -11,8 +11,8 @@ using namespace slime;
 
 namespace {
 
-// 16 lanes cover one 128-element group (8 bf16 each); a warp covers 2 * kGroupsPerLane consecutive groups
-// and issues all of its loads before it uses any of them. kContig: both matrices are dense (pitch == cols), so a
+// Dequantisation: 16 lanes cover one 128-element group (8 values each); a warp covers 2 * kGroupsPerLane consecutive
+// groups and issues all of its loads before it uses any of them. kContig: both matrices are dense (pitch == cols), so a
 // group's offset is its index times 128 and no row / column split (a 64-bit division) is needed.
 constexpr int kGroupsPerLane = 2;
 
@@ -31,36 +31,44 @@ __device__ __forceinline__ void group_offsets(long long gid, int groups_per_row,
     }
 }
 
+// Quantisation: 8 lanes per group, each with elements [8 s, 8 s + 8) and [64 + 8 s, 64 + 8 s + 8) of it, so every load
+// and store instruction of a warp touches whole 128-byte (64-byte for fp8) runs, and the per-group work (three
+// shuffle steps, two divisions) is shared by 16 elements per lane instead of 8. A warp covers 4 * kQuantPasses groups.
+constexpr int kQuantPasses = 2;
+
 template<bool kContig>
 __global__ void __launch_bounds__(256) quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                                                          float* __restrict__ scales, long long n_groups,
                                                          int groups_per_row, long long ldx, long long ldq)
 {
     const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    const int       half = (threadIdx.x >> 4) & 1, sub = threadIdx.x & 15;
-    long long       gid[kGroupsPerLane], ox[kGroupsPerLane], oq[kGroupsPerLane];
-    uint4           raw[kGroupsPerLane];
+    const int       quad = (threadIdx.x >> 3) & 3, sub = threadIdx.x & 7;
+    long long       gid[kQuantPasses], ox[kQuantPasses], oq[kQuantPasses];
+    uint4           lo[kQuantPasses], hi[kQuantPasses];
 #pragma unroll
-    for (int j = 0; j < kGroupsPerLane; ++j) {
-        gid[j] = warp * (2 * kGroupsPerLane) + 2 * j + half;
-        raw[j] = make_uint4(0u, 0u, 0u, 0u);
+    for (int j = 0; j < kQuantPasses; ++j) {
+        gid[j] = warp * (4 * kQuantPasses) + 4 * j + quad;
+        lo[j] = hi[j] = make_uint4(0u, 0u, 0u, 0u);
         if (gid[j] < n_groups) {
             group_offsets<kContig>(gid[j], groups_per_row, ldx, ldq, ox[j], oq[j]);
-            raw[j] = *reinterpret_cast<const uint4*>(x + ox[j] + sub * 8);
+            lo[j] = *reinterpret_cast<const uint4*>(x + ox[j] + sub * 8);
+            hi[j] = *reinterpret_cast<const uint4*>(x + ox[j] + 64 + sub * 8);
         }
     }
 #pragma unroll
-    for (int j = 0; j < kGroupsPerLane; ++j) {
-        float v[8];
-        unpack_bf16x8(raw[j], v);
+    for (int j = 0; j < kQuantPasses; ++j) {
+        float v[16];
+        unpack_bf16x8(lo[j], v);
+        unpack_bf16x8(hi[j], v + 8);
         float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
 #pragma unroll
-        for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 16));  // all 32 lanes take part
+        for (int o = 4; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 8));  // all 32 lanes take part
         if (gid[j] < n_groups) {
             const Fp8Scale fs = fp8_scale_from_amax(amax);
-            *reinterpret_cast<uint2*>(q + oq[j] + sub * 8) = quant_fp8x8(v, fs.inv);
+            *reinterpret_cast<uint2*>(q + oq[j] + sub * 8)      = quant_fp8x8(v, fs.inv);
+            *reinterpret_cast<uint2*>(q + oq[j] + 64 + sub * 8) = quant_fp8x8(v + 8, fs.inv);
             if (sub == 0) scales[gid[j]] = fs.scale;
         }
     }
@@ -149,7 +157,7 @@ int slime_fp8_quant_1x128(const void* x, void* q, float* scales, long long rows,
     if (ldx % 8 != 0 || ldq % 8 != 0) return fail("fp8 quant: row pitches must be multiples of 8 elements");
     if (rows <= 0) return 0;
     const long long n_groups = rows * (cols / 128);
-    const long long per_block = 256 / 16 * kGroupsPerLane;
+    const long long per_block = 256 / 8 * kQuantPasses;
     const long long blocks    = (n_groups + per_block - 1) / per_block;
     if (blocks > 0x7fffffffLL) return fail("fp8 quant: %lld groups exceed one launch", n_groups);
     auto kernel = (ldx == cols && ldq == cols) ? quant_1x128_kernel<true> : quant_1x128_kernel<false>;
