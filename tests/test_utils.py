@@ -71,3 +71,33 @@ def test_collective_buffer_names_of_the_reference_resolve():
 
     with pytest.raises(AttributeError):
         dlslime.no_such_name
+
+
+def test_names_in_the_documentation_resolve():
+    """Every dotted ``dlslime_b200.…`` name in the documentation and the README is importable."""
+    import importlib
+    import pathlib
+    import re
+
+    root = pathlib.Path(__file__).resolve().parent.parent
+    files = [root / "README.md", *sorted((root / "docs").rglob("*.md"))]
+    names = set()
+    for f in files:
+        names.update(re.findall(r"\bdlslime_b200(?:\.[A-Za-z_][A-Za-z0-9_]*)+", f.read_text()))
+    assert len(names) > 10
+    missing = []
+    for name in sorted(names):
+        parts = name.split(".")
+        obj, i = None, len(parts)
+        while i > 0:  # longest importable module prefix, then attributes
+            try:
+                obj = importlib.import_module(".".join(parts[:i]))
+                break
+            except ImportError:
+                i -= 1
+        try:
+            for attr in parts[i:]:
+                obj = getattr(obj, attr)
+        except AttributeError:
+            missing.append(name)
+    assert not missing, f"documented names that do not exist: {missing}"
