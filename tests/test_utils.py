@@ -101,3 +101,24 @@ def test_names_in_the_documentation_resolve():
         except AttributeError:
             missing.append(name)
     assert not missing, f"documented names that do not exist: {missing}"
+
+
+def test_bench_reports_unavailable_without_a_gpu():
+    """On a host without CUDA both arms of bench.py print one JSON line saying so and exit 0."""
+    import json
+    import pathlib
+    import subprocess
+    import sys
+
+    import pytest
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present; the benchmark itself runs under the gpu marker's tier")
+    root = pathlib.Path(__file__).resolve().parent.parent
+    for impl in ("ours", "reference"):
+        res = subprocess.run([sys.executable, str(root / "bench.py"), "--impl", impl, "--steps", "1", "--warmup", "3"],
+                             capture_output=True, text=True, timeout=300)
+        assert res.returncode == 0, res.stderr[-2000:]
+        line = json.loads(res.stdout.strip().splitlines()[-1])
+        assert line["impl"] == impl and "unavailable" in line
