@@ -19,6 +19,7 @@ using namespace slime;
 void bind_rpc(py::module_& m);
 void bind_ctrl(py::module_& m);
 void bind_extra_transports(py::module_& m);
+void bind_bridge(py::module_& m);
 
 static void bind_cache(py::module_& m)
 {
@@ -265,4 +266,5 @@ PYBIND11_MODULE(_slime_c, m)
     bind_rpc(m);
     bind_ctrl(m);
     bind_extra_transports(m);
+    bind_bridge(m);
 }

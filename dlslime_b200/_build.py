@@ -182,9 +182,51 @@ def build_stress(sanitizer: str, verbose: bool = False) -> Path:
     return exe
 
 
+def torch_plugin_path() -> Path:
+    return PKG / ("_slime_torch" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+
+
+def build_torch_plugin(verbose: bool = False) -> Path | None:
+    """The C++ ``torch.distributed`` backend (csrc/torch/slime_backend.cpp): built against the installed torch with
+    torch's own ABI settings. It reaches the runtime through the C table of ``slime_bridge.h`` only, so it links
+    libtorch and nothing of this package. Returns None when torch is not importable."""
+    src = CSRC / "torch" / "slime_backend.cpp"
+    out = torch_plugin_path()
+    if not src.exists():
+        return None
+    try:
+        import torch
+        from torch.utils import cpp_extension as ce
+    except Exception:
+        return None
+    dep = max(src.stat().st_mtime, (CSRC / "include" / "slime_bridge.h").stat().st_mtime)
+    stamp = OBJ / "torch" / "built_for"
+    tag = f"{torch.__version__}"
+    if out.exists() and out.stat().st_mtime >= dep and stamp.exists() and stamp.read_text() == tag:
+        return out
+    (OBJ / "torch").mkdir(parents=True, exist_ok=True)
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else os.environ.get("CXX", "g++")
+    inc = [*ce.include_paths(), sysconfig.get_paths()["include"], str(CSRC / "include")]
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    defs = ["-DTORCH_EXTENSION_NAME=_slime_torch", "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={abi}"]
+    for name in ("COMPILER_TYPE", "STDLIB", "BUILD_ABI"):
+        val = getattr(torch._C, f"_PYBIND11_{name}", None)
+        if val is not None:
+            defs.append(f'-DPYBIND11_{name}="{val}"')
+    libdirs = ce.library_paths()
+    obj = OBJ / "torch" / "slime_backend.o"
+    _run([cxx, "-O2", "-g0", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread", "-Wno-unused-function", *defs,
+          *sum((["-isystem", str(i)] for i in inc), []), "-c", str(src), "-o", str(obj)], verbose)
+    _run([cxx, "-shared", "-o", str(out), str(obj), *sum((["-L", d] for d in libdirs), []),
+          *sum(([f"-Wl,-rpath,{d}"] for d in libdirs), []), "-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python", "-pthread"], verbose)
+    stamp.write_text(tag)
+    return out
+
+
 def build_all(verbose: bool = False) -> None:
     build_cuda(verbose=verbose)
     build_host(verbose=verbose)
+    build_torch_plugin(verbose=verbose)
 
 
 if __name__ == "__main__":
@@ -195,6 +237,9 @@ if __name__ == "__main__":
         build_cuda(verbose=v)
     elif "--host" in sys.argv:
         build_host(verbose=v)
+    elif "--torch" in sys.argv:
+        print("built:", build_torch_plugin(verbose=True))
+        sys.exit(0)
     else:
         build_all(verbose=v)
     print("built:", cuda_lib_path(), host_ext_path())

@@ -4,6 +4,10 @@
     dist.init_process_group("dlslime", rank=r, world_size=n)
     dist.send(t, dst=1); dist.recv(t, src=0); dist.batch_isend_irecv([...])
 
+Two forms with one contract: a C++ ``c10d::Backend`` (``csrc/torch/slime_backend.cpp``, built against the installed
+torch; the default when it loads) and the Python ``ProcessGroup`` below (``SLIME_TORCH_BACKEND=python``, or when the
+extension is not built).
+
 Like the reference's backend (``dlslime/csrc/torch/slime_backend.h:105-208`` in the reference) it builds one
 endpoint per peer at construction, exchanges their ``endpoint_info()`` through the c10d store (keys
 ``SLIME_ENDPOINT_<rank>_<peer>``), connects the full mesh, and implements ``send`` / ``recv`` only; every
@@ -181,7 +185,36 @@ class SlimeProcessGroup(dist.ProcessGroup):
             pass
 
 
+def _load_cpp():
+    """The C++ backend (``csrc/torch/slime_backend.cpp``, a ``c10d::Backend``), or None with the reason."""
+    try:
+        from . import _slime_torch  # built by dlslime_b200/_build.py against the installed torch
+
+        return _slime_torch, ""
+    except ImportError as e:
+        return None, str(e)
+
+
+def implementation() -> str:
+    """``"cpp"`` or ``"python"``: which form ``init_process_group("dlslime")`` creates. ``SLIME_TORCH_BACKEND`` forces one;
+    by default the C++ backend is used when its extension is built and loads."""
+    want = os.environ.get("SLIME_TORCH_BACKEND", "")
+    if want == "python":
+        return "python"
+    mod, why = _load_cpp()
+    if mod is None:
+        if want == "cpp":
+            raise RuntimeError(f"SLIME_TORCH_BACKEND=cpp but the extension does not load: {why}")
+        return "python"
+    return "cpp"
+
+
 def _create(store, rank, size, timeout):
+    if implementation() == "cpp":
+        mod, _ = _load_cpp()
+        ms = int(timeout.total_seconds() * 1000) if isinstance(timeout, timedelta) else 300_000
+        return mod.create_backend(store, rank, size, ms, _slime_c.bridge_table(), os.environ.get("SLIME_BACKEND_TRANSPORT", ""),
+                                  "127.0.0.1")
     return SlimeProcessGroup(store, rank, size, timeout)
 
 

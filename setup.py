@@ -19,6 +19,7 @@ class BuildNative(build_py):
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
         mod.build_host()
+        mod.build_torch_plugin()
         if os.environ.get("BUILD_NVLINK", "ON").upper() not in ("OFF", "0", "FALSE"):
             mod.build_cuda()
         super().run()

@@ -33,8 +33,32 @@ def main():
         dist.all_reduce(torch.ones(1))
         raise SystemExit("all_reduce should not be supported")
     except (NotImplementedError, RuntimeError) as e:
-        assert "not supported" in str(e)
-    print(f"BACKEND_OK {rank}", flush=True)
+        assert "not support" in str(e), str(e)  # "is not supported" (Python form) / "does not support allreduce" (c10d::Backend)
+    several = [torch.full((17,), float(rank)), torch.full((5, 3), float(rank) + 0.5)]  # every tensor of a list is moved
+    got = [torch.empty(17), torch.empty(5, 3)]
+    pg = dist.distributed_c10d._get_default_group()
+    if rank == 0:
+        pg.send(several, 1, 0).wait()
+        pg.recv(got, 1, 0).wait()
+    else:
+        pg.recv(got, 0, 0).wait()
+        pg.send(several, 0, 0).wait()
+    assert torch.all(got[0] == float(peer)) and torch.all(got[1] == float(peer) + 0.5)
+    # wait(timeout) is honoured: a receive that nobody sends ends with status 402 instead of blocking
+    import time
+    from datetime import timedelta
+
+    if rank == 0:
+        w = pg.recv([torch.empty(8)], 1, 0)
+        t0 = time.monotonic()
+        try:
+            w.wait(timedelta(milliseconds=300))
+            raise SystemExit("the unmatched recv should have timed out")
+        except RuntimeError as e:
+            assert "402" in str(e) and time.monotonic() - t0 < 5.0, str(e)
+    else:
+        time.sleep(1.5)  # stay connected while rank 0 waits
+    print(f"BACKEND_OK {rank} {dlslime_b200.torch_backend.implementation()}", flush=True)
     os._exit(0)  # skip the default teardown barrier, which this backend does not implement
 
 
