@@ -79,6 +79,7 @@ PYBIND11_MODULE(_slime_c, m)
     m.attr("_BUILD_INTRA_OPS") = true;   // dlslime_b200.ops: all-gather, EP dispatch/combine, AG-GEMM
     m.attr("_BUILD_INTER_OPS") = false;
     m.attr("_BUILD_RPC")       = true;
+    m.attr("_BUILD_NVTX")      = slime::kNvtxCompiledIn;  // NVTX ranges around the signal operations (core/nvtx.h)
 
     m.def(
         "discover_topology",

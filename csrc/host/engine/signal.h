@@ -18,6 +18,7 @@
 #include <mutex>
 #include <vector>
 
+#include "core/nvtx.h"
 #include "core/ring.h"
 
 namespace slime {
@@ -160,6 +161,7 @@ public:
     void init() override { reset_all(); }
     void record_gpu_ready() override
     {
+        SLIME_NVTX_RANGE("slime.signal.record_gpu_ready", kNvtxSignal);
         if (stream_ != nullptr && stream_hooks().record_value(stream_, w_.dev, 1ull) == 0) return;
         w_.host[0].store(1, std::memory_order_release);
     }
@@ -173,10 +175,12 @@ public:
     void bind_stream(void* stream) override { stream_ = stream; }
     void wait_comm_done_on_stream(uint32_t mask) override
     {
+        SLIME_NVTX_RANGE("slime.signal.wait_comm_done_on_stream", kNvtxSignal);
         if (stream_ != nullptr) stream_hooks().wait_mask(stream_, static_cast<char*>(w_.dev) + 8, mask, 0ull);
     }
     bool wait_comm_done_cpu(uint32_t mask, int64_t timeout_ms = -1) override
     {
+        SLIME_NVTX_RANGE("slime.signal.wait_comm_done_cpu", kNvtxWait);
         auto satisfied = [&] { return forced_.load(std::memory_order_acquire) || (get_comm_done_mask() & mask) == mask; };
         for (int i = 0; i < 2000; ++i) {
             if (satisfied()) return true;

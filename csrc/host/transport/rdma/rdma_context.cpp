@@ -6,6 +6,7 @@
 
 #include "core/env.h"
 #include "core/log.h"
+#include "core/nvtx.h"
 #include "core/ring.h"
 #include "obs/obs.h"
 #include "topology/topology.h"
@@ -139,6 +140,7 @@ void RdmaContext::remove_sink(uint32_t qp_num)
 
 void RdmaContext::cq_loop()
 {
+    SLIME_NVTX_THREAD("slime.rdma.cq");
     const int               burst = std::max(1, engine_env().poll_count);
     std::vector<Completion> wcs(burst);
     int                     empty_spins = 0;

@@ -7,6 +7,7 @@
 #include <sstream>
 
 #include "core/log.h"
+#include "core/nvtx.h"
 #include "core/ring.h"
 #include "transport/rdma/rdma_endpoint.h"
 
@@ -89,6 +90,7 @@ void RdmaWorker::pin()
 
 void RdmaWorker::run()
 {
+    SLIME_NVTX_THREAD("slime.rdma.worker");
     pin();
     std::vector<std::weak_ptr<RdmaEndpoint>> eps;
     int idle = 0;

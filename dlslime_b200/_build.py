@@ -48,6 +48,15 @@ def _nvcc() -> str:
     return cand
 
 
+def _cuda_include() -> list[Path]:
+    """The CUDA toolkit's include directory when there is one: the host runtime takes only the header-only NVTX 3 from it
+    (csrc/host/core/nvtx.h) and builds without it."""
+    for root in (os.environ.get("CUDA_HOME"), os.environ.get("CUDA_PATH"), "/usr/local/cuda"):
+        if root and (Path(root) / "include" / "nvtx3" / "nvToolsExt.h").exists():
+            return [Path(root) / "include"]
+    return []
+
+
 def _newest_header_mtime(dirs) -> float:
     newest = 0.0
     for d in dirs:
@@ -122,7 +131,7 @@ def build_host(verbose: bool = False, workers: int | None = None) -> Path:
     hdir = CSRC / "host"
     if not hdir.exists():
         return host_ext_path()
-    inc = [CSRC / "include", hdir, Path(pybind11.get_include()), Path(sysconfig.get_paths()["include"])]
+    inc = [CSRC / "include", hdir, Path(pybind11.get_include()), Path(sysconfig.get_paths()["include"]), *_cuda_include()]
     dep = _newest_header_mtime([CSRC / "include", hdir])
     (OBJ / "host").mkdir(parents=True, exist_ok=True)
     # The system compiler links libstdc++ dynamically. Some environments export CXX as a wrapper that

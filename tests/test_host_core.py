@@ -73,3 +73,17 @@ def test_ascend_endpoint_is_an_interface_stub():
     assert info["host"] == "127.0.0.1" and info["mr_info"]["buf"]["length"] == 64
     with pytest.raises(RuntimeError, match="not available"):
         ep.connect(info)
+
+
+def test_nvtx_ranges_are_compiled_in_where_the_toolkit_headers_exist():
+    """The host runtime wraps its signal operations in NVTX ranges when it was built with the CUDA toolkit's headers on
+    the include path (they are header-only); without them the macros are no-ops and the flag says so."""
+    import pathlib
+
+    from dlslime_b200 import _build, _slime_c
+
+    assert isinstance(_slime_c._BUILD_NVTX, bool)
+    if _build._cuda_include():
+        assert _slime_c._BUILD_NVTX
+    text = (pathlib.Path(_build.CSRC) / "host" / "engine" / "signal.h").read_text()
+    assert text.count("SLIME_NVTX_RANGE(") >= 3
