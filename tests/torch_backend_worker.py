@@ -44,6 +44,18 @@ def main():
         pg.recv(got, 0, 0).wait()
         pg.send(several, 0, 0).wait()
     assert torch.all(got[0] == float(peer)) and torch.all(got[1] == float(peer) + 0.5)
+    if "--cuda" in sys.argv:  # device tensors are staged through host memory; both ranks may share one GPU
+        dev = torch.device("cuda", 0)
+        x = torch.arange(4096, dtype=torch.float32, device=dev) * (rank + 1)
+        y = torch.empty(4096, dtype=torch.float32, device=dev)
+        if rank == 0:
+            dist.send(x, dst=1)
+            dist.recv(y, src=1)
+        else:
+            dist.recv(y, src=0)
+            dist.send(x, dst=0)
+        torch.cuda.synchronize()
+        assert torch.equal(y, torch.arange(4096, dtype=torch.float32, device=dev) * (peer + 1))
     # wait(timeout) is honoured: a receive that nobody sends ends with status 402 instead of blocking
     import time
     from datetime import timedelta
