@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Host-side benchmarks of the endpoint API and the services on top of it (no GPU needed).
 
-    python bench/host_bench.py io        [--transport tcp|rdma] [--sizes 4096,65536,1048576,16777216] [--batch 1] [--iters 200]
+    python bench/host_bench.py io        [--transport tcp|rdma] [--sizes 4096,65536,1048576,16777216] [--batch 1] [--concurrency 1] [--iters 200]
     python bench/host_bench.py sendrecv  [--transport tcp|rdma] [--sizes ...]
     python bench/host_bench.py rpc       [--sizes 64,4096,65536,1048576] [--iters 500]
     python bench/host_bench.py cache     [--length 16777216] [--iters 20]
@@ -68,12 +68,15 @@ def cmd_io(args):
             t0 = time.perf_counter()
             for _ in range(args.iters):
                 t = time.perf_counter()
-                fn(batch).wait(30000)
+                futs = [fn(batch) for _ in range(args.concurrency)]  # `concurrency` operations of `batch` pieces in flight
+                for f in futs:
+                    f.wait(30000)
                 lat.append(time.perf_counter() - t)
             dt = time.perf_counter() - t0
-            print(json.dumps({"bench": "endpoint_io", "transport": a.kind(), "op": op, "bytes": size, "batch": args.batch, "qp": args.qp,
+            print(json.dumps({"bench": "endpoint_io", "transport": a.kind(), "op": op, "bytes": size, "batch": args.batch,
+                              "concurrency": args.concurrency, "qp": args.qp,
                               "p50_us": round(pct(lat, 0.5) * 1e6, 1), "p99_us": round(pct(lat, 0.99) * 1e6, 1),
-                              "mb_s": round(size * args.batch * args.iters / dt / 1e6, 1)}), flush=True)
+                              "mb_s": round(size * args.batch * args.concurrency * args.iters / dt / 1e6, 1)}), flush=True)
     a.shutdown()
     b.shutdown()
 
@@ -199,6 +202,7 @@ if __name__ == "__main__":
     ap.add_argument("--transport", default="tcp", choices=["tcp", "rdma"])
     ap.add_argument("--sizes", default="4096,65536,1048576,16777216")
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--concurrency", type=int, default=1, help="io: operations kept in flight per iteration")
     ap.add_argument("--qp", type=int, default=2)
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--length", type=int, default=16 << 20)
