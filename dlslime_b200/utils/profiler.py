@@ -128,3 +128,51 @@ def group_profile(name: str = "trace", out_dir: str = "prof", enabled: bool = Tr
             os.makedirs(out_dir, exist_ok=True)
             with gzip.open(os.path.join(out_dir, f"{name}.merged.json.gz"), "wt") as f:
                 json.dump(merge_traces(gathered), f)
+
+
+def merge_trace_files(input_dir: str, output: str | None = None) -> str:
+    """Merge every Chrome trace (``*.json`` / ``*.json.gz``) found under ``input_dir`` (recursively, in sorted order) into
+    one file; the rank label of a trace is its path relative to ``input_dir``. Returns the output path. The job of the
+    reference's ``dlslime/utils/json_merge_manually.py``: traces written per rank by separate runs or hosts, merged later."""
+    import pathlib
+    import time
+
+    root = pathlib.Path(input_dir)
+    files = sorted(p for p in root.rglob("*") if p.is_file() and (p.name.endswith(".json") or p.name.endswith(".json.gz"))
+                   and ".merged." not in p.name)
+    if not files:
+        raise FileNotFoundError(f"no trace files under {input_dir}")
+    traces, names = [], []
+    for p in files:
+        opener = gzip.open if p.name.endswith(".gz") else open
+        with opener(p, "rt") as f:
+            data = json.load(f)
+        if isinstance(data, list):  # the bare-array form of the trace format
+            data = {"traceEvents": data}
+        if "traceEvents" not in data:
+            continue
+        traces.append(data)
+        names.append(str(p.relative_to(root)))
+    if not traces:
+        raise ValueError(f"none of the {len(files)} JSON files under {input_dir} is a Chrome trace")
+    out = output or str(root / f"merged_trace_{time.strftime('%Y%m%d_%H%M%S')}.merged.json.gz")
+    opener = gzip.open if out.endswith(".gz") else open
+    with opener(out, "wt") as f:
+        json.dump(merge_traces(traces, names), f)
+    return out
+
+
+def main(argv=None) -> int:
+    import argparse
+
+    ap = argparse.ArgumentParser(prog="python -m dlslime_b200.utils.profiler",
+                                 description="Merge the Chrome traces found under a directory into one trace, one process group per file.")
+    ap.add_argument("-i", "--input-dir", required=True)
+    ap.add_argument("-o", "--output", default=None, help="output file (.json or .json.gz); default: merged_trace_<time>.merged.json.gz in the input directory")
+    a = ap.parse_args(argv)
+    print(merge_trace_files(a.input_dir, a.output))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

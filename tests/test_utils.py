@@ -122,3 +122,29 @@ def test_bench_reports_unavailable_without_a_gpu():
         assert res.returncode == 0, res.stderr[-2000:]
         line = json.loads(res.stdout.strip().splitlines()[-1])
         assert line["impl"] == impl and "unavailable" in line
+
+
+def test_trace_files_of_a_directory_are_merged(tmp_path):
+    import gzip
+    import json
+
+    from dlslime_b200.utils import profiler
+
+    (tmp_path / "host0").mkdir()
+    (tmp_path / "host1" / "deep").mkdir(parents=True)
+    ev = lambda name, pid: {"ph": "X", "name": name, "pid": pid, "tid": 1, "ts": 0, "dur": 5}
+    (tmp_path / "host0" / "rank0.json").write_text(json.dumps({"traceEvents": [ev("a", 7)]}))
+    with gzip.open(tmp_path / "host1" / "deep" / "rank1.json.gz", "wt") as f:
+        json.dump([ev("b", 7)], f)  # bare-array form
+    (tmp_path / "notes.json").write_text(json.dumps({"not": "a trace"}))
+    out = tmp_path / "all.json"
+    assert profiler.main(["-i", str(tmp_path), "-o", str(out)]) == 0
+    merged = json.loads(out.read_text())
+    xs = [e for e in merged["traceEvents"] if e["ph"] == "X"]
+    assert sorted(e["name"] for e in xs) == ["a", "b"] and len({e["pid"] for e in xs}) == 2
+    labels = [e["args"]["name"] for e in merged["traceEvents"] if e.get("name") == "process_name"]
+    assert any("host0/rank0.json" in n for n in labels) and any("rank1.json.gz" in n for n in labels)
+    import pytest
+
+    with pytest.raises(FileNotFoundError):
+        profiler.merge_trace_files(str(tmp_path / "host0" / "nothing-here"))
