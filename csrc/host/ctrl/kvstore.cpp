@@ -72,6 +72,16 @@ KvStore::Value& KvStore::get_or_create(const std::string& key, Type t)
     return *v;
 }
 
+// A live value of kind `t`, nullptr when the key is absent; a key that holds another kind of value is an error for
+// reads as well as for writes, as in Redis.
+KvStore::Value* KvStore::find_typed(const std::string& key, Type t)
+{
+    Value* v = find_live(key);
+    if (v != nullptr && v->type != t)
+        throw std::runtime_error("WRONGTYPE Operation against a key holding the wrong kind of value");
+    return v;
+}
+
 // ------------------------------------------------------------------ strings / generic
 bool KvStore::set(const std::string& key, const std::string& value, int64_t ttl_ms, bool nx)
 {
@@ -302,8 +312,8 @@ int64_t KvStore::hset(const std::string& key, const std::vector<std::pair<std::s
 std::optional<std::string> KvStore::hget(const std::string& key, const std::string& field)
 {
     std::lock_guard<std::mutex> g(mu_);
-    Value* v = find_live(key);
-    if (v == nullptr || v->type != Type::Hash) return std::nullopt;
+    Value* v = find_typed(key, Type::Hash);
+    if (v == nullptr) return std::nullopt;
     auto it = v->hash.find(field);
     if (it == v->hash.end()) return std::nullopt;
     return it->second;
@@ -312,16 +322,16 @@ std::optional<std::string> KvStore::hget(const std::string& key, const std::stri
 std::vector<std::pair<std::string, std::string>> KvStore::hgetall(const std::string& key)
 {
     std::lock_guard<std::mutex> g(mu_);
-    Value* v = find_live(key);
-    if (v == nullptr || v->type != Type::Hash) return {};
+    Value* v = find_typed(key, Type::Hash);
+    if (v == nullptr) return {};
     return {v->hash.begin(), v->hash.end()};
 }
 
 int64_t KvStore::hdel(const std::string& key, const std::vector<std::string>& fields)
 {
     std::lock_guard<std::mutex> g(mu_);
-    Value* v = find_live(key);
-    if (v == nullptr || v->type != Type::Hash) return 0;
+    Value* v = find_typed(key, Type::Hash);
+    if (v == nullptr) return 0;
     int64_t n = 0;
     for (const auto& f : fields) n += static_cast<int64_t>(v->hash.erase(f));
     if (v->hash.empty()) data_.erase(key);
@@ -358,8 +368,8 @@ int64_t KvStore::rpush(const std::string& key, const std::vector<std::string>& v
 std::optional<std::string> KvStore::lpop(const std::string& key)
 {
     std::lock_guard<std::mutex> g(mu_);
-    Value* v = find_live(key);
-    if (v == nullptr || v->type != Type::List || v->list.empty()) return std::nullopt;
+    Value* v = find_typed(key, Type::List);
+    if (v == nullptr || v->list.empty()) return std::nullopt;
     std::string s = std::move(v->list.front());
     v->list.pop_front();
     if (v->list.empty()) data_.erase(key);
@@ -369,8 +379,8 @@ std::optional<std::string> KvStore::lpop(const std::string& key)
 std::optional<std::string> KvStore::rpop(const std::string& key)
 {
     std::lock_guard<std::mutex> g(mu_);
-    Value* v = find_live(key);
-    if (v == nullptr || v->type != Type::List || v->list.empty()) return std::nullopt;
+    Value* v = find_typed(key, Type::List);
+    if (v == nullptr || v->list.empty()) return std::nullopt;
     std::string s = std::move(v->list.back());
     v->list.pop_back();
     if (v->list.empty()) data_.erase(key);
@@ -380,15 +390,15 @@ std::optional<std::string> KvStore::rpop(const std::string& key)
 int64_t KvStore::llen(const std::string& key)
 {
     std::lock_guard<std::mutex> g(mu_);
-    Value* v = find_live(key);
-    return (v == nullptr || v->type != Type::List) ? 0 : static_cast<int64_t>(v->list.size());
+    Value* v = find_typed(key, Type::List);
+    return v == nullptr ? 0 : static_cast<int64_t>(v->list.size());
 }
 
 std::vector<std::string> KvStore::lrange(const std::string& key, int64_t start, int64_t stop)
 {
     std::lock_guard<std::mutex> g(mu_);
-    Value* v = find_live(key);
-    if (v == nullptr || v->type != Type::List) return {};
+    Value* v = find_typed(key, Type::List);
+    if (v == nullptr) return {};
     const int64_t n = static_cast<int64_t>(v->list.size());
     if (start < 0) start = std::max<int64_t>(0, n + start);
     if (stop < 0) stop = n + stop;
@@ -457,8 +467,8 @@ std::string KvStore::xadd(const std::string& key, const std::string& id,
 int64_t KvStore::xlen(const std::string& key)
 {
     std::lock_guard<std::mutex> g(mu_);
-    Value* v = find_live(key);
-    return (v == nullptr || v->type != Type::Stream) ? 0 : static_cast<int64_t>(v->stream.size());
+    Value* v = find_typed(key, Type::Stream);
+    return v == nullptr ? 0 : static_cast<int64_t>(v->stream.size());
 }
 
 std::vector<std::pair<std::string, std::vector<StreamEntry>>>
@@ -501,8 +511,8 @@ KvStore::xread(const std::vector<std::pair<std::string, std::string>>& keys_ids,
 std::vector<StreamEntry> KvStore::xrange(const std::string& key, const std::string& start, const std::string& end, size_t count)
 {
     std::lock_guard<std::mutex> g(mu_);
-    Value* v = find_live(key);
-    if (v == nullptr || v->type != Type::Stream) return {};
+    Value* v = find_typed(key, Type::Stream);
+    if (v == nullptr) return {};
     StreamId lo{0, 0}, hi{UINT64_MAX, UINT64_MAX};
     if (start != "-" && !StreamId::parse(start, lo)) throw std::runtime_error("ERR Invalid stream ID");
     if (end != "+" && !StreamId::parse(end, hi)) throw std::runtime_error("ERR Invalid stream ID");

@@ -110,6 +110,7 @@ private:
     };
     Value* find_live(const std::string& key);  // expires lazily; caller holds mu_
     Value& get_or_create(const std::string& key, Type t);
+    Value* find_typed(const std::string& key, Type t);
 
     std::mutex                   mu_;
     std::condition_variable      cv_;

@@ -93,3 +93,148 @@ def test_cache_directory_never_hands_a_slab_out_twice(program):
     for peer, version in list(live):
         assert srv.delete_assignments(peer, version)
     assert srv.stats().free_slabs == total
+
+
+# ------------------------------------------------------------------------------------------------
+# the embedded store against a model: strings, hashes and lists with time-to-live on an injected clock
+# ------------------------------------------------------------------------------------------------
+KEYS = st.sampled_from(["k1", "k2", "k3"])
+VALS = st.sampled_from(["a", "b", "c", "dd"])
+kv_ops = st.lists(st.one_of(
+    st.tuples(st.just("set"), KEYS, VALS, st.sampled_from([-1, 50, 500])),
+    st.tuples(st.just("get"), KEYS),
+    st.tuples(st.just("del"), KEYS),
+    st.tuples(st.just("hset"), KEYS, VALS, VALS),
+    st.tuples(st.just("hget"), KEYS, VALS),
+    st.tuples(st.just("hdel"), KEYS, VALS),
+    st.tuples(st.just("lpush"), KEYS, VALS),
+    st.tuples(st.just("rpush"), KEYS, VALS),
+    st.tuples(st.just("lpop"), KEYS),
+    st.tuples(st.just("rpop"), KEYS),
+    st.tuples(st.just("pexpire"), KEYS, st.sampled_from([10, 100, 1000])),
+    st.tuples(st.just("tick"), st.sampled_from([1, 9, 60, 600])),
+), min_size=1, max_size=60)
+
+
+class _Model:
+    """What Redis does for this subset: one namespace, typed values, a deadline per key, empty containers vanish."""
+
+    def __init__(self):
+        self.now, self.d = 1_000_000, {}
+
+    def _live(self, k):
+        e = self.d.get(k)
+        if e is not None and e[2] is not None and e[2] <= self.now:
+            del self.d[k]
+            e = None
+        return e
+
+    def typed(self, k, kind, create):
+        e = self._live(k)
+        if e is None:
+            if not create:
+                return None
+            e = self.d[k] = [kind, {} if kind == "hash" else [] if kind == "list" else "", None]
+        if e[0] != kind:
+            raise TypeError
+        return e
+
+    def drop_if_empty(self, k):
+        e = self.d.get(k)
+        if e is not None and e[0] in ("hash", "list") and not e[1]:
+            del self.d[k]
+
+
+@settings(max_examples=200, deadline=None)
+@given(kv_ops)
+def test_kv_store_matches_the_model(program):
+    import pytest
+
+    from dlslime_b200 import _slime_c
+
+    kv, m = _slime_c.ctrl.KvStore(), _Model()
+    kv.set_clock(lambda: m.now)
+
+    def both(model_fn, real_fn):
+        """Runs the model first; a type clash there must be a WRONGTYPE error in the store."""
+        try:
+            want = model_fn()
+        except TypeError:
+            with pytest.raises(RuntimeError, match="WRONGTYPE"):
+                real_fn()
+            return
+        assert real_fn() == want
+
+    for op in program:
+        name, args = op[0], op[1:]
+        if name == "tick":
+            m.now += args[0]
+        elif name == "set":
+            k, v, px = args
+            m._live(k)
+            m.d[k] = ["string", v, None if px < 0 else m.now + px]  # SET replaces any type and clears the deadline
+            assert kv.set(k, v, px=px) is True
+        elif name == "get":
+            both(lambda: (lambda e: None if e is None else e[1])(m.typed(args[0], "string", False)), lambda: kv.get(args[0]))
+        elif name == "del":
+            want = 1 if m._live(args[0]) is not None else 0
+            m.d.pop(args[0], None)
+            assert kv.delete(args[0]) == want
+        elif name == "hset":
+            k, f, v = args
+
+            def mh():
+                e = m.typed(k, "hash", True)
+                new = 0 if f in e[1] else 1
+                e[1][f] = v
+                return new
+            both(mh, lambda: kv.hset(k, {f: v}))
+        elif name == "hget":
+            k, f = args
+            both(lambda: (lambda e: None if e is None else e[1].get(f))(m.typed(k, "hash", False)), lambda: kv.hget(k, f))
+        elif name == "hdel":
+            k, f = args
+
+            def mhd():
+                e = m.typed(k, "hash", False)
+                n = 0 if e is None or f not in e[1] else 1
+                if n:
+                    del e[1][f]
+                    m.drop_if_empty(k)
+                return n
+            both(mhd, lambda: kv.hdel(k, f))
+        elif name in ("lpush", "rpush"):
+            k, v = args
+
+            def mp():
+                e = m.typed(k, "list", True)
+                e[1].insert(0, v) if name == "lpush" else e[1].append(v)
+                return len(e[1])
+            both(mp, lambda: getattr(kv, name)(k, v))
+        elif name in ("lpop", "rpop"):
+            k = args[0]
+
+            def mpop():
+                e = m.typed(k, "list", False)
+                if e is None:
+                    return None
+                v = e[1].pop(0) if name == "lpop" else e[1].pop()
+                m.drop_if_empty(k)
+                return v
+            both(mpop, lambda: getattr(kv, name)(k))
+        elif name == "pexpire":
+            k, ms = args
+            e = m._live(k)
+            if e is not None:
+                e[2] = m.now + ms
+            assert kv.pexpire(k, ms) is (e is not None)
+        # after every step: same set of live keys, same types, same list contents
+        live = {k for k in list(m.d) if m._live(k) is not None}
+        assert {k for k in ("k1", "k2", "k3") if kv.exists(k)} == live
+        assert kv.dbsize() == len(live)
+        for k in live:
+            assert kv.type(k) == m.d[k][0]
+            if m.d[k][0] == "list":
+                assert kv.lrange(k, 0, -1) == m.d[k][1] and kv.llen(k) == len(m.d[k][1])
+            ttl = kv.pttl(k)
+            assert ttl == (-1 if m.d[k][2] is None else m.d[k][2] - m.now)
