@@ -1,5 +1,7 @@
 #include "engine/memory_pool.h"
 
+#include <iterator>
+
 #include <functional>
 
 #include "core/log.h"
@@ -15,17 +17,24 @@ static bool is_system_name(const std::string& n)
 int32_t LocalMemoryPool::register_memory_region(uintptr_t addr, uint64_t length, const std::optional<std::string>& name)
 {
     std::lock_guard<std::mutex> g(mu_);
-    int32_t handle = -1;
+    int32_t by_name = -1, by_ptr = -1;
     if (name) {
         auto it = by_name_.find(*name);
-        if (it != by_name_.end()) handle = it->second;
+        if (it != by_name_.end()) by_name = it->second;
     }
-    if (handle < 0) {
+    {
         auto it = by_ptr_.find(addr);
-        if (it != by_ptr_.end()) handle = it->second;
+        if (it != by_ptr_.end()) by_ptr = it->second;
     }
+    // A name that belongs to one region cannot be pointed at memory that another live region starts at: one of the two
+    // would lose its identity (the reference refuses this as well, "registered to diff handle").
+    if (by_name >= 0 && by_ptr >= 0 && by_name != by_ptr) return -1;
+    int32_t handle = by_name >= 0 ? by_name : by_ptr;
     if (handle >= 0) {
         MemoryRegion& r = regions_[handle];
+        // a further name for a region that is already registered is an alias of it (the reference keeps one handle per
+        // pointer and lets several names resolve to it, dlslime/csrc/engine/rdma/memory_pool.cpp:27-40 in the reference)
+        if (name && by_name_.find(*name) == by_name_.end()) by_name_[*name] = handle;
         if (r.addr == addr && r.length >= length) return handle;  // idempotent
         // same name or same pointer, but moved or grown: register again under the same handle
         if (on_unregister) on_unregister(r);
@@ -66,7 +75,8 @@ int32_t LocalMemoryPool::unregister_memory_region(int32_t handle)
     MemoryRegion& r = regions_[handle];
     if (on_unregister) on_unregister(r);
     obs::record_mr_unregister(r.system, r.length);
-    by_name_.erase(r.name);
+    for (auto it = by_name_.begin(); it != by_name_.end();)  // the name it was registered under and its aliases
+        it = it->second == handle ? by_name_.erase(it) : std::next(it);
     by_ptr_.erase(r.addr);
     r.alive = false;
     return 0;
@@ -104,15 +114,15 @@ Json LocalMemoryPool::mr_info() const
 {
     std::lock_guard<std::mutex> g(mu_);
     Json out = Json::object();
-    for (size_t h = 0; h < regions_.size(); ++h) {
-        const MemoryRegion& r = regions_[h];
+    for (const auto& [name, h] : by_name_) {  // every name, aliases included, describes its region
+        const MemoryRegion& r = regions_[static_cast<size_t>(h)];
         if (!r.alive) continue;
         Json e      = Json::object();
         e["handle"] = static_cast<long long>(h);
         e["addr"]   = static_cast<unsigned long long>(r.addr);
         e["rkey"]   = static_cast<unsigned long long>(r.rkey);
         e["length"] = static_cast<unsigned long long>(r.length);
-        out[r.name] = e;
+        out[name]   = e;
     }
     return out;
 }

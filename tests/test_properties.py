@@ -12,6 +12,9 @@ assignments = st.lists(
 @settings(max_examples=150, deadline=None)
 @given(assignments, st.integers(1, 1 << 21))
 def test_split_by_max_length_covers_every_byte_once_in_order(batch, max_len):
+    from hypothesis import assume
+
+    assume(sum(a.length for a in batch) // max_len < 5000)  # keep the number of pieces (and the run time) small
     out = split_assign_by_max_length(batch, max_len)
     assert all(x.length <= max_len or x.length == 0 for x in out)
     it = iter(out)
@@ -238,3 +241,112 @@ def test_kv_store_matches_the_model(program):
                 assert kv.lrange(k, 0, -1) == m.d[k][1] and kv.llen(k) == len(m.d[k][1])
             ttl = kv.pttl(k)
             assert ttl == (-1 if m.d[k][2] is None else m.d[k][2] - m.now)
+
+
+stream_ops = st.lists(st.one_of(
+    st.tuples(st.just("xadd"), st.sampled_from(["s1", "s2"]), VALS, st.sampled_from([0, 0, 3, 5])),
+    st.tuples(st.just("xread"), st.sampled_from(["s1", "s2"]), st.integers(0, 12), st.sampled_from([0, 1, 4])),
+    st.tuples(st.just("tick"), st.sampled_from([0, 1, 7])),
+    st.tuples(st.just("back"), st.sampled_from([1, 5])),  # the clock steps backwards: ids must still grow
+), min_size=1, max_size=50)
+
+
+@settings(max_examples=150, deadline=None)
+@given(stream_ops)
+def test_streams_keep_order_trim_and_resume(program):
+    """Stream ids grow strictly whatever the clock does; MAXLEN keeps the newest entries; a reader that resumes from the
+    last id it saw gets exactly the entries added since (the mailbox handshake depends on this)."""
+    from dlslime_b200 import _slime_c
+
+    kv = _slime_c.ctrl.KvStore()
+    now = [10_000]
+    kv.set_clock(lambda: now[0])
+    model = {"s1": [], "s2": []}  # (id tuple, id text, fields)
+    key_of = lambda text: tuple(int(x) for x in text.split("-"))
+    for op in program:
+        if op[0] == "tick":
+            now[0] += op[1]
+        elif op[0] == "back":
+            now[0] -= op[1]
+        elif op[0] == "xadd":
+            _, k, v, maxlen = op
+            text = kv.xadd(k, {"f": v}, maxlen=maxlen)
+            ident = key_of(text)
+            if model[k]:
+                assert ident > model[k][-1][0]
+            model[k].append((ident, text, {"f": v}))
+            if maxlen:
+                model[k] = model[k][-maxlen:]
+        else:
+            _, k, seen, count = op
+            entries = model[k]
+            last = entries[min(seen, len(entries)) - 1][1] if entries and seen else "0-0"
+            want = [(t, f) for i, t, f in entries if i > key_of(last)]
+            if count:
+                want = want[:count]
+            got = kv.xread({k: last}, count, None)
+            assert got == ([(k, want)] if want else [])
+        for k, entries in model.items():
+            assert kv.xlen(k) == len(entries)
+            assert kv.xrange(k, "-", "+") == [(t, f) for _, t, f in entries]
+
+
+pool_ops = st.lists(st.one_of(
+    st.tuples(st.just("reg"), st.sampled_from(["a", "b", None]), st.sampled_from([0x1000, 0x2000, 0x3000]), st.sampled_from([64, 128, 4096])),
+    st.tuples(st.just("unreg_name"), st.sampled_from(["a", "b", "auto_0x1000", "auto_0x2000", "auto_0x3000"])),
+    st.tuples(st.just("unreg_handle"), st.integers(0, 6)),
+), min_size=1, max_size=40)
+
+
+@settings(max_examples=200, deadline=None)
+@given(pool_ops)
+def test_memory_pool_handles_are_stable_and_regions_only_grow(program):
+    """A name identifies its region (registering it again returns the same handle, a larger length grows the region); a
+    second name for a pointer that is registered already becomes an alias of that region; unregistering through any name
+    or through the handle removes the region with all of its names; handles of live regions are distinct."""
+    from dlslime_b200 import _slime_c
+
+    pool = _slime_c.MemoryPool()
+    names, regions = {}, {}  # name -> handle; handle -> [addr, length]
+    for op in program:
+        if op[0] == "reg":
+            _, name, addr, length = op
+            key = name or f"auto_{addr:#x}"
+            h = pool.register_memory_region(addr, length, name)
+            by_ptr = next((hh for hh, r in regions.items() if r[0] == addr), None)
+            if key in names and name is not None and by_ptr is not None and by_ptr != names[key]:
+                assert h == -1  # the name belongs to another region than the one that starts at this address: refused
+                continue
+            assert h >= 0
+            if name is None and by_ptr is not None:  # no name given: the pointer identifies the region, nothing is added
+                assert h == by_ptr
+                if regions[h][1] < length:
+                    regions[h][1] = length
+            elif key in names:  # the name wins: same handle, moved and / or grown
+                assert h == names[key]
+                if regions[h][0] != addr or regions[h][1] < length:
+                    regions[h] = [addr, length]
+            elif by_ptr is not None:  # a new name for a registered pointer: alias
+                assert h == by_ptr
+                names[key] = h
+                if regions[h][1] < length:
+                    regions[h][1] = length
+            else:
+                assert h not in regions, "a live handle was handed out twice"
+                names[key], regions[h] = h, [addr, length]
+        else:
+            if op[0] == "unreg_name":
+                h = names.get(op[1])
+                rc = pool.unregister_memory_region(op[1])
+            else:
+                h = op[1] if op[1] in regions else None
+                rc = pool.unregister_memory_region(op[1])
+            assert (rc == 0) == (h is not None)
+            if h is not None:
+                del regions[h]
+                names = {k: v for k, v in names.items() if v != h}
+        info = pool.mr_info()
+        assert pool.live_count() == len(regions) and set(info) == set(names)
+        for k, h in names.items():
+            assert (info[k]["handle"], info[k]["addr"], info[k]["length"]) == (h, regions[h][0], regions[h][1])
+            assert pool.get_handle(k) == h
