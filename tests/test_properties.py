@@ -350,3 +350,78 @@ def test_memory_pool_handles_are_stable_and_regions_only_grow(program):
         for k, h in names.items():
             assert (info[k]["handle"], info[k]["addr"], info[k]["length"]) == (h, regions[h][0], regions[h][1])
             assert pool.get_handle(k) == h
+
+
+# ------------------------------------------------------------------------------------------------
+# JSON through the whole control plane: client -> HTTP -> C++ parser -> store -> C++ writer -> HTTP -> client
+# ------------------------------------------------------------------------------------------------
+json_leaves = st.one_of(
+    st.none(), st.booleans(), st.integers(-(2 ** 53), 2 ** 53),
+    st.floats(allow_nan=False, allow_infinity=False, width=64),
+    st.text(max_size=20),  # any unicode, including control characters, quotes, backslashes and astral code points
+)
+json_values = st.recursive(json_leaves, lambda inner: st.one_of(st.lists(inner, max_size=4), st.dictionaries(st.text(max_size=8), inner, max_size=4)),
+                           max_leaves=12)
+
+
+def test_json_survives_the_control_plane_round_trip():
+    from hypothesis import HealthCheck
+
+    from dlslime_b200.nanoctrl import NanoCtrlClient, start_local_nanoctrl
+
+    ctrl = start_local_nanoctrl()
+    try:
+        client = NanoCtrlClient(ctrl.url, scope="json-fuzz")
+        counter = [0]
+
+        @settings(max_examples=150, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+        @given(st.dictionaries(st.text(max_size=8), json_values, max_size=4))
+        def run(metadata):
+            counter[0] += 1
+            eid = f"fuzz:{counter[0]}"
+            assert client.register(eid, "fuzz", endpoint={"host": "h", "port": 1}, metadata=metadata)["status"] == "ok"
+            info = client.get_entity_info(eid)
+            assert info is not None and info["metadata"] == metadata and info["endpoint"] == {"host": "h", "port": 1}
+            client.unregister(eid)
+
+        run()
+    finally:
+        ctrl.stop()
+
+
+def test_resp_front_end_carries_any_text_and_reports_wrong_types():
+    """Keys, fields and values with any characters (CR LF, quotes, empty, astral) survive the RESP2 front end, and a
+    command against a key of another kind comes back as a WRONGTYPE error, as a Redis server answers."""
+    import pytest
+    from hypothesis import HealthCheck
+
+    from dlslime_b200.nanoctrl import RespClient, RespError, start_local_nanoctrl
+
+    ctrl = start_local_nanoctrl()
+    try:
+        r = RespClient("127.0.0.1", ctrl.resp_port, timeout=5.0)
+        assert r.ping()
+        texts = st.text(max_size=30)
+
+        @settings(max_examples=120, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+        @given(texts.filter(lambda s: s != ""), texts, st.dictionaries(texts, texts, min_size=1, max_size=4), st.lists(texts, min_size=1, max_size=5))
+        def run(key, value, mapping, items):
+            r.flushall()
+            assert r.set("s:" + key, value) and r.get("s:" + key) == value
+            r.hset("h:" + key, mapping=mapping)
+            assert r.hgetall("h:" + key) == mapping
+            for f, v in mapping.items():
+                assert r.hget("h:" + key, f) == v
+            assert r.rpush("l:" + key, *items) == len(items)
+            assert [r.lpop("l:" + key) for _ in items] == items and r.llen("l:" + key) == 0
+            assert sorted(r.keys("*")) == sorted(["s:" + key, "h:" + key])
+            with pytest.raises(RespError, match="WRONGTYPE"):
+                r.hget("s:" + key, "f")
+            with pytest.raises(RespError, match="WRONGTYPE"):
+                r.lpush("h:" + key, "x")
+            assert r.ping()  # the connection is still in step after the errors
+
+        run()
+        r.close()
+    finally:
+        ctrl.stop()
