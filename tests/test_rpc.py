@@ -113,3 +113,48 @@ def test_close_fails_pending_calls(rpc_pair):
     d._rpc_channels["worker:0"].session.close()
     with pytest.raises(RpcError):
         fut.wait(5)
+
+
+def test_payload_sizes_around_the_slot_capacity():
+    """Requests and replies up to exactly one slot's capacity pass; one byte more is refused on the side that would have
+    sent it, with the limit in the message, and the session carries on."""
+    from dlslime_b200.rpc import RemoteRpcError, RpcError
+
+    class Blob:
+        @method(raw=True)
+        def echo(self, data):
+            return data
+
+        @method(raw=True)
+        def grow(self, data):
+            return bytes((i * 7) % 251 for i in range(int.from_bytes(data[:4], "little")))
+
+    ctrl = start_local_nanoctrl()
+    w, d = PeerAgent(ctrl.url, alias="worker:s"), PeerAgent(ctrl.url, alias="driver:s")
+    for a in (w, d):
+        a._rpc_max_inflight, a._rpc_buffer_size = 4, 64 << 10  # four slots of 16 KiB
+    d.connect_to("worker:s").wait(10)
+    w.connect_to("driver:s").wait(10)
+    stop = threading.Event()
+    t = threading.Thread(target=serve, args=(w, Blob(), "driver:s"), kwargs={"stop_event": stop}, daemon=True)
+    t.start()
+    try:
+        p = proxy(d, "worker:s", Blob)
+        cap = (16 << 10) - c.rpc.HEADER_SIZE
+        for n in (0, 1, cap - 1, cap):
+            payload = bytes((i * 3) % 256 for i in range(n))
+            assert p.echo(payload).wait(10) == payload
+            assert p.grow(n.to_bytes(4, "little")).wait(10) == bytes((i * 7) % 251 for i in range(n))
+        for n in (cap + 1, 3 * cap):
+            with pytest.raises(RpcError, match=str(cap)):
+                p.echo(bytes(n)).wait(10)
+            with pytest.raises(RemoteRpcError, match=str(cap)):
+                p.grow(n.to_bytes(4, "little")).wait(10)
+        assert p.echo(b"still in step").wait(10) == b"still in step"
+        p.close()
+    finally:
+        stop.set()
+        t.join(3)
+        d.shutdown()
+        w.shutdown()
+        ctrl.stop()
