@@ -37,6 +37,9 @@ int32_t LocalMemoryPool::register_memory_region(uintptr_t addr, uint64_t length,
         if (name && by_name_.find(*name) == by_name_.end()) by_name_[*name] = handle;
         if (r.addr == addr && r.length >= length) return handle;  // idempotent
         // same name or same pointer, but moved or grown: register again under the same handle
+        if (r.addr != addr)  // worth a line: two owners using one name in one registry would look exactly like this
+            SLIME_LOG_WARN("memory region '", r.name, "' moves from ", reinterpret_cast<void*>(r.addr), " to ",
+                           reinterpret_cast<void*>(addr), " under handle ", handle);
         if (on_unregister) on_unregister(r);
         obs::record_mr_grow(r.system, r.length, length);
         by_ptr_.erase(r.addr);

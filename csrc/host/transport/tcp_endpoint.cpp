@@ -306,30 +306,28 @@ bool TcpEndpoint::post_op(Op& op)
         if (!send_all(out_fd_, &h, sizeof(h))) return false;
         return send_all(out_fd_, reinterpret_cast<const void*>(std::get<0>(op.chunk) + std::get<1>(op.chunk)), h.length);
     }
-    uint64_t posted = 0;
+    // Every piece is checked before the first byte leaves: a batch with a piece that names an unknown region or runs
+    // past one fails as a whole, moves nothing, and leaves nothing in flight for the peer to answer.
+    std::vector<MemoryRegion> locals(op.assign.size()), remotes(op.assign.size());
     for (size_t i = 0; i < op.assign.size(); ++i) {
-        const auto&  a = op.assign[i];
-        MemoryRegion local, remote;
-        if (!local_pool_->get_mr(static_cast<int32_t>(std::get<0>(a)), local)
-            || !remote_pool_->get_remote_mr(static_cast<int32_t>(std::get<1>(a)), remote)
-            || !local.contains(std::get<3>(a), std::get<4>(a)) || !remote.contains(std::get<2>(a), std::get<4>(a))) {
+        const auto& a = op.assign[i];
+        if (!local_pool_->get_mr(static_cast<int32_t>(std::get<0>(a)), locals[i])
+            || !remote_pool_->get_remote_mr(static_cast<int32_t>(std::get<1>(a)), remotes[i])
+            || !locals[i].contains(std::get<3>(a), std::get<4>(a)) || !remotes[i].contains(std::get<2>(a), std::get<4>(a))) {
             SLIME_LOG_ERROR("tcp endpoint: assignment ", i, " names an unknown region or exceeds it");
-            op.state->fail(FAILED);
-            // finish the batch with an empty last piece so the peer still acknowledges
-            WireHdr h;
-            h.kind  = op.opcode == OpCode::READ ? REQ_WRITE : REQ_WRITE;
-            h.flags = F_LAST;
-            h.id    = op.id;
-            h.handle = ~0ull;
-            if (op.opcode == OpCode::READ) {
-                // nothing outstanding for a read that failed locally: complete it here
+            {
                 std::lock_guard<std::mutex> g(inflight_mu_);
                 inflight_.erase(op.id);
-                complete(op.state, FAILED);
-                return true;
             }
-            return send_all(out_fd_, &h, sizeof(h));
+            complete(op.state, FAILED);
+            return true;
         }
+    }
+    uint64_t posted = 0;
+    for (size_t i = 0; i < op.assign.size(); ++i) {
+        const auto&         a      = op.assign[i];
+        const MemoryRegion& local  = locals[i];
+        const MemoryRegion& remote = remotes[i];
         const bool last = i + 1 == op.assign.size();
         WireHdr    h;
         h.id     = op.id;

@@ -425,3 +425,58 @@ def test_resp_front_end_carries_any_text_and_reports_wrong_types():
         r.close()
     finally:
         ctrl.stop()
+
+
+# ------------------------------------------------------------------------------------------------
+# one-sided transfers over the TCP endpoint against two byte arrays
+# ------------------------------------------------------------------------------------------------
+REGION = 1 << 16
+piece = st.tuples(st.integers(0, REGION), st.integers(0, REGION), st.sampled_from([0, 1, 7, 64, 1000, 4096, 30000, REGION]))
+transfer_ops = st.lists(st.tuples(st.sampled_from(["read", "write"]), st.lists(piece, min_size=1, max_size=6)), min_size=1, max_size=8)
+
+
+def test_tcp_transfers_match_a_model_and_bad_batches_change_nothing():
+    """Random batches of (remote offset, local offset, length), zero lengths and whole-region pieces included: the two
+    regions end up as the same sequence of copies applied to two byte arrays; a batch with a piece that leaves its
+    region fails as a whole and moves nothing."""
+    import ctypes
+    import random
+
+    import pytest
+    from hypothesis import HealthCheck
+
+    from dlslime_b200 import _slime_c as c
+
+    a, b = c.TcpEndpoint(), c.TcpEndpoint()
+    ba, bb = ctypes.create_string_buffer(REGION), ctypes.create_string_buffer(REGION)
+    a.register_memory_region("buf", ctypes.addressof(ba), 0, REGION)
+    b.register_memory_region("buf", ctypes.addressof(bb), 0, REGION)
+    a.connect(b.endpoint_info())
+    b.connect(a.endpoint_info())
+    try:
+        @settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+        @given(transfer_ops)
+        def run(program):
+            rnd = random.Random(3)  # the same bytes for every example, so that a failure replays
+            local, remote = bytearray(rnd.randbytes(REGION)), bytearray(rnd.randbytes(REGION))
+            ba.raw, bb.raw = bytes(local), bytes(remote)
+            for op, pieces in program:
+                ok = all(ro + n <= REGION and lo + n <= REGION for ro, lo, n in pieces)
+                fut = getattr(a, op)([(0, 0, ro, lo, n) for ro, lo, n in pieces])
+                if not ok:
+                    with pytest.raises(RuntimeError):
+                        fut.wait(10_000)
+                    assert ba.raw == bytes(local) and bb.raw == bytes(remote), "a refused batch moved bytes"
+                    continue
+                assert fut.wait(10_000) == 0
+                for ro, lo, n in pieces:  # pieces of one batch are applied in order
+                    if op == "write":
+                        remote[ro:ro + n] = local[lo:lo + n]
+                    else:
+                        local[lo:lo + n] = remote[ro:ro + n]
+                assert ba.raw == bytes(local) and bb.raw == bytes(remote)
+
+        run()
+    finally:
+        a.shutdown()
+        b.shutdown()

@@ -378,3 +378,63 @@ def test_slimerpc_over_rdma_links():
         print("ok")
     """, timeout=180)
     assert "ok" in out
+
+
+def test_random_batches_match_a_model_and_bad_batches_fail_cleanly():
+    """Seeded random batches of reads and writes (zero lengths, stripes over four queue pairs, pieces that end exactly at
+    the region's end) against two byte arrays; a batch with a piece past its region fails, and the endpoint keeps working."""
+    out = run_child("""
+        import random
+        rnd = random.Random(11)
+        n = 1 << 18
+        a, b = pair(num_qp=4)
+        la, rb = buf(n), buf(n)
+        local, remote = bytearray(rnd.randbytes(n)), bytearray(rnd.randbytes(n))
+        ctypes.memmove(la, bytes(local), n); ctypes.memmove(rb, bytes(remote), n)
+        # endpoints on one device share that device's registry, so the two regions need different names in one process
+        a.register_memory_region("near", ctypes.addressof(la), 0, n)
+        b.register_memory_region("far", ctypes.addressof(rb), 0, n)
+        link(a, b)
+        lh, rh = a.get_mr_handle("near"), a.get_remote_mr_handle("far")
+        sizes = [0, 1, 7, 64, 1000, 4096, 65536, 100_000, n]
+        bad_seen = 0
+        for step in range(150):
+            op = rnd.choice(["read", "write"])
+            pieces = []
+            for _ in range(rnd.randint(1, 6)):
+                ln = rnd.choice(sizes)
+                if rnd.random() < 0.1:   # sometimes out of range on one side
+                    ro, lo = rnd.randint(0, n), rnd.randint(0, n)
+                else:
+                    ro, lo = rnd.randint(0, n - ln), rnd.randint(0, n - ln)
+                pieces.append((ro, lo, ln))
+            # destinations of one batch must not overlap (stripes of different pieces run concurrently)
+            dst = sorted(((lo, lo + ln) if op == "read" else (ro, ro + ln)) for ro, lo, ln in pieces if ln)
+            if any(x[1] > y[0] for x, y in zip(dst, dst[1:])):
+                continue
+            ok = all(ro + ln <= n and lo + ln <= n for ro, lo, ln in pieces)
+            fut = getattr(a, op)([(lh, rh, ro, lo, ln) for ro, lo, ln in pieces])
+            if not ok:
+                bad_seen += 1
+                try:
+                    st = fut.wait(5000)
+                    assert st != 0, (step, op, pieces)
+                except RuntimeError:
+                    pass
+                # whatever part of a failed batch landed, the endpoints must stay usable; resynchronise the model
+                local[:] = bytes(la); remote[:] = bytes(rb)
+                if not a.connected():
+                    break
+                continue
+            assert fut.wait(5000) == 0, (step, op, pieces)
+            for ro, lo, ln in pieces:
+                if op == "write":
+                    remote[ro:ro + ln] = local[lo:lo + ln]
+                else:
+                    local[lo:lo + ln] = remote[ro:ro + ln]
+            assert bytes(la) == bytes(local) and bytes(rb) == bytes(remote), (step, op, pieces)
+        assert a.write([(lh, rh, 0, 0, 16)]).wait(5000) == 0
+        a.shutdown(); b.shutdown()
+        print("ok", bad_seen)
+    """, timeout=240)
+    assert "ok" in out
