@@ -179,3 +179,58 @@ def test_entities_events_and_lease(ctrl):
     assert cl.unregister("cache:0")["status"] == "ok"  # absent is still ok
     assert cl.get_entity_info("cache:0") is None
     assert [(e["event_type"], e["revision"]) for e in events] == [("ADD", 1), ("REMOVE", 2)]
+
+
+def test_http_routes_survive_malformed_requests():
+    """Seeded junk on every route (wrong types, truncated JSON, raw bytes, wrong methods): the server always answers with
+    JSON and a sensible status, never hangs up, and still serves afterwards."""
+    import random
+    import urllib.error
+    import urllib.request
+
+    ctrl = start_local_nanoctrl()
+    routes = ["/heartbeat", "/start_peer_agent", "/query", "/cleanup", "/v1/desired_topology/x", "/register_mr", "/get_mr_info",
+              "/register", "/unregister", "/get_entity_info", "/list_entities", "/get_redis_address", "/nope"]
+    keys = ["entity_type", "entity_id", "kind", "endpoint", "metadata", "agent_name", "alias", "address", "target_peers", "mr_name",
+            "addr", "length", "rkey", "src", "dst", "scope", "symmetric", "resource", "name_prefix", "x"]
+    rnd = random.Random(5)
+
+    def junk(depth=0):
+        k = rnd.randint(0, 7 if depth < 3 else 4)
+        if k == 0:
+            return None
+        if k == 1:
+            return rnd.choice([True, False])
+        if k == 2:
+            return rnd.randint(-2 ** 40, 2 ** 40)
+        if k == 3:
+            return rnd.random() * 1e6
+        if k == 4:
+            return "".join(chr(rnd.choice([34, 92, 10, 0x1F600, 65, 0xE9, 0])) for _ in range(rnd.randint(0, 6)))
+        if k == 5:
+            return [junk(depth + 1) for _ in range(rnd.randint(0, 3))]
+        return {rnd.choice(keys): junk(depth + 1) for _ in range(rnd.randint(0, 5))}
+
+    try:
+        for _ in range(500):
+            route, kind = rnd.choice(routes), rnd.random()
+            if kind < 0.7:
+                body = json.dumps(junk()).encode()
+            elif kind < 0.85:
+                body = bytes(rnd.randrange(256) for _ in range(rnd.randint(0, 40)))
+            else:
+                body = json.dumps(junk()).encode()[: rnd.randint(0, 10)]
+            req = urllib.request.Request(ctrl.url + route, data=body, headers={"Content-Type": "application/json"},
+                                         method=rnd.choice(["POST", "POST", "GET", "PUT"]))
+            try:
+                with urllib.request.urlopen(req, timeout=5) as r:
+                    code, text = r.status, r.read()
+            except urllib.error.HTTPError as e:
+                code, text = e.code, e.read()
+            assert code in (200, 400, 404, 405, 409, 500), (route, body, code)
+            json.loads(text)
+        client = NanoCtrlClient(ctrl.url)
+        assert client.check_connection()
+        assert client.register("after:1", "probe")["status"] == "ok" and client.get_entity_info("after:1")["kind"] == "probe"
+    finally:
+        ctrl.stop()
