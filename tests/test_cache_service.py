@@ -69,3 +69,44 @@ def test_put_get_roundtrip_through_the_control_plane():
         eng.shutdown()
         srv.stop()
         ctrl.stop()
+
+
+def test_http_service_survives_malformed_requests():
+    """Seeded junk on every route (wrong types, huge and negative numbers, raw bytes, wrong methods): always a JSON answer
+    with a sensible status, no slab leaks, and the service still works afterwards."""
+    import random
+
+    http = CacheHttpServer(CacheService(slab_size=128 * K, memory_size=1024 * K)).start()
+    try:
+        rnd = random.Random(9)
+        keys = ["peer_agent_id", "assignments", "version", "mr_key", "remote_mr_key", "target_offset", "source_offset", "length", "x"]
+        def junk(d=0):
+            k = rnd.randint(0, 7 if d < 3 else 4)
+            if k == 0: return None
+            if k == 1: return rnd.choice([True, False])
+            if k == 2: return rnd.choice([-1, 0, 1, 2**31, 2**63, 2**64, -2**63, 300 * K])
+            if k == 3: return rnd.random() * 1e6
+            if k == 4: return rnd.choice(["", "e", "peer\n", "é"])
+            if k == 5: return [junk(d + 1) for _ in range(rnd.randint(0, 3))]
+            return {rnd.choice(keys): junk(d + 1) for _ in range(rnd.randint(0, 6))}
+        codes = {}
+        opener = urllib.request.build_opener(urllib.request.ProxyHandler({}))
+        for i in range(300):
+            route = rnd.choice(["/store", "/query", "/delete", "/stats", "/healthz", "/peer-agent", "/zzz"])
+            kind = rnd.random()
+            body = json.dumps(junk()).encode() if kind < 0.8 else bytes(rnd.randrange(256) for _ in range(rnd.randint(0, 30)))
+            req = urllib.request.Request(http.url + route, data=body, method=rnd.choice(["POST", "POST", "GET"]))
+            try:
+                with opener.open(req, timeout=5) as r:
+                    code, text = r.status, r.read()
+            except urllib.error.HTTPError as e:
+                code, text = e.code, e.read()
+            codes[code] = codes.get(code, 0) + 1
+            assert code in (200, 400, 404, 405, 501, 503), (route, body, code, text[:200])
+            json.loads(text)
+        st = get_json(http.url, "/stats")
+        assert st["num_slabs"] == 8 and st["used_slabs"] + st["free_slabs"] == 8
+        m = post_json(http.url, "/store", {"peer_agent_id": "after", "assignments": [{"mr_key": 1, "remote_mr_key": 2, "target_offset": 0, "source_offset": 0, "length": 10}]})
+        assert post_json(http.url, "/query", {"peer_agent_id": "after", "version": m["version"]}) == m
+    finally:
+        http.stop()
