@@ -13,6 +13,7 @@ over RESP, and every wait has a timeout.
 
 from __future__ import annotations
 
+import hashlib
 import json
 import os
 import socket
@@ -116,6 +117,7 @@ class PeerAgent:
         self._connections_lock = threading.RLock()
         self._connected_cond = threading.Condition(self._connections_lock)
         self._notified: set[str] = set()
+        self._desired_peers: set[str] = set()  # every peer connect_to was called for (the posted topology)
         self._logical_regions: Dict[str, LogicalMemoryRegion] = {}
         self._materialized: Dict[tuple, MaterializedMemoryRegion] = {}
         self._pools: Dict[ResourceKey, Any] = {}
@@ -130,9 +132,20 @@ class PeerAgent:
 
         self._register()
         self._store = RespClient.from_address(self._redis_address)
+        # Whatever sits in this alias's stream now was addressed to an earlier incarnation (one that crashed: a clean exit
+        # deletes the stream). Its endpoint descriptions are dead, so the mailbox starts behind the last of them; what peers
+        # send from now on has a larger id. Taken before the resource record is published, which is what peers need to
+        # address us at all.
+        start_id = "0-0"
+        try:
+            old = self._store.execute("XRANGE", self._key(f"stream:{self.alias}"), "-", "+")
+            if old:
+                start_id = old[-1][0] if isinstance(old[-1][0], str) else old[-1][0].decode()
+        except Exception:
+            pass
         self._publish_resource_record()
         self._purge_stale_keys()
-        self._mailbox = StreamMailbox(self)
+        self._mailbox = StreamMailbox(self, start_id=start_id)
         self._mailbox.start()
         self._inbox_thread = threading.Thread(target=self._inbox_loop, name=f"inbox-{self.alias}", daemon=True)
         self._inbox_thread.start()
@@ -307,6 +320,8 @@ class PeerAgent:
                     pass
         self._rpc_channels.pop(peer, None)
         self._resource_cache.pop(peer, None)
+        with self._connections_lock:
+            self._desired_peers.discard(peer)  # connect_to() asks for it again if the peer returns
 
     # ------------------------------------------------------------------ discovery
     def list_agents(self) -> List[str]:
@@ -406,17 +421,38 @@ class PeerAgent:
         local_key = ResourceKey(meta.get("dst_device", ""), int(meta.get("ib_port", 1)), link)
         peer_key = ResourceKey(meta.get("src_device", ""), int(meta.get("ib_port", 1)), link)
         probe = DirectedConnection(self.alias, peer, local_key, peer_key, int(meta.get("qp_num", 1)), meta.get("profile", "default"))
+        digest = hashlib.sha1(json.dumps(info, sort_keys=True).encode()).hexdigest()
+        stale = None
         with self._connections_lock:
             conn = self._connections.get(probe.conn_id)
+            if conn is not None and conn.state == "connected":
+                if conn.peer_digest == digest:
+                    return  # the announcement this link was built from, seen again
+                # The peer announces other endpoints than the ones this link is connected to: it went away and came back
+                # under the same alias (its cleanup notice may never have reached us, e.g. after a crash). The old link is
+                # dead; drop it and shake hands again with a fresh endpoint.
+                stale = conn
+                self._connections.pop(conn.conn_id, None)
+                self._notified.discard(conn.conn_id)
+                stale.state = "closed"
+                conn = None
             if conn is None:
                 conn = self._connections[probe.conn_id] = probe
-            if conn.state == "connected":
-                return
             conn.state = "connecting"
+        if stale is not None:
+            log.info("%s: %s restarted; replacing link %s", self.alias, peer, stale.conn_id)
+            if stale.endpoint is not None:
+                try:
+                    stale.endpoint.shutdown()  # fails what was still in flight on the dead link with 403
+                except Exception:
+                    pass
+            self._rpc_channels.pop(peer, None)
+            self._resource_cache.pop(peer, None)
         try:
             ep = self._ensure_endpoint(conn)
             self._announce(conn)
             ep.connect(info)
+            conn.peer_digest = digest
         except Exception:
             with self._connections_lock:
                 conn.state = "failed"
@@ -454,7 +490,12 @@ class PeerAgent:
                     self._connected_cond.notify_all()
 
         fut.add_done_callback(_mark_failed)
-        self._client.set_desired_topology(self.alias, [peer_alias], min_bw=min_bw)
+        # The stored specification is this agent's whole desired topology (the control plane replaces it on every post and
+        # uses it to find whom to notify when this agent leaves), so every peer asked for so far is posted again.
+        with self._connections_lock:
+            self._desired_peers.add(peer_alias)
+            targets = sorted(self._desired_peers)
+        self._client.set_desired_topology(self.alias, targets, min_bw=min_bw)
         return PeerConnection(self, conn.conn_id)
 
     def _wait_connected(self, conn_id: str, timeout_sec: float = 60.0) -> None:

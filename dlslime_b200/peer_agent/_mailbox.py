@@ -25,12 +25,12 @@ log = get_logger("peer_agent.mailbox")
 
 
 class StreamMailbox:
-    def __init__(self, agent, block_ms: int = 50):
+    def __init__(self, agent, block_ms: int = 50, start_id: str = "0-0"):
         self.agent = agent
         self.block_ms = block_ms
         self._stop = threading.Event()
         self._thread: threading.Thread | None = None
-        self._last_id = "0-0"
+        self._last_id = start_id  # entries up to this id belong to an earlier incarnation of the alias
         # fault-injection hook for tests: called with the message dict, returns False to drop it
         self.message_filter = None
 

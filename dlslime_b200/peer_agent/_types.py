@@ -55,6 +55,7 @@ class DirectedConnection:
     endpoint: Any = None
     state: str = "pending"  # pending | connecting | connected | failed | closed
     remote_handles: dict = field(default_factory=dict)  # mr name -> (remote handle, cached info)
+    peer_digest: str = ""  # fingerprint of the endpoint description this link was connected to
     lock: threading.Lock = field(default_factory=threading.Lock)
 
     @property

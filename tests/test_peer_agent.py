@@ -177,3 +177,74 @@ def test_obs_reporter_snapshot_and_stopped_marker(ctrl):
         c.obs_set_enabled_for_test(False)
     stopped = json.loads(ctrl.store.get("obs:peer:A"))
     assert stopped["status"] == "stopped" and ctrl.store.pttl("obs:peer:A") <= 15_000
+
+
+def test_concurrent_full_mesh_then_rejoin_after_exit_and_after_crash(ctrl):
+    """Five agents connect to each other at the same time from five threads; every ordered pair writes. Then one agent
+    leaves cleanly and comes back under its alias, and later dies without any cleanup and comes back again: both times the
+    others shake hands anew (a peer that announces other endpoints than the ones a link is connected to has restarted)."""
+    import threading
+
+    n = 5
+    agents, bufs = [], []
+    for i in range(n):
+        a = PeerAgent(ctrl.url, alias=f"n{i}", scope="mesh")
+        b = ctypes.create_string_buffer(bytes([i + 1]) * 4096, 4096)
+        a.register_memory_region("m", ctypes.addressof(b), 0, 4096)
+        agents.append(a), bufs.append(b)
+    try:
+        errs = []
+
+        def connect_all(i):
+            try:
+                for c in [agents[i].connect_to(f"n{j}") for j in range(n) if j != i]:
+                    c.wait(20)
+            except Exception as e:  # noqa: BLE001
+                errs.append((i, repr(e)))
+
+        ths = [threading.Thread(target=connect_all, args=(i,)) for i in range(n)]
+        [t.start() for t in ths]
+        [t.join(60) for t in ths]
+        assert not errs and not any(t.is_alive() for t in ths)
+        futs = [(i, j, agents[i].write(f"n{j}", [("m", 2048, 16 * i, 16)])) for i in range(n) for j in range(n) if i != j]
+        assert all(f.wait(20) == 0 for _, _, f in futs)
+        assert all(bufs[j].raw[16 * i:16 * i + 16] == bytes([i + 1]) * 16 for i in range(n) for j in range(n) if i != j)
+        # the posted topology is cumulative, so everyone this agent connected to is told when it leaves
+        spec = json.loads(ctrl.store.get("mesh:spec:topology:n2"))
+        assert sorted(spec["target_peers"]) == ["n0", "n1", "n3", "n4"]
+
+        def rejoin(fill):
+            b = ctypes.create_string_buffer(bytes([fill]) * 4096, 4096)
+            agents[2] = PeerAgent(ctrl.url, alias="n2", scope="mesh")
+            bufs[2] = b
+            agents[2].register_memory_region("m", ctypes.addressof(b), 0, 4096)
+            for i in (0, 1, 3):
+                c1, c2 = agents[i].connect_to("n2"), agents[2].connect_to(f"n{i}")
+                c1.wait(20)
+                c2.wait(20)
+                assert agents[i].write("n2", [("m", 2048, 16 * i, 16)]).wait(20) == 0
+                assert b.raw[16 * i:16 * i + 16] == bytes([i + 1]) * 16
+                assert agents[2].write(f"n{i}", [("m", 2048, 16 * 2, 16)]).wait(20) == 0
+                assert bufs[i].raw[32:48] == bytes([fill]) * 16
+
+        agents[2].shutdown()  # clean exit: the others get a cleanup notice
+        time.sleep(0.5)
+        rejoin(77)
+        # a crash: no cleanup call, no key removed by the agent itself; its lease just runs out
+        dead = agents[2]
+        dead._client.cleanup_peer = lambda *a, **k: None
+        dead._store_delete_disabled = True
+        dead._stop.set()
+        dead._mailbox.stop()
+        for c in list(dead._connections.values()):
+            if c.endpoint is not None:
+                c.endpoint.shutdown()
+        ctrl.store.delete("mesh:agent:n2")
+        time.sleep(0.3)
+        rejoin(88)
+    finally:
+        for a in agents:
+            try:
+                a.shutdown()
+            except Exception:
+                pass
