@@ -220,8 +220,10 @@ def test_concurrent_full_mesh_then_rejoin_after_exit_and_after_crash(ctrl):
             agents[2].register_memory_region("m", ctypes.addressof(b), 0, 4096)
             for i in (0, 1, 3):
                 c1, c2 = agents[i].connect_to("n2"), agents[2].connect_to(f"n{i}")
-                c1.wait(20)
+                # the newcomer's side first: once it is up, the old agent has at least begun to replace a link that it
+                # still believed connected (after a crash nothing told it otherwise), and its handle waits for the new one
                 c2.wait(20)
+                c1.wait(20)
                 assert agents[i].write("n2", [("m", 2048, 16 * i, 16)]).wait(20) == 0
                 assert b.raw[16 * i:16 * i + 16] == bytes([i + 1]) * 16
                 assert agents[2].write(f"n{i}", [("m", 2048, 16 * 2, 16)]).wait(20) == 0
