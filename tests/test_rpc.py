@@ -158,3 +158,28 @@ def test_payload_sizes_around_the_slot_capacity():
         d.shutdown()
         w.shutdown()
         ctrl.stop()
+
+
+def test_calls_from_many_threads_share_one_channel(rpc_pair):
+    """Eight client threads on one proxy (four slots): bursts of serialised calls and parallel echoes, every reply goes
+    to its own future and the serialised method ran exactly once per call."""
+    p, svc, _ = rpc_pair
+    errs = []
+
+    def worker(t):
+        try:
+            for i in range(60):
+                if i % 3 == 0:
+                    futs = [p.add(i + k, t) for k in range(3)]
+                    assert [f.wait(20) for f in futs] == [i + k + t for k in range(3)]
+                else:
+                    payload = bytes([t]) * (i % 50)
+                    assert p.echo(payload).wait(20) == payload
+        except Exception as e:  # noqa: BLE001
+            errs.append((t, repr(e)))
+
+    ths = [threading.Thread(target=worker, args=(t,)) for t in range(8)]
+    [t.start() for t in ths]
+    [t.join(120) for t in ths]
+    assert not errs and not any(t.is_alive() for t in ths)
+    assert svc.calls == 8 * 20 * 3
