@@ -85,10 +85,28 @@ int32_t LocalMemoryPool::unregister_memory_region(int32_t handle)
     return 0;
 }
 
+// By name: a region that other names still refer to only loses this name; the last name takes the region with it.
 int32_t LocalMemoryPool::unregister_memory_region(const std::string& name)
 {
-    int32_t h = get_mr_handle(name);
-    return h < 0 ? -1 : unregister_memory_region(h);
+    int32_t h = -1;
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = by_name_.find(name);
+        if (it == by_name_.end()) return -1;
+        h = it->second;
+        std::string other;
+        for (const auto& [n, hh] : by_name_)
+            if (hh == h && n != name) {
+                other = n;
+                break;
+            }
+        if (!other.empty()) {
+            by_name_.erase(it);
+            if (regions_[static_cast<size_t>(h)].name == name) regions_[static_cast<size_t>(h)].name = other;
+            return 0;
+        }
+    }
+    return unregister_memory_region(h);
 }
 
 int32_t LocalMemoryPool::get_mr_handle(const std::string& name) const

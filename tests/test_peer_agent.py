@@ -250,3 +250,24 @@ def test_concurrent_full_mesh_then_rejoin_after_exit_and_after_crash(ctrl):
                 a.shutdown()
             except Exception:
                 pass
+
+
+def test_names_that_share_memory_are_independent(ctrl):
+    """Two logical regions on the same pointer and a window into it: all three are reachable by name from a peer, and
+    unregistering one of the two full-size names leaves the other one working."""
+    a, b = PeerAgent(ctrl.url, alias="A"), PeerAgent(ctrl.url, alias="B")
+    try:
+        src = _region(a, "src", 4096, fill=7)
+        dst = ctypes.create_string_buffer(4096)
+        b.register_memory_region("kv", ctypes.addressof(dst), 0, 4096)
+        b.register_memory_region("kv_alias", ctypes.addressof(dst), 0, 4096)
+        b.register_memory_region("kv_tail", ctypes.addressof(dst), 2048, 2048)
+        a.connect_to("B").wait(10)
+        b.connect_to("A").wait(10)
+        assert a.write("B", [("src", "kv_alias", 0, 0, 100)]).wait(10) == 0 and dst.raw[:100] == src.raw[:100]
+        assert a.write("B", [("src", "kv_tail", 100, 0, 50)]).wait(10) == 0 and dst.raw[2048:2098] == src.raw[100:150]
+        assert b.unregister_memory_region("kv_alias") and sorted(b.list_mem_keys()) == ["kv", "kv_tail"]
+        assert a.write("B", [("src", "kv", 200, 300, 10)]).wait(10) == 0 and dst.raw[300:310] == src.raw[200:210]
+    finally:
+        a.shutdown()
+        b.shutdown()
