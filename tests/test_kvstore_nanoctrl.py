@@ -234,3 +234,24 @@ def test_http_routes_survive_malformed_requests():
         assert client.register("after:1", "probe")["status"] == "ok" and client.get_entity_info("after:1")["kind"] == "probe"
     finally:
         ctrl.stop()
+
+
+def test_entities_expire_without_heartbeat_on_an_injected_clock():
+    """Through the HTTP routes: an entity lives ENTITY_TTL_SECS after its last heartbeat, a heartbeat for one that is gone
+    says not_found (the caller re-registers), and listings show only what is alive."""
+    ctrl = start_local_nanoctrl()
+    try:
+        now = [ctrl.store.now_ms()]
+        ctrl.store.set_clock(lambda: now[0])
+        cl = NanoCtrlClient(ctrl.url, scope="ttl")
+        for i in range(3):
+            assert cl.register(f"svc:{i}", "worker")["status"] == "ok"
+        assert sorted(e["entity_id"] for e in cl.list_entities(kind="worker")) == ["svc:0", "svc:1", "svc:2"]
+        now[0] += (c.ctrl.ENTITY_TTL_SECS - 1) * 1000
+        assert cl.heartbeat("svc:0") == "ok"
+        now[0] += 2_000
+        assert sorted(e["entity_id"] for e in cl.list_entities(kind="worker")) == ["svc:0"]
+        assert cl.heartbeat("svc:1") == "not_found" and cl.get_entity_info("svc:2") is None
+        assert cl.register("svc:1", "worker")["status"] == "ok" and cl.heartbeat("svc:1") == "ok"
+    finally:
+        ctrl.stop()
