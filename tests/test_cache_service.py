@@ -110,3 +110,59 @@ def test_http_service_survives_malformed_requests():
         assert post_json(http.url, "/query", {"peer_agent_id": "after", "version": m["version"]}) == m
     finally:
         http.stop()
+
+
+def test_concurrent_engines_put_get_delete_and_no_slab_leaks():
+    """Four engines, each with its own PeerAgent, put / get / delete random extents at the same time: every read-back is
+    byte exact and the directory ends with every slab free."""
+    import random
+    import threading
+
+    from dlslime_b200.peer_agent import PeerAgent
+
+    ctrl = start_local_nanoctrl()
+    srv = CacheServer(ctrl.url, slab_size=128 * K, memory_size=16 << 20, alias="cache-agent:0")
+    errs = []
+
+    def engine(k):
+        ag = None
+        try:
+            ag = PeerAgent(ctrl.url, alias=f"engine:{k}")
+            rnd = random.Random(k)
+            n = 1 << 20
+            buf = ctypes.create_string_buffer(rnd.randbytes(n), n)
+            orig = buf.raw
+            ag.register_memory_region("kv", ctypes.addressof(buf), 0, n)
+            cl = CacheClient(ctrl=ctrl.url, peer_agent=ag)
+            cl.connect_to_server()
+            live = []
+
+            def read_back(v, o, ln):
+                ctypes.memset(ctypes.addressof(buf) + o, 0, ln)
+                cl.get("kv", ag.alias, v)
+                assert buf.raw[o:o + ln] == orig[o:o + ln], (k, v)
+                assert cl.delete(ag.alias, v)
+
+            for _ in range(10):
+                off, ln = rnd.randrange(0, n - 300_000), rnd.choice([1, 4096, 128 * K, 200_000, 300_000])
+                live.append((cl.put("kv", [(off, ln)])["version"], off, ln))
+                if len(live) > 2 and rnd.random() < 0.5:
+                    read_back(*live.pop(rnd.randrange(len(live))))
+            for item in live:
+                read_back(*item)
+        except Exception as e:  # noqa: BLE001
+            errs.append((k, repr(e)))
+        finally:
+            if ag is not None:
+                ag.shutdown()
+
+    try:
+        ths = [threading.Thread(target=engine, args=(k,)) for k in range(4)]
+        [t.start() for t in ths]
+        [t.join(120) for t in ths]
+        assert not errs and not any(t.is_alive() for t in ths), errs
+        st = srv.service.stats()
+        assert st.used_slabs == 0 and st.free_slabs == st.num_slabs and st.num_assignment_entries == 0
+    finally:
+        srv.stop()
+        ctrl.stop()
