@@ -82,7 +82,9 @@ char* b_endpoint_info(void* h)
 int b_endpoint_connect(void* h, const char* info_json, char* err, size_t err_len)
 {
     try {
-        return static_cast<EpBox*>(h)->ep->connect(Json::parse(info_json));
+        const int rc = static_cast<EpBox*>(h)->ep->connect(Json::parse(info_json));
+        if (rc != 0) set_err(err, err_len, "the endpoint refused the peer's description (wrong kind of endpoint, or unreachable); see the log");
+        return rc;
     }
     catch (const std::exception& e) {
         set_err(err, err_len, e.what());

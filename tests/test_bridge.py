@@ -63,3 +63,39 @@ def test_bad_requests_report_instead_of_crashing():
     assert ep
     assert b.endpoint_connect(ep, b"{not json", err, 256) != 0 and err.value
     b.endpoint_destroy(ep)
+
+
+def test_rdma_endpoints_through_the_table_on_the_software_fabric():
+    """transport "rdma" builds RC endpoints (here on the in-process fabric); mixing kinds is refused with a message."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = textwrap.dedent("""
+        import ctypes as C, sys
+        sys.path.insert(0, %r)
+        from test_bridge import Bridge, _info
+        from dlslime_b200 import _slime_c
+        b = Bridge.from_address(_slime_c.bridge_table())
+        err = C.create_string_buffer(256)
+        x, y = b.endpoint_create(b"rdma", b"", 0, err, 256), b.endpoint_create(b"rdma", b"", 1, err, 256)
+        t = b.endpoint_create(b"tcp", b"127.0.0.1", 2, err, 256)
+        assert x and y and t and b.endpoint_kind(x) == b"rdma" and b.endpoint_kind(t) == b"tcp"
+        ix, iy, it = _info(b, x), _info(b, y), _info(b, t)
+        assert b.endpoint_connect(x, it, err, 256) != 0 and err.value   # an RC endpoint cannot take a TCP description
+        assert b.endpoint_connect(x, iy, err, 256) == 0 and b.endpoint_connect(y, ix, err, 256) == 0
+        src = C.create_string_buffer(bytes(range(250)) * 400, 100_000)
+        dst = C.create_string_buffer(100_000)
+        r, s = b.recv(y, C.addressof(dst), 100_000), b.send(x, C.addressof(src), 100_000)
+        assert b.future_wait(s, 10_000) == 0 and b.future_wait(r, 10_000) == 0 and dst.raw == src.raw
+        for f in (s, r):
+            b.future_free(f)
+        for e in (x, y, t):
+            b.endpoint_destroy(e)
+        print("ok")
+    """ % os.path.join(repo, "tests"))
+    res = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, PYTHONPATH=repo, SLIME_RDMA_PROVIDER="loopback"),
+                         capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0 and "ok" in res.stdout, res.stdout[-1500:] + res.stderr[-1500:]
