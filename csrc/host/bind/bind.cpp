@@ -67,8 +67,10 @@ static void bind_future(py::module_& m, const char* name)
              py::arg("timeout") = -1.0, py::call_guard<py::gil_scoped_release>(),
              "Block until the operation completed; returns the status (0 ok, 402 timeout, 403 failed).")
         .def("done", &Fut::done)
-        .def("wait_on_stream", &Fut::wait_on_stream,
-             "Make the stream given at submission wait on the device for this operation (stream-ordered signals only).");
+        .def("wait_on_stream", &Fut::wait_on_stream, py::arg("limit_ms") = 0.0,
+             "Make the stream given at submission wait on the device for this operation (stream-ordered signals only). "
+             "The wait is bounded (limit_ms, else SLIME_STREAM_WAIT_MS, else 1 s); if it runs out, wait() returns 402.")
+        .def("stream_wait_timed_out", &Fut::stream_wait_timed_out);
 }
 
 PYBIND11_MODULE(_slime_c, m)
@@ -148,6 +150,8 @@ PYBIND11_MODULE(_slime_c, m)
         .def("force_complete", &DeviceSignal::force_complete)
         .def("bind_stream", [](DeviceSignal& s, uintptr_t stream) { s.bind_stream(reinterpret_cast<void*>(stream)); })
         .def("wait_comm_done_on_stream", &DeviceSignal::wait_comm_done_on_stream, py::arg("mask") = 1)
+        .def("stream_wait_timed_out", &DeviceSignal::stream_wait_timed_out)
+        .def("set_stream_wait_limit_ms", [](DeviceSignal& s, double ms) { s.set_stream_wait_limit_ns(static_cast<unsigned long long>(ms * 1e6)); })
         .def("reset_all", &DeviceSignal::reset_all);
     // Addresses of four C functions (see StreamHooks); the kernel library's loader passes its own.
     m.def("install_stream_hooks", [](uintptr_t alloc_words, uintptr_t free_words, uintptr_t record_value, uintptr_t wait_mask) {
@@ -166,12 +170,14 @@ PYBIND11_MODULE(_slime_c, m)
         .def("wait", [](const ReadWriteFuture& f, double timeout) { return f.wait(timeout < 0 ? -1 : static_cast<int64_t>(timeout * 1000)); },
              py::arg("timeout") = -1.0, py::call_guard<py::gil_scoped_release>())
         .def("done", &ReadWriteFuture::done)
-        .def("wait_on_stream", &ReadWriteFuture::wait_on_stream);
+        .def("wait_on_stream", &ReadWriteFuture::wait_on_stream, py::arg("limit_ms") = 0.0)
+        .def("stream_wait_timed_out", &ReadWriteFuture::stream_wait_timed_out);
     py::class_<ImmRecvFuture, std::shared_ptr<ImmRecvFuture>>(m, "SlimeImmRecvFuture")
         .def("wait", [](const ImmRecvFuture& f, double timeout) { return f.wait(timeout < 0 ? -1 : static_cast<int64_t>(timeout * 1000)); },
              py::arg("timeout") = -1.0, py::call_guard<py::gil_scoped_release>())
         .def("done", &ImmRecvFuture::done)
-        .def("wait_on_stream", &ImmRecvFuture::wait_on_stream)
+        .def("wait_on_stream", &ImmRecvFuture::wait_on_stream, py::arg("limit_ms") = 0.0)
+        .def("stream_wait_timed_out", &ImmRecvFuture::stream_wait_timed_out)
         .def("imm_data", &ImmRecvFuture::imm_data)
         .def("time_trace_enabled", &ImmRecvFuture::time_trace_enabled)
         .def("time_trace_start_ns", &ImmRecvFuture::time_trace_start_ns)

@@ -59,7 +59,10 @@ public:
     int32_t wait(int64_t timeout_ms = -1) const override
     {
         if (!st_->signal->wait_comm_done_cpu(st_->expected_mask, timeout_ms)) return TIME_OUT;
-        return st_->completion_status.load(std::memory_order_acquire);
+        const int32_t s = st_->completion_status.load(std::memory_order_acquire);
+        // a stream that gave up waiting for this operation ran its consumers without the data
+        if (s == SUCCESS && st_->signal->stream_wait_timed_out()) return TIME_OUT;
+        return s;
     }
     bool done() const
     {
@@ -67,7 +70,14 @@ public:
     }
     // Makes the stream the operation was submitted with wait (bounded, on the device) for its completion; a no-op for
     // host-only signals.
-    void wait_on_stream() const { st_->signal->wait_comm_done_on_stream(st_->expected_mask); }
+    // limit_ms > 0 sets the time limit of this wait (default: SLIME_STREAM_WAIT_MS, else 1 s). If the limit runs out,
+    // wait() reports TIME_OUT from then on, whatever the transfer itself does later.
+    void wait_on_stream(double limit_ms = 0.0) const
+    {
+        if (limit_ms > 0) st_->signal->set_stream_wait_limit_ns(static_cast<unsigned long long>(limit_ms * 1e6));
+        st_->signal->wait_comm_done_on_stream(st_->expected_mask);
+    }
+    bool stream_wait_timed_out() const { return st_->signal->stream_wait_timed_out(); }
     const std::shared_ptr<EndpointOpState>& state() const { return st_; }
 
 protected:

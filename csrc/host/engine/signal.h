@@ -13,6 +13,7 @@
 #include <chrono>
 #include <condition_variable>
 #include <cstdint>
+#include <cstdlib>
 #include <functional>
 #include <memory>
 #include <mutex>
@@ -33,6 +34,11 @@ public:
     virtual void     set_comm_done(int lane)                        = 0;
     virtual void     bind_stream(void* stream)                      = 0;
     virtual void     wait_comm_done_on_stream(uint32_t mask)        = 0;
+    // True once a stream-ordered wait gave up at its time limit: what was queued behind it on the stream ran without
+    // the transferred bytes, so the operation must not be reported as a success.
+    virtual bool     stream_wait_timed_out() const { return false; }
+    // Time limit of the stream-ordered wait in nanoseconds (0 = the process default, SLIME_STREAM_WAIT_MS or 1 s).
+    virtual void     set_stream_wait_limit_ns(unsigned long long) {}
     // Blocks until (done & mask) == mask or force_complete(); timeout_ms < 0 waits for ever.
     // Returns false on timeout.
     virtual bool wait_comm_done_cpu(uint32_t mask, int64_t timeout_ms = -1) = 0;
@@ -48,8 +54,10 @@ struct StreamHooks {
     int (*free_words)(void* host)                                                                   = nullptr;
     // enqueue on `stream`: *word = value (release at system scope): "the buffer is ready once this has run"
     int (*record_value)(void* stream, void* dev_word, unsigned long long value)                     = nullptr;
-    // enqueue on `stream`: wait (bounded) until (*word & mask) == mask
-    int (*wait_mask)(void* stream, void* dev_word, unsigned long long mask, unsigned long long limit_ns) = nullptr;
+    // enqueue on `stream`: wait (bounded) until (*word & mask) == mask; when the limit runs out first, store 1 to
+    // *timeout_word (release at system scope) and return
+    int (*wait_mask)(void* stream, void* dev_word, unsigned long long mask, unsigned long long limit_ns,
+                     void* dev_timeout_word) = nullptr;
     bool installed() const { return alloc_words && free_words && record_value && wait_mask; }
 };
 inline StreamHooks& stream_hooks()
@@ -112,11 +120,12 @@ private:
     std::condition_variable cv_;
 };
 
-// Pool of device-addressable words (two per signal), allocated from the hooks in chunks and recycled.
+// Pool of device-addressable words (four per signal: ready, done, wait-timed-out, spare), allocated from the hooks in
+// chunks and recycled.
 class MappedWordPool {
 public:
     struct Pair {
-        std::atomic<unsigned long long>* host = nullptr;  // [2]
+        std::atomic<unsigned long long>* host = nullptr;  // [4]
         void*                            dev  = nullptr;  // device address of host[0]
     };
     static MappedWordPool& get()
@@ -130,9 +139,9 @@ public:
         if (free_.empty()) {
             constexpr unsigned long long kPairs = 128;
             void *h = nullptr, *d = nullptr;
-            if (!stream_hooks().installed() || stream_hooks().alloc_words(2 * kPairs, &h, &d) != 0) return false;
+            if (!stream_hooks().installed() || stream_hooks().alloc_words(4 * kPairs, &h, &d) != 0) return false;
             for (unsigned long long i = 0; i < kPairs; ++i)
-                free_.push_back(Pair{reinterpret_cast<std::atomic<unsigned long long>*>(h) + 2 * i, static_cast<char*>(d) + 16 * i});
+                free_.push_back(Pair{reinterpret_cast<std::atomic<unsigned long long>*>(h) + 4 * i, static_cast<char*>(d) + 32 * i});
         }
         out = free_.back();
         free_.pop_back();
@@ -149,11 +158,25 @@ private:
     std::vector<Pair> free_;
 };
 
-// DeviceSignal whose two words the GPU can read and write: "ready" is set by a one-thread kernel in stream order
+// Process default of the stream-ordered wait's time limit.
+inline unsigned long long default_stream_wait_ns()
+{
+    static const unsigned long long ns = [] {
+        const char* raw = std::getenv("SLIME_STREAM_WAIT_MS");
+        char*       end = nullptr;
+        const double ms = raw ? std::strtod(raw, &end) : 0.0;
+        return (raw && end && *end == 0 && ms > 0) ? static_cast<unsigned long long>(ms * 1e6) : 1000000000ull;
+    }();
+    return ns;
+}
+
+// DeviceSignal whose words the GPU can read and write: "ready" is set by a one-thread kernel in stream order
 // (so the transfer engine posts only after the producer kernels on that stream have finished), "done" can be waited
 // for by a bounded one-thread kernel in stream order (so consumer kernels queue behind the transfer without a host
 // round trip). The reference does this with cuStreamWriteValue32 / cuStreamWaitValue32
-// (dlslime/csrc/device/cuda/cuda_signal.h:40-118 in the reference); kernels give the wait a time limit.
+// (dlslime/csrc/device/cuda/cuda_signal.h:40-118 in the reference); kernels give the wait a time limit, and a wait
+// that runs into it sets the third word, which turns the operation's status into TIME_OUT (402): the stream went on
+// without the data, and the caller must be told.
 class MappedSignal final: public DeviceSignal {
 public:
     explicit MappedSignal(const MappedWordPool::Pair& w): w_(w) { reset_all(); }
@@ -176,8 +199,12 @@ public:
     void wait_comm_done_on_stream(uint32_t mask) override
     {
         SLIME_NVTX_RANGE("slime.signal.wait_comm_done_on_stream", kNvtxSignal);
-        if (stream_ != nullptr) stream_hooks().wait_mask(stream_, static_cast<char*>(w_.dev) + 8, mask, 0ull);
+        if (stream_ != nullptr)
+            stream_hooks().wait_mask(stream_, static_cast<char*>(w_.dev) + 8, mask, limit_ns_ ? limit_ns_ : default_stream_wait_ns(),
+                                     static_cast<char*>(w_.dev) + 16);
     }
+    bool stream_wait_timed_out() const override { return w_.host[2].load(std::memory_order_acquire) != 0; }
+    void set_stream_wait_limit_ns(unsigned long long ns) override { limit_ns_ = ns; }
     bool wait_comm_done_cpu(uint32_t mask, int64_t timeout_ms = -1) override
     {
         SLIME_NVTX_RANGE("slime.signal.wait_comm_done_cpu", kNvtxWait);
@@ -204,6 +231,7 @@ public:
     {
         w_.host[0].store(0, std::memory_order_relaxed);
         w_.host[1].store(0, std::memory_order_relaxed);
+        w_.host[2].store(0, std::memory_order_relaxed);
         forced_.store(false, std::memory_order_release);
     }
 
@@ -214,6 +242,7 @@ private:
         cv_.notify_all();
     }
     MappedWordPool::Pair    w_;
+    unsigned long long      limit_ns_ = 0;
     std::atomic<bool>       forced_{false};
     void*                   stream_ = nullptr;
     std::mutex              mu_;

@@ -3,6 +3,7 @@
 #include <cstring>
 #include <stdexcept>
 
+#include "core/env.h"
 #include "core/log.h"
 
 namespace slime {
@@ -88,7 +89,10 @@ void RpcSession::post_committed(uint32_t tag, uint64_t request_id, uint32_t targ
                                                       static_cast<uint64_t>(target_slot) * slot_size_, 0, h.total_len)};
     auto fut = ep_->write_with_imm(assign, static_cast<int32_t>(target_slot));
     // the single send buffer may be reused as soon as the write completed
-    const int32_t st = fut->wait(-1);
+    // bounded like every other host wait: a peer that stops draining must not hold send_mu_ for ever
+    static const int64_t post_ms = get_env<int64_t>("SLIME_RPC_POST_TIMEOUT_MS", 30000);
+    const int32_t st = fut->wait(post_ms > 0 ? post_ms : 30000);
+    if (st == TIME_OUT) throw std::runtime_error("rpc session: write did not complete within " + std::to_string(post_ms) + " ms (status 402)");
     if (st != SUCCESS) throw std::runtime_error("rpc session: write failed with status " + std::to_string(st));
 }
 

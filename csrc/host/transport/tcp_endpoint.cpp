@@ -11,6 +11,7 @@
 #include <sys/types.h>
 #include <unistd.h>
 
+#include "core/env.h"
 #include "core/log.h"
 #include "obs/obs.h"
 
@@ -526,7 +527,22 @@ void TcpEndpoint::server_loop(int fd)
             if (ok && !send_all(fd, reinterpret_cast<const void*>(r.addr + h.offset), h.length)) break;
         }
         else if (h.kind == REQ_SEND) {
-            std::vector<uint8_t> payload(h.length);
+            // The length comes from the peer: a corrupt or hostile header must neither pin gigabytes of host memory
+            // nor take the process down with an allocation failure inside this thread. Above the limit
+            // (SLIME_TCP_MAX_MESSAGE_BYTES, default 1 GiB) the connection is closed.
+            static const uint64_t max_msg = get_env<uint64_t>("SLIME_TCP_MAX_MESSAGE_BYTES", 1ull << 30);
+            if (h.length > max_msg) {
+                SLIME_LOG_WARN("tcp endpoint: message of ", h.length, " bytes exceeds the limit of ", max_msg, "; closing the connection");
+                break;
+            }
+            std::vector<uint8_t> payload;
+            try {
+                payload.resize(h.length);
+            }
+            catch (const std::exception&) {
+                SLIME_LOG_WARN("tcp endpoint: no memory for a message of ", h.length, " bytes; closing the connection");
+                break;
+            }
             if (h.length && !recv_all(fd, payload.data(), h.length)) break;
             deliver_message(std::move(payload));
             WireHdr ack;

@@ -31,7 +31,8 @@ int slime_signal_flag_kernel(void* flag, unsigned long long value, int add, void
 // cudaMalloc-backed region with a CUDA IPC handle (64 bytes) that other
 // processes on the node can map. Returns the device pointer in *ptr.
 int slime_hook_record_value(void* stream, void* dev_word, unsigned long long value);
-int slime_hook_wait_mask(void* stream, void* dev_word, unsigned long long mask, unsigned long long limit_ns);
+int slime_hook_wait_mask(void* stream, void* dev_word, unsigned long long mask, unsigned long long limit_ns,
+                         void* dev_timeout_word);
 int slime_symm_alloc(unsigned long long bytes, void** ptr, unsigned char* ipc_handle_out64);
 int slime_symm_free(void* ptr);
 int slime_ipc_get_handle(const void* ptr, unsigned char* ipc_handle_out64, unsigned long long* offset_out,
@@ -116,6 +117,10 @@ int   slime_nvlink_ep_register_remote(void* ep, const char* name, const unsigned
                                       unsigned long long length, unsigned long long addr, int same_process);
 int   slime_nvlink_ep_handle(void* ep, const char* name, int remote);
 unsigned long long slime_nvlink_ep_remote_addr(void* ep, int handle);
+// out4 = {code, site, block, aux} of the endpoint's kernel status page (code 0 = ok, 402 = a copy never landed, in which
+// case the batch's completion word was withheld)
+int slime_nvlink_ep_status(void* ep, unsigned int* out4);
+int slime_nvlink_ep_status_clear(void* ep);
 // tuples: n x {local_handle, remote_handle, remote_offset, local_offset, length} as u64.
 int slime_nvlink_ep_transfer(void* ep, const unsigned long long* tuples, int n, int is_write, void* signal,
                              unsigned long long signal_value, int signal_add, int max_blocks, void* stream);

@@ -24,9 +24,11 @@
 //    every GPU that loads the library, held until the process exits.
 //  * The first call on each device looks up the device address of that array (one query,
 //    cached per device). Make that first call during start-up, outside any stream capture.
-//  * The segment table is copied from the caller's host arrays with an ordinary asynchronous
-//    memory copy; with pageable host arrays the copy has finished reading them when the call
-//    returns.
+//  * The segment table is built from the caller's host arrays while the call runs and copied
+//    to the device with ordinary asynchronous copies from pageable memory, which have finished
+//    reading their source when the call returns. For the same reason a stream that is being
+//    captured is refused with an error.
+//  * Zero-length segments are allowed anywhere in the batch and move nothing.
 //  * Every call on a device uses the same array. Calls whose kernels could overlap on the
 //    GPU (different streams, no ordering between them) would overwrite each other's table:
 //    issue them on one stream, or order them with events.

@@ -73,14 +73,19 @@ inline int make_tmap_2d(CUtensorMap* tm, const void* base, CUtensorMapDataType d
     return 0;
 }
 
+// Multiprocessor count of the current device (cached per device ordinal: a process may drive several GPUs).
 inline int sm_count()
 {
-    static int n = 0;
+    constexpr int kMaxDev = 64;
+    static int    cached[kMaxDev] = {0};
+    int           dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= kMaxDev) dev = 0;
+    int n = cached[dev];
     if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
         if (n <= 0) n = 148;
+        cached[dev] = n;
     }
     return n;
 }

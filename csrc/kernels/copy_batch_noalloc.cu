@@ -112,6 +112,12 @@ int slime_copy_batch_noalloc(const unsigned long long* dst, const unsigned long 
     if (n == 0) return 0;
     if (dst == nullptr || src == nullptr || len == nullptr) return fail("no-alloc copy: null argument array");
     cudaStream_t   stream  = static_cast<cudaStream_t>(stream_v);
+    // The table below is copied from this function's stack at call time; a capturing stream would record the
+    // copy for later instead, when the stack is gone.
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    SLIME_CUDA_OK(cudaStreamIsCapturing(stream, &capturing));
+    if (capturing != cudaStreamCaptureStatusNone)
+        return fail("no-alloc copy: the stream is being captured; this call reads its arguments when it is made");
     unsigned char* scratch = nullptr;
     if (scratch_for_current_device(&scratch)) return -1;
 

@@ -49,6 +49,8 @@ struct CopyArgs {
     unsigned long long  signal_value;
     int                 signal_add;
     unsigned int*       block_counter;
+    unsigned long long  unit_bytes;  // work unit: kUnitBytes, or smaller so that several CTAs share one piece
+    KernelStatus*       status;      // where a wait that ran out is recorded (mapped host memory; may be null)
 };
 
 __device__ __forceinline__ void copy_unit(unsigned char* dst, const unsigned char* src, unsigned long long n)
@@ -103,8 +105,8 @@ __global__ void __launch_bounds__(kThreads) p2p_scatter_gather_kernel(CopyArgs a
             s_seg = a.table ? a.table[lo] : inl.seg[lo];
         }
         __syncthreads();
-        const unsigned long long off = (u - s_seg.first_unit) * kUnitBytes;
-        const unsigned long long n   = min(kUnitBytes, s_seg.len - off);
+        const unsigned long long off = (u - s_seg.first_unit) * a.unit_bytes;
+        const unsigned long long n   = min(a.unit_bytes, s_seg.len - off);
         copy_unit(reinterpret_cast<unsigned char*>(s_seg.dst + off), reinterpret_cast<const unsigned char*>(s_seg.src + off), n);
         __syncthreads();
     }
@@ -127,15 +129,61 @@ __global__ void __launch_bounds__(kThreads) p2p_scatter_gather_kernel(CopyArgs a
 }
 
 // The same batch through the bulk-copy engine, for batches whose addresses and lengths are all multiples of 16 bytes.
-// One thread per CTA drives a ring of shared-memory buffers: a 64 KiB unit is fetched with up to eight 8 KiB
-// global -> shared bulk loads that are all in flight together (loads from peer memory included), and every chunk
-// is handed on with a shared -> global bulk store as soon as it has landed. Measured between two GPUs it moves
-// data exactly as fast as the 256-thread load/store kernel (contiguous 768 / 707 GB/s read / write, 4096 scattered
-// 64 KiB pieces 264 / 668 GB/s): the scattered read is limited by the remote side (every piece touches another
-// page of a 4 GiB region), not by how the copy is issued. What the engine buys is occupancy: one warp per CTA
-// instead of eight, so a transfer that runs beside compute kernels takes almost no issue slots from them.
+// One thread per CTA drives a ring of shared-memory buffers over the CTA's whole sequence of 8 KiB chunks (unit after
+// unit, with no drain between units): global -> shared bulk loads (peer memory included) run ahead of the shared ->
+// global bulk stores by the ring depth, and a buffer is reloaded as soon as the copy engine has read it. What the
+// engine buys over the 256-thread load/store kernel is occupancy: one warp per CTA instead of eight, so a transfer
+// that runs beside compute kernels takes almost no issue slots from them.
+//
+// A wait that runs out is recorded in the status page, the CTA stops issuing, and the batch's completion word is NOT
+// published (by any CTA: the last one to report in looks at the status page first), so a future on it times out
+// instead of reporting bytes that never landed.
 constexpr int kBulkBufs  = 8;
 constexpr int kBulkChunk = 8192;
+constexpr int kBulkLag   = 2;  // stores that may still be reading their buffers when the next load is issued
+
+struct BulkCursor {
+    unsigned long long unit;   // current unit (blockIdx.x, + gridDim.x, ...)
+    unsigned long long src, dst, bytes;  // of the unit
+    unsigned long long done;   // bytes of the unit already consumed by this cursor
+    bool               valid;
+};
+
+__device__ __forceinline__ void bulk_cursor_load_unit(const CopyArgs& a, const InlineBatch& inl, BulkCursor& c)
+{
+    c.valid = c.unit < a.n_units;
+    if (!c.valid) return;
+    int lo = 0, hi = a.n_seg - 1;
+    while (lo < hi) {
+        const int                mid = (lo + hi + 1) >> 1;
+        const unsigned long long fu  = a.table ? a.table[mid].first_unit : inl.seg[mid].first_unit;
+        if (fu <= c.unit)
+            lo = mid;
+        else
+            hi = mid - 1;
+    }
+    const Segment            seg = a.table ? a.table[lo] : inl.seg[lo];
+    const unsigned long long off = (c.unit - seg.first_unit) * a.unit_bytes;
+    c.src   = seg.src + off;
+    c.dst   = seg.dst + off;
+    c.bytes = min(a.unit_bytes, seg.len - off);
+    c.done  = 0;
+}
+
+// Returns the size of the cursor's next chunk and its addresses, and advances the cursor.
+__device__ __forceinline__ uint32_t bulk_cursor_next(const CopyArgs& a, const InlineBatch& inl, BulkCursor& c,
+                                                     unsigned long long* src, unsigned long long* dst)
+{
+    const uint32_t n = static_cast<uint32_t>(min(static_cast<unsigned long long>(kBulkChunk), c.bytes - c.done));
+    *src = c.src + c.done;
+    *dst = c.dst + c.done;
+    c.done += n;
+    if (c.done >= c.bytes) {
+        c.unit += gridDim.x;
+        bulk_cursor_load_unit(a, inl, c);
+    }
+    return n;
+}
 
 __global__ void __launch_bounds__(32) p2p_bulk_kernel(CopyArgs a, InlineBatch inl)
 {
@@ -144,51 +192,54 @@ __global__ void __launch_bounds__(32) p2p_bulk_kernel(CopyArgs a, InlineBatch in
     if (threadIdx.x == 0) {
         for (int b = 0; b < kBulkBufs; ++b) mbar_init(&bars[b], 1);
         fence_mbar_init();
-        unsigned int parity = 0;  // bit c: phase of barrier c
-        bool         ok     = true;
-        for (unsigned long long u = blockIdx.x; u < a.n_units && ok; u += gridDim.x) {
-            int lo = 0, hi = a.n_seg - 1;
-            while (lo < hi) {
-                const int                mid = (lo + hi + 1) >> 1;
-                const unsigned long long fu  = a.table ? a.table[mid].first_unit : inl.seg[mid].first_unit;
-                if (fu <= u)
-                    lo = mid;
-                else
-                    hi = mid - 1;
+        BulkCursor ld{}, st{};
+        ld.unit = st.unit = blockIdx.x;
+        bulk_cursor_load_unit(a, inl, ld);
+        bulk_cursor_load_unit(a, inl, st);
+        unsigned long long n_ld = 0, n_st = 0;
+        auto issue_load = [&]() {
+            const int          b = static_cast<int>(n_ld % kBulkBufs);
+            unsigned long long src, dst;
+            const uint32_t     bytes = bulk_cursor_next(a, inl, ld, &src, &dst);
+            mbar_arrive_expect_tx(&bars[b], bytes);
+            bulk_load_g2s(bulk_smem + b * kBulkChunk, reinterpret_cast<const void*>(src), bytes, &bars[b]);
+            ++n_ld;
+        };
+        while (n_ld < kBulkBufs - kBulkLag && ld.valid) issue_load();
+        bool ok = true;
+        while (st.valid) {
+            const int b = static_cast<int>(n_st % kBulkBufs);
+            if (!mbar_wait(&bars[b], static_cast<uint32_t>((n_st / kBulkBufs) & 1), a.status, 20, b)) {
+                ok = false;  // the load never landed: stop issuing, leave through the common exit
+                break;
             }
-            const Segment            seg = a.table ? a.table[lo] : inl.seg[lo];
-            const unsigned long long off = (u - seg.first_unit) * kUnitBytes;
-            const unsigned long long n   = min(kUnitBytes, seg.len - off);
-            const int                nch = static_cast<int>((n + kBulkChunk - 1) / kBulkChunk);
-            tma_store_wait_read<0>();  // the stores of the previous unit have left the buffers
-            for (int c = 0; c < nch; ++c) {
-                const unsigned long long o     = static_cast<unsigned long long>(c) * kBulkChunk;
-                const uint32_t           bytes = static_cast<uint32_t>(min(static_cast<unsigned long long>(kBulkChunk), n - o));
-                mbar_arrive_expect_tx(&bars[c], bytes);
-                bulk_load_g2s(bulk_smem + c * kBulkChunk, reinterpret_cast<const void*>(seg.src + off + o), bytes, &bars[c]);
-            }
-            for (int c = 0; c < nch; ++c) {
-                const unsigned long long o     = static_cast<unsigned long long>(c) * kBulkChunk;
-                const uint32_t           bytes = static_cast<uint32_t>(min(static_cast<unsigned long long>(kBulkChunk), n - o));
-                if (!mbar_wait(&bars[c], (parity >> c) & 1u, nullptr, 20, c)) {
-                    ok = false;  // the load never landed: stop issuing, leave through the common exit
-                    break;
-                }
-                parity ^= 1u << c;
-                bulk_store_s2g(reinterpret_cast<void*>(seg.dst + off + o), bulk_smem + c * kBulkChunk, bytes);
-                tma_store_commit();
+            unsigned long long src, dst;
+            const uint32_t     bytes = bulk_cursor_next(a, inl, st, &src, &dst);
+            bulk_store_s2g(reinterpret_cast<void*>(dst), bulk_smem + b * kBulkChunk, bytes);
+            tma_store_commit();
+            ++n_st;
+            if (ld.valid) {
+                // the buffer the next load goes into was read by store number n_ld - kBulkBufs, which is at least
+                // kBulkLag stores back: wait until only the most recent kBulkLag stores may still be reading
+                tma_store_wait_read<kBulkLag>();
+                issue_load();
             }
         }
         tma_store_wait<0>();  // every byte has been written before the CTA reports in
         fence_proxy_async();
+        (void)ok;
         if (a.signal != nullptr) {
             fence_acq_rel_sys();
             if (atomicAdd(a.block_counter, 1u) == gridDim.x - 1) {
                 fence_acq_rel_sys();
-                if (a.signal_add)
-                    red_add_release_sys(a.signal, a.signal_value);
-                else
-                    st_release_sys(a.signal, a.signal_value);
+                // a CTA whose wait ran out has recorded it before counting itself in
+                const bool failed = a.status != nullptr && *reinterpret_cast<volatile unsigned int*>(&a.status->code) != 0;
+                if (!failed) {
+                    if (a.signal_add)
+                        red_add_release_sys(a.signal, a.signal_value);
+                    else
+                        st_release_sys(a.signal, a.signal_value);
+                }
                 *a.block_counter = 0;
             }
         }
@@ -224,6 +275,9 @@ struct Endpoint {
     unsigned int*              counters  = nullptr;  // one block counter per staging slot
     int                        next_counter = 0;
     int                        device = 0;
+    KernelStatus*              status_host = nullptr;  // mapped page the bulk kernel reports into
+    KernelStatus*              status_dev  = nullptr;
+    std::mutex                 submit_mu;  // the staging-slot and counter cursors, when threads share an endpoint
 };
 
 int ensure_staging(Endpoint* ep)
@@ -232,7 +286,23 @@ int ensure_staging(Endpoint* ep)
     SLIME_CUDA_OK(cudaGetDevice(&ep->device));
     SLIME_CUDA_OK(cudaMalloc(&ep->counters, sizeof(unsigned int) * 64));
     SLIME_CUDA_OK(cudaMemset(ep->counters, 0, sizeof(unsigned int) * 64));
+    void *sh = nullptr, *sd = nullptr;
+    if (slime_status_alloc(&sh, &sd)) return -1;
+    ep->status_host = static_cast<KernelStatus*>(sh);
+    ep->status_dev  = static_cast<KernelStatus*>(sd);
     return 0;
+}
+
+// Work unit of the batched kernels. 64 KiB by default; SLIME_NVLINK_UNIT_KB (16 .. 1024, a multiple of 16) overrides
+// it, e.g. 16 so that four CTAs work on each 64 KiB piece at the same time.
+unsigned long long unit_bytes_setting()
+{
+    static const unsigned long long v = [] {
+        const char* raw = std::getenv("SLIME_NVLINK_UNIT_KB");
+        const long  kb  = raw ? std::strtol(raw, nullptr, 10) : 0;
+        return (kb >= 16 && kb <= 1024 && kb % 16 == 0) ? static_cast<unsigned long long>(kb) << 10 : kUnitBytes;
+    }();
+    return v;
 }
 
 int ensure_slot(StagingSlot& s)
@@ -264,6 +334,7 @@ int slime_nvlink_ep_destroy(void* h)
         if (s.done) cudaEventDestroy(s.done);
     }
     if (ep->counters) cudaFree(ep->counters);
+    if (ep->status_host) slime_status_free(ep->status_host);
     delete ep;
     return 0;
 }
@@ -388,6 +459,28 @@ unsigned long long slime_nvlink_ep_remote_addr(void* h, int handle)
     return ep->remote[handle].addr;
 }
 
+// Status page of the endpoint's kernels: code (0 = ok, 402 = a copy never landed), site, block and aux word.
+// Returns 0 and zeros when no kernel of this endpoint has run yet.
+int slime_nvlink_ep_status(void* h, unsigned int* out4)
+{
+    Endpoint* ep = static_cast<Endpoint*>(h);
+    out4[0] = out4[1] = out4[2] = out4[3] = 0;
+    if (ep == nullptr || ep->status_host == nullptr) return 0;
+    const volatile KernelStatus* st = ep->status_host;
+    out4[0] = st->code;
+    out4[1] = st->where;
+    out4[2] = st->block;
+    out4[3] = st->aux;
+    return 0;
+}
+
+int slime_nvlink_ep_status_clear(void* h)
+{
+    Endpoint* ep = static_cast<Endpoint*>(h);
+    if (ep != nullptr && ep->status_host != nullptr) memset(ep->status_host, 0, sizeof(KernelStatus));
+    return 0;
+}
+
 // Few, large pieces are a job for the copy engines: no SM is occupied, nothing is staged, and for one contiguous
 // region a DMA copy is a few percent faster than any kernel (it has no tail and no launch-shaped ramp). The kernels
 // take over where the copy engines lose: many pieces, each of which would cost one host call and one DMA set-up.
@@ -411,7 +504,8 @@ static int resolve_segment(Endpoint* ep, int index, long long lh, long long rh, 
         return fail("nvlink endpoint: assignment %d names unknown remote region %lld", index, rh);
     const Region& L = ep->local[lh];
     const Region& R = ep->remote[rh];
-    if (loff + len > L.length || roff + len > R.length)
+    // written so that no sum can wrap: an offset near 2^64 (a negative number on the caller's side) is refused
+    if (loff > L.length || len > L.length - loff || roff > R.length || len > R.length - roff)
         return fail("nvlink endpoint: assignment %d exceeds a region (local %llu+%llu of %llu, remote %llu+%llu of %llu)", index,
                     loff, len, L.length, roff, len, R.length);
     *dst = is_write ? R.addr + roff : L.addr + loff;
@@ -472,7 +566,9 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
             return 0;
         }
     }
+    std::lock_guard<std::mutex> submit(ep->submit_mu);
     if (ensure_staging(ep)) return -1;
+    const unsigned long long unit = unit_bytes_setting();
     int done = 0;
     do {
         const int          batch = std::min(n - done, kStagingEntries);
@@ -506,11 +602,13 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
         }
         for (int i = 0; i < batch; ++i) {
             seg_out[i].first_unit = units;
-            units += (seg_out[i].len + kUnitBytes - 1) / kUnitBytes;
+            units += (seg_out[i].len + unit - 1) / unit;
         }
         CopyArgs a{};
-        a.n_seg   = batch;
-        a.n_units = units;
+        a.n_seg      = batch;
+        a.n_units    = units;
+        a.unit_bytes = unit;
+        a.status     = ep->status_dev;
         const bool last_batch = done + batch >= n;
         if (last_batch && signal != nullptr) {
             a.signal        = static_cast<unsigned long long*>(signal);
@@ -527,10 +625,11 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
         if (all_aligned && !bulk_off && units > 0) {
             // three 64 KiB rings fit in one SM's shared memory
             constexpr int kBulkSmem = kBulkBufs * kBulkChunk;
-            static bool   configured = false;
-            if (!configured) {
+            static bool   configured[64] = {false};  // the attribute belongs to the device's copy of the function
+            const int     dev_slot = ep->device >= 0 && ep->device < 64 ? ep->device : 0;
+            if (!configured[dev_slot]) {
                 SLIME_CUDA_OK(cudaFuncSetAttribute(p2p_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmem));
-                configured = true;
+                configured[dev_slot] = true;
             }
             long long grid = static_cast<long long>(std::min<unsigned long long>(units, static_cast<unsigned long long>(sm_count()) * 3));
             if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;

@@ -16,12 +16,17 @@ __global__ void wait_flag_kernel(const unsigned long long* flag, unsigned long l
     wait_flag_ge(flag, target, st, 100, 0, limit_ns ? limit_ns : kDefaultWaitNs);
 }
 
-__global__ void wait_mask_kernel(const unsigned long long* word, unsigned long long mask, unsigned long long limit_ns)
+__global__ void wait_mask_kernel(const unsigned long long* word, unsigned long long mask, unsigned long long limit_ns,
+                                 unsigned long long* timed_out)
 {
     const unsigned long long lim = limit_ns ? limit_ns : kDefaultWaitNs;
     const unsigned long long t0  = globaltimer_ns();
     while ((ld_acquire_sys(word) & mask) != mask) {
-        if (globaltimer_ns() - t0 > lim) return;  // bounded: the host sees the operation's own status
+        if (globaltimer_ns() - t0 > lim) {
+            // bounded: the stream goes on, and the word tells the host that it did so without the data
+            if (timed_out != nullptr) st_release_sys(timed_out, 1ull);
+            return;
+        }
         __nanosleep(100);
     }
 }
@@ -111,9 +116,11 @@ int slime_hook_record_value(void* stream, void* dev_word, unsigned long long val
     return 0;
 }
 
-int slime_hook_wait_mask(void* stream, void* dev_word, unsigned long long mask, unsigned long long limit_ns)
+int slime_hook_wait_mask(void* stream, void* dev_word, unsigned long long mask, unsigned long long limit_ns,
+                         void* dev_timeout_word)
 {
-    wait_mask_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned long long*>(dev_word), mask, limit_ns);
+    wait_mask_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned long long*>(dev_word), mask, limit_ns,
+                                                                    static_cast<unsigned long long*>(dev_timeout_word));
     SLIME_CUDA_OK(cudaGetLastError());
     return 0;
 }

@@ -38,6 +38,8 @@ _lib.declare("slime_nvlink_ep_local_info", [_v, _i, _ubp, _ullp, _ullp, _ullp])
 _lib.declare("slime_nvlink_ep_register_remote", [_v, _cp, _ubp, _ull, _ull, _ull, _i])
 _lib.declare("slime_nvlink_ep_handle", [_v, _cp, _i])
 _lib.declare("slime_nvlink_ep_transfer", [_v, _v, _i, _i, _v, _ull, _i, _i, _v])
+_lib.declare("slime_nvlink_ep_status", [_v, ctypes.POINTER(ctypes.c_uint)])
+_lib.declare("slime_nvlink_ep_status_clear", [_v])
 _ll = ctypes.c_longlong
 _lib.declare("slime_nvlink_ep_copy1", [_v, _ll, _ll, _ull, _ull, _ull, _i, _v, _ull, _v])
 
@@ -51,9 +53,10 @@ class NVLinkFuture:
     mapped host memory, so no stream synchronise is needed), or 402 after ``timeout``.
     """
 
-    def __init__(self, flags_host: int | None, index: int, target: int, stream, on_done=None):
+    def __init__(self, flags_host: int | None, index: int, target: int, stream, on_done=None, status=None):
         self._host, self._index, self._target, self._stream = flags_host, index, target, stream
         self._on_done = on_done  # called once, the first time completion is observed (accounting)
+        self._status = status  # callable -> kernel status code of the endpoint (non-zero: the word will never come)
 
     def done(self) -> bool:
         if self._host is None:
@@ -69,9 +72,13 @@ class NVLinkFuture:
         if self._host is None:
             return 0
         t0 = time.monotonic()
+        polls = 0
         while not self.done():
             if timeout is not None and time.monotonic() - t0 > timeout:
                 return 402
+            polls += 1
+            if self._status is not None and polls % 1024 == 0 and self._status() != 0:
+                return 402  # a copy of this endpoint gave up: its completion word was withheld
             time.sleep(0)
         return 0
 
@@ -167,6 +174,9 @@ class NVLinkEndpoint:
                     raise KeyError(f"memory region not found: local={ln!r} remote={rn!r}")
                 rows.append((lh, rh, roff, loff, length))
             assign = rows
+        for row in assign:
+            if min(int(v) for v in row) < 0:
+                raise ValueError(f"negative handle, offset or length in assignment {tuple(row)!r}")
         arr = np.ascontiguousarray(np.asarray(assign, dtype=np.uint64).reshape(-1, 5))
         return arr
 
@@ -198,6 +208,8 @@ class NVLinkEndpoint:
         if type(assign) is list and len(assign) == 1 and type(assign[0][0]) is int and max_blocks == 0:
             # one contiguous piece by handle: scalar arguments, no table, a copy-engine copy
             lh, rh, roff, loff, length = assign[0]
+            if roff < 0 or loff < 0 or length < 0:  # ctypes would turn these into offsets near 2^64
+                raise ValueError(f"negative offset or length in assignment {tuple(assign[0])!r}")
             flag_dev, seq, fut = None, 0, None
             if want_future:
                 i = self._next_flag
@@ -217,9 +229,20 @@ class NVLinkEndpoint:
             flag_dev = self._flags_dev + 8 * i
             _lib.call("slime_nvlink_ep_transfer", self._h, arr.ctypes.data, arr.shape[0], int(is_write), flag_dev,
                       self._flag_seq[i], 0, max_blocks, sp)
-            return NVLinkFuture(self._flags_host, i, self._flag_seq[i], sp)
+            return NVLinkFuture(self._flags_host, i, self._flag_seq[i], sp, status=self._status_code)
         _lib.call("slime_nvlink_ep_transfer", self._h, arr.ctypes.data, arr.shape[0], int(is_write), None, 0, 0, max_blocks, sp)
         return NVLinkFuture(None, 0, 0, sp)
+
+    def kernel_status(self) -> dict:
+        """Status page of this endpoint's kernels: ``code`` 0 = ok, 402 = a bounded wait for a copy ran out."""
+        out = (ctypes.c_uint * 4)()
+        _lib.call("slime_nvlink_ep_status", self._h, out)
+        return {"code": out[0], "where": out[1], "block": out[2], "aux": out[3]}
+
+    def _status_code(self) -> int:
+        out = (ctypes.c_uint * 4)()
+        _lib.load().slime_nvlink_ep_status(self._h, out)
+        return out[0]
 
     def read(self, assign, stream=None, want_future: bool = True):
         """remote -> local for every tuple; one kernel launch for the whole batch."""

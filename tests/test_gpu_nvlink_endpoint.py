@@ -80,6 +80,37 @@ def test_out_of_range_piece_is_refused(pair):
     assert torch.equal(mine, before)
 
 
+def test_wrapped_and_negative_offsets_are_refused(pair):
+    """An offset near 2^64 (what a negative number becomes in an unsigned argument) must not pass the range check
+    by wrapping `offset + length`; the refusal happens on the host, before anything is launched."""
+    import ctypes
+
+    import numpy as np
+
+    from dlslime_b200 import _lib
+    from dlslime_b200._lib import SlimeCudaError
+
+    ep, mine, theirs = pair
+    lh, rh = ep.get_mr_handle("buf"), ep.get_remote_mr_handle("buf")
+    before_m, before_t = mine.clone(), theirs.clone()
+    for bad in [(lh, rh, -16, 0, 32), (lh, rh, 0, -16, 32), (lh, rh, 0, 0, -1)]:
+        with pytest.raises(ValueError):
+            ep.read([bad])  # scalar route
+        with pytest.raises(ValueError):
+            ep.write([bad, (lh, rh, 0, 0, 16)])  # table route
+    huge = (1 << 64) - 16
+    # straight through the C entry points, as a caller without the Python checks would
+    lib = _lib.load()
+    assert lib.slime_nvlink_ep_copy1(ep._h, lh, rh, ctypes.c_ulonglong(huge), 0, 32, 0, None, 0, None) < 0
+    assert lib.slime_nvlink_ep_copy1(ep._h, lh, rh, 0, ctypes.c_ulonglong(huge), 32, 1, None, 0, None) < 0
+    for row in [(lh, rh, huge, 0, 32), (lh, rh, 0, huge, 32), (lh, rh, 16, 16, huge)]:
+        arr = np.asarray([row, (lh, rh, 0, 0, 16)] * 8, dtype=np.uint64)  # 16 pieces: the kernel route
+        with pytest.raises(SlimeCudaError):
+            ep.read(arr)
+    torch.cuda.synchronize()
+    assert torch.equal(mine, before_m) and torch.equal(theirs, before_t)
+
+
 def test_write_with_imm_after_single_piece(pair):
     """The immediate travels behind a copy-engine write in stream order (self-connected pair shares one mailbox owner)."""
     ep, mine, theirs = pair

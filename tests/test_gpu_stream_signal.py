@@ -62,3 +62,38 @@ def test_transfer_is_ordered_after_the_stream_and_before_its_waiters():
     env = dict(os.environ, PYTHONPATH=REPO, SLIME_BYPASS_DEVICE_SIGNAL="0")
     r = subprocess.run([sys.executable, "-c", body], env=env, capture_output=True, text=True, timeout=200)
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+def test_stream_wait_that_runs_out_is_reported():
+    """A word that nobody sets and a 20 ms limit: the one-thread wait kernel gives up, the stream continues, and the
+    signal says so (a future built on it then answers 402 instead of success)."""
+    body = textwrap.dedent("""
+        import torch
+        from dlslime_b200 import _lib, _slime_c as C
+        _lib.load()
+        s = torch.cuda.Stream()
+        sig = C.create_signal(False)
+        sig.bind_stream(s.cuda_stream)
+        sig.set_stream_wait_limit_ms(20.0)
+        assert not sig.stream_wait_timed_out()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(s):
+            t0.record(s)
+            sig.wait_comm_done_on_stream(0b1)      # bit 0 is never set
+            t1.record(s)
+        s.synchronize()
+        ms = t0.elapsed_time(t1)
+        assert 15.0 < ms < 500.0, ms
+        assert sig.stream_wait_timed_out()
+        # a satisfied wait leaves the word alone
+        sig.reset_all()
+        sig.set_comm_done(0)
+        with torch.cuda.stream(s):
+            sig.wait_comm_done_on_stream(0b1)
+        s.synchronize()
+        assert not sig.stream_wait_timed_out()
+        print("ok")
+    """)
+    env = dict(os.environ, PYTHONPATH=REPO, SLIME_BYPASS_DEVICE_SIGNAL="0")
+    r = subprocess.run([sys.executable, "-c", body], env=env, capture_output=True, text=True, timeout=200)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]

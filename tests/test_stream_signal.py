@@ -14,7 +14,7 @@ def test_transfer_waits_for_the_stream_and_stream_can_wait_for_the_transfer():
         from ctypes import CFUNCTYPE, POINTER, c_int, c_ulonglong, c_void_p
         from dlslime_b200 import _slime_c as C
 
-        keep, stream_queue = [], []
+        keep, stream_queue, waits = [], [], []
 
         @CFUNCTYPE(c_int, c_ulonglong, POINTER(c_void_p), POINTER(c_void_p))
         def alloc(n, host, dev):
@@ -32,9 +32,10 @@ def test_transfer_waits_for_the_stream_and_stream_can_wait_for_the_transfer():
             stream_queue.append(("record", stream, word, value))
             return 0
 
-        @CFUNCTYPE(c_int, c_void_p, c_void_p, c_ulonglong, c_ulonglong)
-        def wait(stream, word, mask, limit):
+        @CFUNCTYPE(c_int, c_void_p, c_void_p, c_ulonglong, c_ulonglong, c_void_p)
+        def wait(stream, word, mask, limit, timeout_word):
             stream_queue.append(("wait", stream, word, mask))
+            waits.append((limit, timeout_word))
             return 0
 
         addr = lambda f: ctypes.cast(f, c_void_p).value
@@ -75,6 +76,19 @@ def test_transfer_waits_for_the_stream_and_stream_can_wait_for_the_transfer():
         f.wait_on_stream()
         kind, stream, word, mask = stream_queue.pop()
         assert (kind, stream) == ("wait", 5) and ctypes.c_ulonglong.from_address(word).value & mask == mask
+        assert waits[-1][0] == 1_000_000_000 and not f.stream_wait_timed_out()
+
+        # a stream-ordered wait that runs into its limit: the "device" sets the timeout word, and the future must say
+        # 402 although the transfer itself succeeded (the stream's consumers ran without the data)
+        f2 = a.write([(a.get_mr_handle("src"), a.get_remote_mr_handle("dst"), 0, 0, n)], stream=5)
+        kind, stream, word, value = stream_queue.pop()
+        ctypes.c_ulonglong.from_address(word).value = value
+        assert f2.wait(10) == 0
+        f2.wait_on_stream(limit_ms=20)
+        limit, timeout_word = waits[-1]
+        assert limit == 20_000_000
+        ctypes.c_ulonglong.from_address(timeout_word).value = 1          # what the bounded kernel does when it gives up
+        assert f2.stream_wait_timed_out() and f2.wait(10) == 402
         a.shutdown(); b.shutdown()
         print("ok")
     """)

@@ -140,3 +140,35 @@ def test_injected_faults(pair):
     a.inject_fault("reset", 1)
     with pytest.raises(RuntimeError):
         a.write([(0, 0, 0, 0, 64)]).wait(5)
+
+
+def test_oversized_message_closes_the_connection_instead_of_the_process():
+    """The length of a two-sided message comes from the peer. Above SLIME_TCP_MAX_MESSAGE_BYTES the receiving side
+    closes the connection (the sender's operation fails) and nothing is allocated for it; the process lives on."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    body = textwrap.dedent("""
+        import ctypes
+        from dlslime_b200 import _slime_c as c
+        n = 1 << 16
+        ba, bb = ctypes.create_string_buffer(n), ctypes.create_string_buffer(n)
+        a, b = c.TcpEndpoint(), c.TcpEndpoint()
+        a.register_memory_region("buf", ctypes.addressof(ba), 0, n)
+        b.register_memory_region("buf", ctypes.addressof(bb), 0, n)
+        a.connect(b.endpoint_info()); b.connect(a.endpoint_info())
+        ok = a.send((ctypes.addressof(ba), 0, 512))
+        r = b.recv((ctypes.addressof(bb), 0, 1024))
+        assert ok.wait(5) == 0 and r.wait(5) == 0
+        big = a.send((ctypes.addressof(ba), 0, 4096))      # above the 1 KiB limit set below
+        st = big.wait(5)
+        assert st in (402, 403), st
+        a.shutdown(); b.shutdown()
+        print("alive")
+    """)
+    env = dict(os.environ, PYTHONPATH=repo, SLIME_TCP_MAX_MESSAGE_BYTES="1024")
+    r = subprocess.run([sys.executable, "-c", body], env=env, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "alive" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
