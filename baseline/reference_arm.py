@@ -3,12 +3,13 @@
 The reference (installed under ``baseline/_ref``) ships no kernels and no dispatch / combine op. What
 a user of it has is ``NVLinkEndpoint.read`` (one ``cudaMemcpyAsync`` per assignment, read only), so the
 step is composed the way such a user would: torch for routing, fp8 block quantisation, sorting by
-expert, the per-expert SwiGLU FFN (cuBLAS) and the weighted sum; NCCL for the count exchange and the
-barriers; the reference endpoint for every token row that crosses GPUs, pulled by the receiving rank.
-Nothing from the ``dlslime_b200`` package is imported here.
+expert, the grouped SwiGLU FFN and the weighted sum (``baseline/torch_moe.py``); NCCL for the count
+exchange and the barriers; the reference endpoint for every token row that crosses GPUs, pulled by the
+receiving rank. Nothing from the ``dlslime_b200`` package is imported here or by anything this imports.
 
-With one GPU nothing crosses ranks and the reference endpoint has nothing to do (it cannot map memory
-of its own process); the local segments are then plain device copies, which the result records.
+With one GPU nothing crosses ranks: the reference package is loaded and its endpoint registers the arena,
+but it has nothing to read (it cannot map memory of its own process), so the local segments are plain
+device copies; the result says so (``reference_package_used``).
 """
 
 from __future__ import annotations
@@ -16,8 +17,7 @@ from __future__ import annotations
 import os
 import sys
 
-E, TOPK, HIDDEN, INTER = 256, 8, 7168, 2048
-FP8_MAX = 448.0
+from .torch_moe import E, HIDDEN, TOPK, ExpertFFN, combine, dequant_1x128, init_weights, quant_1x128, route
 
 
 def _load_reference():
@@ -27,19 +27,6 @@ def _load_reference():
     from dlslime import _slime_c  # the reference's own extension module
 
     return _slime_c
-
-
-def _init_weights(experts, device, seed=0):
-    import torch
-
-    w13 = torch.empty((len(experts), 2 * INTER, HIDDEN), dtype=torch.bfloat16, device=device)
-    w2 = torch.empty((len(experts), HIDDEN, INTER), dtype=torch.bfloat16, device=device)
-    gen = torch.Generator(device=device)
-    for i, e in enumerate(experts):
-        gen.manual_seed(seed * 100003 + e)
-        w13[i].copy_(torch.randn((2 * INTER, HIDDEN), generator=gen, device=device).mul_(0.02))
-        w2[i].copy_(torch.randn((HIDDEN, INTER), generator=gen, device=device).mul_(0.02))
-    return w13, w2
 
 
 class ReferenceMoE:
@@ -71,17 +58,18 @@ class ReferenceMoE:
         for name, shape, dt in spec:
             nbytes = shape[0] * shape[1] * torch.empty((), dtype=dt).element_size()
             setattr(self, name, self.arena[self.off[name]:self.off[name] + nbytes].view(dt).view(shape))
-        self.w13, self.w2 = _init_weights(range(rank * self.epr, (rank + 1) * self.epr), dev)
+        w13, w2 = init_weights(range(rank * self.epr, (rank + 1) * self.epr), dev)
+        self.ffn = ExpertFFN(w13, w2)
         self.counts_all = torch.empty((world, E), dtype=torch.int64, device=dev)
         self.copies = 0
         self.peers = {}
+        ref = _load_reference()
+        exporter = ref.NVLinkEndpoint()
+        exporter.register_memory_region(self.arena.data_ptr(), 0, total, "arena")
+        self._exporter = exporter
         if world > 1:
-            ref = _load_reference()
-            exporter = ref.NVLinkEndpoint()
-            exporter.register_memory_region(self.arena.data_ptr(), 0, total, "arena")
             infos = [None] * world
             dist.all_gather_object(infos, exporter.endpoint_info())
-            self._exporter = exporter
             # one endpoint per peer (the reference's model is one endpoint per connection); each peer's
             # handle is opened exactly once in this process
             for p in range(world):
@@ -109,16 +97,13 @@ class ReferenceMoE:
     def forward(self, x, logits, out):
         torch, dist = self.torch, self.dist
         T, W, epr = x.shape[0], self.world, self.epr
-        probs = torch.softmax(logits.float(), dim=-1)
-        w, idx = torch.topk(probs, TOPK, dim=-1)
-        xf = x.float().view(T, HIDDEN // 128, 128)
-        scale = xf.abs().amax(-1).clamp_min(1e-4) / FP8_MAX
-        q = (xf / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn).view(T, HIDDEN)
+        w, idx = route(logits)
+        q, scale = quant_1x128(x)
         flat = idx.reshape(-1)
         order = torch.argsort(flat, stable=True)
         tok = order // TOPK
-        self.send_q.copy_(q.view(torch.uint8)[tok])
-        self.send_s.copy_(scale[tok])
+        torch.index_select(q, 0, tok, out=self.send_q)
+        torch.index_select(scale, 0, tok, out=self.send_s)
         counts = torch.bincount(flat, minlength=E)
         if W > 1:
             dist.all_gather_into_tensor(self.counts_all, counts)
@@ -131,87 +116,46 @@ class ReferenceMoE:
         exp_off = torch.cat([torch.zeros(1, dtype=torch.int64), per_expert.cumsum(0)])
         # dispatch: rows of expert j from source s land at exp_off[j] + sum_{s'<s} mine[s', j]
         src_prefix = torch.cat([torch.zeros(1, epr, dtype=torch.int64), mine.cumsum(0)], 0)
+        so, eo, sp, mn = send_off.tolist(), exp_off.tolist(), src_prefix.tolist(), mine.tolist()
         for s in range(W):
-            pairs = [(int(send_off[s, self.rank * epr + j]), int(exp_off[j] + src_prefix[s, j]), int(mine[s, j])) for j in range(epr)]
+            pairs = [(so[s][self.rank * epr + j], eo[j] + sp[s][j], mn[s][j]) for j in range(epr)]
             self._pull(s, "recv_q", self.recv_q, "send_q", self.send_q, pairs, HIDDEN)
             self._pull(s, "recv_s", self.recv_s, "send_s", self.send_s, pairs, HIDDEN // 128 * 4)
-        R = int(exp_off[-1])
-        xd = (self.recv_q[:R].view(torch.float8_e4m3fn).float().view(R, HIDDEN // 128, 128) * self.recv_s[:R].unsqueeze(-1)).view(R, HIDDEN).to(torch.bfloat16)
-        for j in range(epr):
-            a, b = int(exp_off[j]), int(exp_off[j + 1])
-            if b > a:
-                gu = xd[a:b] @ self.w13[j].t()
-                h = torch.nn.functional.silu(gu[:, :INTER]) * gu[:, INTER:]
-                torch.matmul(h, self.w2[j].t(), out=self.y[a:b])
+        R = eo[-1]
+        xd = dequant_1x128(self.recv_q[:R], self.recv_s[:R])
+        offs_host = exp_off[1:].to(torch.int32)
+        self.y[:R].copy_(self.ffn(xd, offs_host.to(x.device, non_blocking=True), offs_host))
         if W > 1:
             dist.barrier()  # every rank's expert outputs are complete before anyone pulls them back
         # combine: my sorted rows of expert e live on rank e // epr at (its exp_off[e % epr] + its src_prefix[me, e % epr])
-        my_off = send_off[self.rank]
+        my_off = so[self.rank]
         for p in range(W):
             cols = c[:, p * epr:(p + 1) * epr]
-            p_exp_off = torch.cat([torch.zeros(1, dtype=torch.int64), cols.sum(0).cumsum(0)])
-            p_prefix = torch.cat([torch.zeros(1, epr, dtype=torch.int64), cols.cumsum(0)], 0)
-            pairs = [(int(p_exp_off[j] + p_prefix[self.rank, j]), int(my_off[p * epr + j]), int(cols[self.rank, j])) for j in range(epr)]
+            p_exp_off = torch.cat([torch.zeros(1, dtype=torch.int64), cols.sum(0).cumsum(0)]).tolist()
+            p_prefix = torch.cat([torch.zeros(1, epr, dtype=torch.int64), cols.cumsum(0)], 0).tolist()
+            colsl = cols.tolist()
+            pairs = [(p_exp_off[j] + p_prefix[self.rank][j], my_off[p * epr + j], colsl[self.rank][j]) for j in range(epr)]
             self._pull(p, "ret", self.ret, "y", self.y, pairs, HIDDEN * 2)
-        unsorted = torch.empty_like(self.ret)
-        unsorted[order] = self.ret
-        out.copy_((unsorted.view(T, TOPK, HIDDEN).float() * w.unsqueeze(-1)).sum(1))
+        combine(self.ret, order, w, out)
         if W > 1:
             dist.barrier()  # nobody may refill its send / result buffers while a peer still reads them
         return out
 
 
-def run(args, rank, world, local, T, make_inputs, sync_all, max_over_ranks, ClockSampler):
-    import torch
-
+def run(args, rank, world, local, T, Harness):
     try:
         layer = ReferenceMoE(rank, world, T)
     except Exception as e:  # the reference failed to import or to map peer memory
         return {"unavailable": f"reference endpoint could not be set up: {type(e).__name__}: {e}"[:300]}
-    n_in = min(4, max(1, args.steps))
-    host_x, host_lg = make_inputs(T, rank, n_in)
-    dev_x = [h.cuda() for h in host_x]
-    dev_lg = [h.cuda() for h in host_lg]
-    out = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device="cuda")
-    host_out = torch.empty((T, HIDDEN), dtype=torch.bfloat16).pin_memory()
-    x_stage, lg_stage = torch.empty_like(dev_x[0]), torch.empty_like(dev_lg[0])
-
-    def step_device(i):
-        layer.forward(dev_x[i % n_in], dev_lg[i % n_in], out)
-
-    def step_e2e(i):
-        x_stage.copy_(host_x[i % n_in], non_blocking=True)
-        lg_stage.copy_(host_lg[i % n_in], non_blocking=True)
-        layer.forward(x_stage, lg_stage, out)
-        host_out.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    def timed(fn):
-        sampler = ClockSampler(local)
-        if rank == 0:
-            sampler.start()
-        for i in range(args.warmup):
-            fn(i)
-        sync_all(world)
-        sampler.mark_begin()
-        layer.copies = 0
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(args.steps):
-            fn(i)
-        e1.record()
-        sync_all(world)
-        sampler.mark_end()
-        clocks = sampler.stop() if rank == 0 else None
-        return max_over_ranks(e0.elapsed_time(e1) / args.steps, world), clocks
-
-    ms_dev, clocks = timed(step_device)
-    copies = layer.copies
-    ms_e2e, _ = timed(step_e2e)
-    remote = (world - 1) / world
-    nv_bytes = T * TOPK * (HIDDEN + HIDDEN // 128 * 4) * remote + T * TOPK * HIDDEN * 2 * remote
-    return {"ms_dev": ms_dev, "ms_e2e": ms_e2e, "clocks": clocks, "T": T, "h2d": host_x[0].numel() * 2 + host_lg[0].numel() * 4,
-            "d2h": host_out.numel() * 2, "launches": 0, "weights_gb": (layer.w13.numel() + layer.w2.numel()) * 2 / 1e9,
-            "nvlink_bytes_per_rank": nv_bytes,
-            "breakdown_us": {"reference_endpoint_copies_per_run": copies,
-                             "transport": "reference NVLinkEndpoint.read" if world > 1 else "local device copies (one GPU: nothing crosses ranks)"}}
+    h = Harness(layer.forward, T, rank, world, local, args, pipelined=args.mode == "normal")
+    res = h.run_all()
+    layer.copies = 0
+    layer.forward(h.dev_x[0], h.dev_lg[0], h.out)
+    res.update({
+        "launches": 0, "weights_gb": (layer.ffn.w13.numel() + layer.ffn.w2.numel()) * 2 / 1e9,
+        "reference_package_used": world > 1,
+        "check": h.check(layer.forward),
+        "notes": {"reference_endpoint_copies_per_step": layer.copies, "expert_ffn": layer.ffn.mode,
+                  "transport": "reference NVLinkEndpoint.read" if world > 1 else
+                  "local device copies (one GPU: nothing crosses ranks; the reference endpoint is loaded and holds the arena)"}})
+    return res

@@ -29,15 +29,34 @@ uint32_t random_psn()
 
 std::shared_ptr<RdmaEndpoint> RdmaEndpoint::create(const std::string& device, int port, const std::string& link_type, int num_qp)
 {
-    auto ctx = ContextManager::get().acquire(device, port, link_type);
+    return create(ContextManager::get().acquire(device, port, link_type), num_qp, nullptr);
+}
+
+std::shared_ptr<RdmaEndpoint> RdmaEndpoint::create(std::shared_ptr<RdmaContext> ctx, int num_qp, std::shared_ptr<RdmaWorker> worker)
+{
+    if (!ctx) throw std::runtime_error("RDMA endpoint needs a context");
     if (num_qp <= 0) num_qp = engine_env().qp_num;
     if (num_qp < 1 || num_qp > 32) throw std::runtime_error("num_qp must be in [1, 32]");
     std::shared_ptr<RdmaEndpoint> ep(new RdmaEndpoint(ctx, num_qp));
     for (auto& ch : ep->ch_)
         for (auto& l : ch.lanes) ctx->add_sink(l.qpn, ep);
-    ep->worker_ = RdmaWorker::for_node(ctx->numa_node());
+    ep->worker_ = worker ? std::move(worker) : RdmaWorker::for_node(ctx->numa_node());
     ep->worker_->add(ep);
     return ep;
+}
+
+void RdmaEndpoint::set_worker(std::shared_ptr<RdmaWorker> worker)
+{
+    if (shut_.load()) return;
+    if (!worker) worker = RdmaWorker::for_node(ctx_->numa_node());
+    if (worker == worker_) return;
+    // joined to the new worker before leaving the old one: process() serialises itself, so a moment with two
+    // workers is harmless, a moment with none would stall queued work
+    auto old = worker_;
+    worker->add(shared_from_this());
+    worker_ = worker;
+    if (old) old->remove(this);
+    worker_->wake();
 }
 
 RdmaEndpoint::RdmaEndpoint(std::shared_ptr<RdmaContext> ctx, int num_qp):

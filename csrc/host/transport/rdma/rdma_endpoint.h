@@ -51,6 +51,10 @@ public:
     // device "" = first device; link_type "RoCE" | "IB" | "". num_qp <= 0 takes SLIME_QP_NUM.
     static std::shared_ptr<RdmaEndpoint> create(const std::string& device = "", int port = 1, const std::string& link_type = "",
                                                 int num_qp = 0);
+    // On an existing context, progressed by `worker` (nullptr = the shared worker of the context's NUMA node).
+    static std::shared_ptr<RdmaEndpoint> create(std::shared_ptr<RdmaContext> ctx, int num_qp, std::shared_ptr<RdmaWorker> worker);
+    // Hands the endpoint to another progress worker (nullptr = back to the shared worker of its NUMA node).
+    void set_worker(std::shared_ptr<RdmaWorker> worker);
     ~RdmaEndpoint() override;
 
     std::string kind() const override { return "rdma"; }

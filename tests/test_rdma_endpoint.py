@@ -438,3 +438,50 @@ def test_random_batches_match_a_model_and_bad_batches_fail_cleanly():
         print("ok", bad_seen)
     """, timeout=240)
     assert "ok" in out
+
+
+def test_reference_style_pool_worker_and_constructor_forms():
+    """Code written against the reference's classes runs unchanged: ``RDMAMemoryPool(context)``,
+    ``RDMAWorker(socket_id, id)`` with start / add_endpoint / stop, and the three ``RDMAEndpoint`` constructors
+    (pool, context, device name), each with an optional worker (dlslime/csrc/python/bind.cpp:163-204,272 in the
+    reference)."""
+    out = run_child("""
+        ctx = C.RDMAContext.acquire("rdma_lo0", 1, "RoCE")
+        pool = C.RDMAMemoryPool(ctx)
+        worker = C.RDMAWorker(0, 0)
+        by_name = C.RDMAWorker("rdma_lo0", 1)
+        assert not worker.running()
+        worker.start()
+        assert worker.running()
+        n = 1 << 20
+        src, dst = buf(n, 0x5a), buf(n, 0)
+        hs = pool.register_memory_region(ctypes.addressof(src), n, "src")
+        hd = pool.register_memory_region(ctypes.addressof(dst), n, "dst")
+        assert pool.get_handle("src") == hs and set(pool.mr_info()) >= {"src", "dst"}
+        a = C.RDMAEndpoint(pool, 2, worker)                     # form 1: pool, num_qp, worker
+        b = C.RDMAEndpoint(ctx, num_qp=2)                       # form 2: context (shared per-node worker)
+        c = C.RDMAEndpoint("rdma_lo0", 1, "RoCE", 2, by_name)   # form 3: device name ... worker (not started yet)
+        assert a.get_pool().get_handle("dst") == hd             # one registry per device: every view sees the regions
+        link(a, b)
+        for name, info in b.endpoint_info()["mr_info"].items():
+            a.register_remote_memory_region(name, info)
+        rh = a.get_remote_mr_handle("dst")
+        assert a.write([(hs, rh, 0, 0, n)]).wait(10) == 0
+        assert bytes(dst[:16]) == bytes([0x5a]) * 16 and dst[n - 1] == 0x5a
+        loops = worker.stats()["loops"]
+        assert loops > 0
+        # stopping the caller's worker hands its endpoints back to the shared one: traffic goes on
+        worker.stop()
+        assert not worker.running()
+        ctypes.memset(src, 0x33, n)
+        assert a.write([(hs, rh, 4096, 4096, 8192)]).wait(10) == 0
+        assert dst[4096] == 0x33 and dst[4095] == 0x5a
+        # a worker that is started after its endpoint was added takes the endpoint over
+        by_name.start(); assert by_name.running()
+        by_name.stop()
+        assert pool.unregister_memory_region("src") == 0
+        for ep in (a, b, c):
+            ep.shutdown()
+        print("ok")
+    """)
+    assert "ok" in out
