@@ -100,7 +100,36 @@ void bind_rdma(py::module_& m)
         .def("mr_info", [](RdmaPoolView& v) { return v.pool->mr_info(); })
         .def("context", [](RdmaPoolView& v) { return v.ctx; });
 
-    py::class_<RdmaWorkerHandle, std::shared_ptr<RdmaWorkerHandle>>(m, "RDMAWorker")
+    // declared before the endpoint (whose constructors take one), filled in after it (add_endpoint takes an endpoint)
+    py::class_<RdmaWorkerHandle, std::shared_ptr<RdmaWorkerHandle>> worker_cls(m, "RDMAWorker");
+
+    // The three constructor forms of the reference (bind.cpp:191-204 in the reference): from a pool, from a context,
+    // from a device name. `worker` = an RDMAWorker of the caller, or None for the shared per-node worker.
+    py::class_<RdmaEndpoint, Endpoint, std::shared_ptr<RdmaEndpoint>>(m, "RDMAEndpoint")
+        .def(py::init([](std::shared_ptr<RdmaPoolView> pool, int num_qp, std::shared_ptr<RdmaWorkerHandle> worker) {
+                 if (!pool) throw std::runtime_error("RDMAEndpoint: pool is None");
+                 return make_endpoint(pool->ctx, num_qp, worker);
+             }),
+             py::arg("pool"), py::arg("num_qp") = 1, py::arg("worker") = nullptr)
+        .def(py::init([](std::shared_ptr<RdmaContext> ctx, int num_qp, std::shared_ptr<RdmaWorkerHandle> worker) {
+                 return make_endpoint(std::move(ctx), num_qp, worker);
+             }),
+             py::arg("context"), py::arg("num_qp") = 1, py::arg("worker") = nullptr)
+        .def(py::init([](const std::string& dev, int port, const std::string& link, int num_qp, std::shared_ptr<RdmaWorkerHandle> worker) {
+                 return make_endpoint(ContextManager::get().acquire(dev, port, link), num_qp, worker);
+             }),
+             py::arg("device_name") = "", py::arg("ib_port") = 1, py::arg("link_type") = "", py::arg("num_qp") = 0,
+             py::arg("worker") = nullptr)
+        .def("get_pool", [](RdmaEndpoint& ep) { return std::make_shared<RdmaPoolView>(ep.context()); })
+        .def("num_qp", &RdmaEndpoint::num_qp)
+        .def("context", &RdmaEndpoint::context)
+        .def("process", &RdmaEndpoint::process)
+        .def("cancel_all", &RdmaEndpoint::cancel_all, py::call_guard<py::gil_scoped_release>())
+        .def("posted_wrs", &RdmaEndpoint::posted_wrs)
+        .def("signaled_wrs", &RdmaEndpoint::signaled_wrs)
+        .def("credit_stalls", &RdmaEndpoint::credit_stalls);
+
+    worker_cls
         .def(py::init([](const std::string& dev_name, int id) {
                  auto w = std::make_shared<RdmaWorkerHandle>();
                  w->id  = id;
@@ -132,31 +161,6 @@ void bind_rdma(py::module_& m)
             return d;
         });
 
-    // The three constructor forms of the reference (bind.cpp:191-204 in the reference): from a pool, from a context,
-    // from a device name. `worker` = an RDMAWorker of the caller, or None for the shared per-node worker.
-    py::class_<RdmaEndpoint, Endpoint, std::shared_ptr<RdmaEndpoint>>(m, "RDMAEndpoint")
-        .def(py::init([](std::shared_ptr<RdmaPoolView> pool, int num_qp, std::shared_ptr<RdmaWorkerHandle> worker) {
-                 if (!pool) throw std::runtime_error("RDMAEndpoint: pool is None");
-                 return make_endpoint(pool->ctx, num_qp, worker);
-             }),
-             py::arg("pool"), py::arg("num_qp") = 1, py::arg("worker") = nullptr)
-        .def(py::init([](std::shared_ptr<RdmaContext> ctx, int num_qp, std::shared_ptr<RdmaWorkerHandle> worker) {
-                 return make_endpoint(std::move(ctx), num_qp, worker);
-             }),
-             py::arg("context"), py::arg("num_qp") = 1, py::arg("worker") = nullptr)
-        .def(py::init([](const std::string& dev, int port, const std::string& link, int num_qp, std::shared_ptr<RdmaWorkerHandle> worker) {
-                 return make_endpoint(ContextManager::get().acquire(dev, port, link), num_qp, worker);
-             }),
-             py::arg("device_name") = "", py::arg("ib_port") = 1, py::arg("link_type") = "", py::arg("num_qp") = 0,
-             py::arg("worker") = nullptr)
-        .def("get_pool", [](RdmaEndpoint& ep) { return std::make_shared<RdmaPoolView>(ep.context()); })
-        .def("num_qp", &RdmaEndpoint::num_qp)
-        .def("context", &RdmaEndpoint::context)
-        .def("process", &RdmaEndpoint::process)
-        .def("cancel_all", &RdmaEndpoint::cancel_all, py::call_guard<py::gil_scoped_release>())
-        .def("posted_wrs", &RdmaEndpoint::posted_wrs)
-        .def("signaled_wrs", &RdmaEndpoint::signaled_wrs)
-        .def("credit_stalls", &RdmaEndpoint::credit_stalls);
 
     // Which verbs provider new contexts would use: (name, "") or (None, reason).
     m.def("rdma_provider", []() -> py::tuple {

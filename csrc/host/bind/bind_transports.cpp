@@ -20,5 +20,12 @@ void bind_extra_transports(py::module_& m)
         .def("connect", [](AscendDirectEndpoint& e, const Json& info) { return e.connect(info); })
         .def("read", [](AscendDirectEndpoint& e, py::object, py::object) { e.read(); }, py::arg("assign"), py::arg("stream") = py::none());
     m.attr("_BUILD_ASCEND_DIRECT") = false;
+#ifndef SLIME_NO_RDMA
     bind_rdma(m);
+#else
+    // built with BUILD_RDMA=OFF: the probes answer, the classes are absent
+    m.attr("_BUILD_RDMA") = py::bool_(false);
+    m.def("rdma_devices", [] { return std::vector<std::string>{}; });
+    m.def("rdma_provider", []() -> py::tuple { return py::make_tuple(py::none(), std::string("built without the RDMA transport (BUILD_RDMA=OFF)")); });
+#endif
 }

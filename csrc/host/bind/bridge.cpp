@@ -8,12 +8,16 @@
 #include "bind_common.h"
 #include "slime_bridge.h"
 #include "transport/endpoint.h"
+#ifndef SLIME_NO_RDMA
 #include "transport/rdma/rdma_endpoint.h"
 #include "transport/rdma/verbs.h"
+#endif
 #include "transport/tcp_endpoint.h"
 
 namespace slime {
+#ifndef SLIME_NO_RDMA
 using namespace slime::rdma;
+#endif
 namespace {
 
 struct EpBox {
@@ -35,20 +39,24 @@ void* b_endpoint_create(const char* transport, const char* bind_host, int rank, 
         const std::string want = transport ? transport : "";
         std::vector<std::string> devices;
         std::string              provider_name;
+#ifndef SLIME_NO_RDMA
         if (want != "tcp") {
             if (VerbsProvider* p = default_provider(nullptr)) {
                 devices       = p->list_devices();
                 provider_name = p->provider_name();
             }
         }
+#endif
         if (want == "rdma" && devices.empty()) {
             set_err(err, err_len, "transport rdma was asked for but no verbs provider with a device exists");
             return nullptr;
         }
         auto box = std::make_unique<EpBox>();
+#ifndef SLIME_NO_RDMA
         if (!devices.empty() && (want == "rdma" || provider_name == "ibverbs"))
             box->ep = RdmaEndpoint::create(devices[static_cast<size_t>(rank < 0 ? 0 : rank) % devices.size()], 1, "", 0);
         else
+#endif
             box->ep = std::make_shared<TcpEndpoint>(bind_host && *bind_host ? bind_host : "127.0.0.1", 0, 1);
         box->kind = box->ep->kind();
         return box.release();

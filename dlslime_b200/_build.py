@@ -24,6 +24,7 @@ _here = os.path.dirname(os.path.abspath(__file__))
 sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != _here]
 
 import concurrent.futures as cf  # noqa: E402
+import re  # noqa: E402
 import shutil  # noqa: E402
 import subprocess  # noqa: E402
 import sysconfig  # noqa: E402
@@ -39,6 +40,30 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",
 ]
 CXX_FLAGS = ["-O2", "-g0", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread", "-Wall", "-Wno-unused-function"]
+
+
+def slime_option(name: str, default: bool) -> bool:
+    """A build switch with an environment override, like the reference's ``slime_option`` CMake macro
+    (cmake/utils.cmake:1-15 in the reference): ``ON|OFF|TRUE|FALSE`` (also ``1|0``, any case); anything else warns and
+    keeps the default.
+
+    ``BUILD_RDMA`` (ON)          the RDMA RC transport (context, endpoint, worker) and its bindings
+    ``BUILD_NVLINK`` (ON)        the sm_100a kernel library (NVLink endpoint and every device op); OFF = host runtime only
+    ``BUILD_PYTHON`` (ON)        the pybind11 module ``_slime_c``; OFF builds only the ``nanoctrl`` binary from the host tree
+    ``BUILD_TORCH_PLUGIN`` (ON)  the C++ ``torch.distributed`` backend
+    ``BUILD_ASCEND_DIRECT`` (OFF) accepted for parity; the transport is an interface stub either way
+    ``BUILD_BENCH`` / ``BUILD_TEST`` (OFF) also build the sanitizer stress programs of the host runtime
+    """
+    raw = os.environ.get(name)
+    if raw is None:
+        return default
+    v = raw.strip().upper()
+    if v in ("ON", "TRUE", "1"):
+        return True
+    if v in ("OFF", "FALSE", "0"):
+        return False
+    print(f"warning: invalid value for {name}: {raw!r}, using default {'ON' if default else 'OFF'}", file=sys.stderr)
+    return default
 
 
 def _nvcc() -> str:
@@ -125,39 +150,53 @@ def build_cuda(verbose: bool = False, ptxas_info: bool = False, workers: int | N
     return out
 
 
-def build_host(verbose: bool = False, workers: int | None = None) -> Path:
+def build_host(verbose: bool = False, workers: int | None = None, out_dir: Path | None = None) -> Path:
+    """The host runtime. ``out_dir`` (default: the package directory) receives ``_slime_c*.so`` and ``_C/nanoctrl``;
+    tests build switch combinations into a scratch directory with it."""
     import pybind11
 
     hdir = CSRC / "host"
     if not hdir.exists():
         return host_ext_path()
+    with_rdma = slime_option("BUILD_RDMA", True)
+    with_python = slime_option("BUILD_PYTHON", True)
+    variant = "host" + ("" if with_rdma else "_nordma")
+    feature_defs = [] if with_rdma else ["-DSLIME_NO_RDMA"]
     inc = [CSRC / "include", hdir, Path(pybind11.get_include()), Path(sysconfig.get_paths()["include"]), *_cuda_include()]
     dep = _newest_header_mtime([CSRC / "include", hdir])
-    (OBJ / "host").mkdir(parents=True, exist_ok=True)
+    (OBJ / variant).mkdir(parents=True, exist_ok=True)
     # The system compiler links libstdc++ dynamically. Some environments export CXX as a wrapper that
     # links it statically, and a second, exported copy of the C++ runtime inside an extension clashes
     # with the one torch loads; --exclude-libs keeps any static archive private in either case.
     cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else os.environ.get("CXX", "g++")
     jobs, objs, main_objs = [], [], []
     for src in sorted(hdir.rglob("*.cpp")):
-        if "stress" in src.relative_to(hdir).parts:
+        parts = src.relative_to(hdir).parts
+        if "stress" in parts:
             continue  # sanitizer stress programs are built by build_stress()
+        if not with_rdma and ("rdma" in parts or src.name == "bind_rdma.cpp"):
+            continue
         rel = "_".join(src.relative_to(hdir).with_suffix("").parts)
-        obj = OBJ / "host" / (rel + ".o")
-        cmd = [cxx, *CXX_FLAGS, *sum((["-I", i] for i in inc), []), "-c", src, "-o", obj]
+        obj = OBJ / variant / (rel + ".o")
+        cmd = [cxx, *CXX_FLAGS, *feature_defs, *sum((["-I", i] for i in inc), []), "-c", src, "-o", obj]
         jobs.append((src, obj, cmd, dep))
         if src.name == "nanoctrl_main.cpp":
             main_objs.append(obj)
         else:
             objs.append(obj)
     changed = _compile_many(jobs, verbose, workers or min(8, os.cpu_count() or 4))
-    out = host_ext_path()
-    if changed or not out.exists():
+    out = host_ext_path() if out_dir is None else Path(out_dir) / host_ext_path().name
+    stamp = OBJ / variant / ("linked_into_" + str(abs(hash(str(out)))))
+    relink = changed or not out.exists() or not stamp.exists()  # another variant may have been linked to this path last
+    if with_python and relink:
         _run([cxx, "-shared", "-o", out, *objs, "-Wl,--exclude-libs,ALL", "-pthread", "-ldl", "-lrt"], verbose)
+        for other in OBJ.glob("host*/linked_into_" + str(abs(hash(str(out))))):
+            other.unlink()
+        stamp.write_text(str(out))
     if main_objs:
-        exe = nanoctrl_bin_path()
-        if changed or not exe.exists():
-            (PKG / "_C").mkdir(parents=True, exist_ok=True)
+        exe = nanoctrl_bin_path() if out_dir is None else Path(out_dir) / "_C" / "nanoctrl"
+        if relink or not exe.exists():
+            exe.parent.mkdir(parents=True, exist_ok=True)
             core = [o for o in objs if not o.name.startswith("bind")]
             _run([cxx, "-o", exe, *main_objs, *core, "-pthread", "-ldl", "-lrt"], verbose)
     return out
@@ -233,9 +272,73 @@ def build_torch_plugin(verbose: bool = False) -> Path | None:
 
 
 def build_all(verbose: bool = False) -> None:
-    build_cuda(verbose=verbose)
+    """Everything the switches ask for (see ``slime_option``); with no switch set: kernels, host runtime, torch plugin."""
+    if slime_option("BUILD_NVLINK", True):
+        build_cuda(verbose=verbose)
     build_host(verbose=verbose)
-    build_torch_plugin(verbose=verbose)
+    if slime_option("BUILD_TORCH_PLUGIN", True) and slime_option("BUILD_PYTHON", True):
+        build_torch_plugin(verbose=verbose)
+    slime_option("BUILD_ASCEND_DIRECT", False)  # validated for parity; the Ascend transport is a stub in either setting
+    if slime_option("BUILD_BENCH", False) or slime_option("BUILD_TEST", False):
+        build_stress("thread", verbose=verbose)
+        build_stress("address,undefined", verbose=verbose)
+
+
+def generate_stubs(out_dir: Path | None = None) -> Path:
+    """Type stubs of the host module (the reference generates them with pybind11-stubgen, scripts/gen_stubs.sh in
+    the reference). Uses pybind11-stubgen when it is installed, else writes the signatures pybind11 puts into the
+    docstrings: classes with their methods, and module-level functions. Returns the written file."""
+    out_dir = Path(out_dir) if out_dir else PKG
+    try:
+        import pybind11_stubgen  # noqa: F401
+
+        _run([sys.executable, "-m", "pybind11_stubgen", "dlslime_b200._slime_c", "--output-dir", str(out_dir.parent),
+              "--ignore-unresolved-names", "json"], False)
+        return out_dir / "_slime_c.pyi"
+    except ImportError:
+        pass
+    import importlib
+    import inspect
+
+    sys.path.insert(0, str(ROOT))
+    mod = importlib.import_module("dlslime_b200._slime_c")
+
+    def sigs(obj, name, indent):
+        doc = (getattr(obj, "__doc__", None) or "").strip().splitlines()
+        lines = [ln.strip() for ln in doc if ln.strip().startswith(name + "(") or (ln.strip()[:3].rstrip(".").isdigit() and name + "(" in ln)]
+        lines = [ln[ln.index(name + "("):] for ln in lines] or [f"{name}(*args, **kwargs)"]
+        out = []
+        for ln in lines:
+            if len(lines) > 1:
+                out.append(f"{indent}@typing.overload")
+            ln = ln.replace("dlslime_b200._slime_c.", "").replace("json", "dict")
+            ln = re.sub(r"[A-Za-z_][\w]*(?:::[\w<>, ]+)+", "typing.Any", ln)  # a C++ type pybind11 could not name
+            out.append(f"{indent}def {ln}: ...")
+        return out
+
+    text = ["# Generated by dlslime_b200._build.generate_stubs() from the pybind11 signatures.", "import typing", ""]
+    for name, obj in sorted(vars(mod).items()):
+        if name.startswith("__"):
+            continue
+        if inspect.isclass(obj):
+            text.append(f"class {name}:")
+            body = []
+            for mname, m in sorted(vars(obj).items()):
+                if mname.startswith("__") and mname != "__init__":
+                    continue
+                if callable(m) or isinstance(m, (staticmethod, classmethod)):
+                    body += sigs(m, mname, "    ")
+            text += body or ["    ..."]
+            text.append("")
+        elif callable(obj):
+            text += sigs(obj, name, "") + [""]
+        elif inspect.ismodule(obj):
+            continue
+        else:
+            text.append(f"{name}: {type(obj).__name__}")
+    path = out_dir / "_slime_c.pyi"
+    path.write_text("\n".join(text) + "\n")
+    return path
 
 
 if __name__ == "__main__":
@@ -246,6 +349,9 @@ if __name__ == "__main__":
         build_cuda(verbose=v)
     elif "--host" in sys.argv:
         build_host(verbose=v)
+    elif "--stubs" in sys.argv:
+        print("stubs:", generate_stubs())
+        sys.exit(0)
     elif "--torch" in sys.argv:
         print("built:", build_torch_plugin(verbose=True))
         sys.exit(0)

@@ -117,6 +117,7 @@ class PeerAgent:
         self._connections_lock = threading.RLock()
         self._connected_cond = threading.Condition(self._connections_lock)
         self._notified: set[str] = set()
+        self._announced_at: dict[str, float] = {}  # conn_id -> time of our announcement (exchange-key fallback)
         self._desired_peers: set[str] = set()  # every peer connect_to was called for (the posted topology)
         self._logical_regions: Dict[str, LogicalMemoryRegion] = {}
         self._materialized: Dict[tuple, MaterializedMemoryRegion] = {}
@@ -157,6 +158,9 @@ class PeerAgent:
             self._obs.start()
 
     # ------------------------------------------------------------------ keys / topology
+    EXCHANGE_TTL = 600  # seconds an exchange key lives
+    EXCHANGE_GRACE = 0.3  # seconds a link waits for qp_ready before the exchange key of its peer is looked up
+
     def _key(self, suffix: str) -> str:
         return f"{self._scope}:{suffix}" if self._scope else suffix
 
@@ -411,9 +415,62 @@ class PeerAgent:
                 return
             self._notified.add(conn.conn_id)
         ep = self._ensure_endpoint(conn)
+        info_json = json.dumps(ep.endpoint_info())
         self._store.xadd(self._key(f"stream:{conn.peer_alias}"),
-                         {"type": "qp_ready", "peer": self.alias, "qp_info": json.dumps(ep.endpoint_info()),
+                         {"type": "qp_ready", "peer": self.alias, "qp_info": info_json,
                           "conn_meta": json.dumps(conn.meta()), "timestamp": str(int(time.time()))}, maxlen=1000)
+        # Interoperation with peers that only speak the older exchange-key handshake
+        # (dlslime/peer_agent/_mailbox.py:342-363 in the reference): the same description under
+        # exchange:{me}:{peer}:{conn_id}, which such a peer GETs, and without the connection id, which is the form it
+        # reads. Its own description is looked for by _poll_exchange_keys.
+        try:
+            self._store.set(self._key(f"exchange:{self.alias}:{conn.peer_alias}:{conn.conn_id}"), info_json, ex=self.EXCHANGE_TTL)
+            self._store.set(self._key(f"exchange:{self.alias}:{conn.peer_alias}"), info_json, ex=self.EXCHANGE_TTL)
+        except Exception as e:
+            log.debug("%s: exchange keys for %s not written: %s", self.alias, conn.peer_alias, e)
+        with self._connections_lock:
+            self._announced_at[conn.conn_id] = time.monotonic()
+
+    def _poll_exchange_keys(self, store=None) -> int:
+        """Connect links whose peer never sent ``qp_ready`` but published ``exchange:{peer}:{me}``.
+
+        Called from the mailbox thread between reads. A link qualifies once it has been announced for
+        ``EXCHANGE_GRACE`` seconds without an answer on the stream. Returns the number of links connected.
+        """
+        store = store or self._store
+        now = time.monotonic()
+        with self._connections_lock:
+            waiting = [c for c in self._connections.values() if c.state in ("pending", "connecting")
+                       and now - self._announced_at.get(c.conn_id, now) >= self.EXCHANGE_GRACE]
+        done = 0
+        for conn in waiting:
+            try:
+                raw = store.get(self._key(f"exchange:{conn.peer_alias}:{self.alias}"))
+            except Exception:
+                return done
+            if not raw:
+                continue
+            try:
+                info = json.loads(raw)
+            except (TypeError, ValueError):
+                log.warning("%s: exchange key of %s does not hold JSON", self.alias, conn.peer_alias)
+                continue
+            with self._connections_lock:
+                if conn.state == "connected":
+                    continue
+                conn.state = "connecting"
+            try:
+                self._ensure_endpoint(conn).connect(info)
+            except Exception as e:
+                log.warning("%s: connect to %s from its exchange key failed: %s", self.alias, conn.peer_alias, e)
+                continue
+            conn.peer_digest = hashlib.sha1(json.dumps(info, sort_keys=True).encode()).hexdigest()
+            with self._connections_lock:
+                conn.state = "connected"
+                self._connected_cond.notify_all()
+            tlog(f"{self.alias}: {conn.conn_id} connected through exchange keys")
+            done += 1
+        return done
 
     def _on_peer_ready(self, peer: str, meta: dict, info: dict) -> None:
         """The peer announced its endpoint: mirror the link locally, answer, connect."""

@@ -7,6 +7,10 @@ arrived before it started are not lost). Two message types travel on it, as in t
 * ``connect_peer`` -- written by NanoCtrl when the desired topology names a peer;
 * ``qp_ready``     -- written by a peer: its ``endpoint_info`` JSON plus the link metadata.
 
+Peers that only speak the older handshake publish their endpoint description under
+``exchange:{peer}:{me}`` instead of sending ``qp_ready``; links that stay unanswered are completed from
+that key (``PeerAgent._poll_exchange_keys``), and this side always writes its own ``exchange:`` keys too.
+
 The rendezvous is symmetric and idempotent: whichever side learns of the link first creates
 its endpoint and announces it once; the other side answers with its own announcement and both
 call ``endpoint.connect`` with what they received.
@@ -64,6 +68,12 @@ class StreamMailbox:
                         self._dispatch(fields)
                     except Exception:
                         log.exception("%s: mailbox message %s failed", self.agent.alias, fields.get("type"))
+            # links that were announced but never answered on the stream: the peer may speak only the older
+            # exchange-key handshake (dlslime/peer_agent/_mailbox.py:342-363 in the reference)
+            try:
+                self.agent._poll_exchange_keys(store)
+            except Exception:
+                log.exception("%s: exchange-key poll failed", self.agent.alias)
         store.close()
 
     def _dispatch(self, msg: dict) -> None:

@@ -1,6 +1,8 @@
 """Packaging: `pip install --no-build-isolation .` builds the native libraries in-tree with nvcc / g++
 (`dlslime_b200/_build.py`) and installs the package with them. Environment switches follow the reference's
-(`BUILD_NVLINK`, default ON: the CUDA kernel library; set it to OFF to install the host runtime only)."""
+`slime_option` set (`BUILD_RDMA`, `BUILD_NVLINK`, `BUILD_PYTHON`, `BUILD_TORCH_PLUGIN`, `BUILD_ASCEND_DIRECT`,
+`BUILD_BENCH`, `BUILD_TEST`; ON|OFF|TRUE|FALSE): e.g. `BUILD_NVLINK=OFF` installs the host runtime only,
+`BUILD_RDMA=OFF` leaves the RDMA transport out, `BUILD_TORCH_PLUGIN=OFF` skips the c10d backend."""
 import os
 import sys
 
@@ -18,10 +20,7 @@ class BuildNative(build_py):
         spec = importlib.util.spec_from_file_location("_slime_build", os.path.join(HERE, "dlslime_b200", "_build.py"))
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
-        mod.build_host()
-        mod.build_torch_plugin()
-        if os.environ.get("BUILD_NVLINK", "ON").upper() not in ("OFF", "0", "FALSE"):
-            mod.build_cuda()
+        mod.build_all()
         super().run()
 
 

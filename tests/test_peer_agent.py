@@ -271,3 +271,50 @@ def test_names_that_share_memory_are_independent(ctrl):
     finally:
         a.shutdown()
         b.shutdown()
+
+
+def test_peer_that_only_speaks_exchange_keys_connects(ctrl):
+    """Interop with the older handshake: the peer never sends ``qp_ready``; it publishes its endpoint description under
+    ``exchange:{peer}:{me}`` and reads ours from ``exchange:{me}:{peer}:{conn_id}``."""
+    import threading
+
+    from dlslime_b200 import _slime_c
+    from dlslime_b200.nanoctrl.client import NanoCtrlClient
+
+    a = PeerAgent(ctrl.url, alias="A", scope="s")
+    legacy = PeerAgent(ctrl.url, alias="OLD", scope="s")  # used for registration and its resource record only ...
+    legacy._mailbox.message_filter = lambda msg: False      # ... it ignores every stream message, as an old peer would
+    legacy._poll_exchange_keys = lambda store=None: 0       # and does not run the new fallback itself
+    ep = _slime_c.TcpEndpoint()
+    n = 1 << 16
+    theirs = ctypes.create_string_buffer(n)
+    ep.register_memory_region("kv", ctypes.addressof(theirs), 0, n)
+    kv = ctrl.store
+    try:
+        ba = _region(a, "kv", fill=5)
+        pending = a.connect_to("OLD")
+        # the old peer: publish, then wait for A's key and connect
+        kv.set("s:exchange:OLD:A", json.dumps(ep.endpoint_info()))
+        deadline = time.time() + 10
+        mine = None
+        while time.time() < deadline and mine is None:
+            keys = [k for k in kv.keys("s:exchange:A:OLD:*")]
+            if keys:
+                mine = json.loads(kv.get(keys[0]))
+            time.sleep(0.02)
+        assert mine is not None, "A never wrote its exchange key"
+        assert json.loads(kv.get("s:exchange:A:OLD")) == mine
+        assert ep.connect(mine) == 0
+        conn = pending.wait(10)
+        assert conn.is_connected()
+        # data flows over the link that was completed from the exchange key (handles straight on the endpoint:
+        # an old peer publishes no named memory keys either)
+        link = a._get_connection("OLD")
+        rh = link.endpoint.register_remote_memory_region("kv", ep.endpoint_info()["mr_info"]["kv"])
+        lh = link.endpoint.get_mr_handle("kv")
+        assert link.endpoint.write([(lh, rh, 128, 0, 4096)]).wait(10) == 0
+        assert theirs.raw[128:128 + 4096] == ba.raw[:4096]
+    finally:
+        ep.shutdown()
+        a.shutdown()
+        legacy.shutdown()
