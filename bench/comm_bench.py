@@ -158,6 +158,21 @@ def case_p2p(rank, world, contiguous=True):
         emit(rank, case="p2p_scatter_4096x64KiB", op=op, bytes=tot, us=round(ms * 1e3, 1), gbs=round(tot / ms / 1e6, 1),
              baseline_memcpy_loop_us=round(base * 1e3, 1), baseline_gbs=round(tot / base / 1e6, 1), speedup=round(base / ms, 2),
              frac_of_nvlink=round(tot / ms / 1e6 / NVLINK_GBS, 3), world=world)
+    if os.environ.get("SLIME_P2P_SWEEP", "0") == "1":
+        # what limits the scattered read: work unit (CTAs per 64 KiB piece), grid size, copy mechanism
+        from dlslime_b200.ops import nvlink as nv
+
+        for op in ("read", "write"):
+            for bulk in (1, 0):
+                for unit_kb in (16, 32, 64):
+                    for blocks in (0, 74, 148, 296, 592):
+                        nv.tune(unit_kb, bulk)
+                        ms = timed(lambda: ep._transfer(arr, op == "write", None, want_future=False, max_blocks=blocks), 10) if active else 0.0
+                        dist.barrier()
+                        ms = max_ms(ms, world)
+                        emit(rank, case="p2p_scatter_sweep", op=op, bulk=bulk, unit_kb=unit_kb, max_blocks=blocks,
+                             us=round(ms * 1e3, 1), gbs=round(seg * nseg / ms / 1e6, 1))
+        nv.tune(64, 1)
     dist.barrier()
     ep.close()
 

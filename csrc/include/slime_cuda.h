@@ -86,6 +86,22 @@ int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* gr
                             const void* row_info, const unsigned long long* scatter_bases8,
                             unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
                             const float* row_scale, void* status, void* stream);
+// The same GEMM (epilogues 0 and 1) over groups that become readable while it runs: the rows of group g are loaded
+// once group_ready[g] (u64, device memory) >= step, step being group_ready_target or *group_ready_epoch when that
+// pointer is not null. The kernel that fills the rows must have been launched before this one (another stream).
+int slime_grouped_gemm_bf16_gated(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                                  int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                                  const void* group_ready, unsigned long long group_ready_target,
+                                  const void* group_ready_epoch, void* status, void* stream);
+
+// group_trace (u64 [2 * num_groups], device memory, may be null): per group, when CTA 0's producer began to wait for it
+// and when it was ready (globaltimer ns). tile_counter (u32 [2], zero before the first launch, may be null): CTAs take
+// tiles from a shared counter instead of every gridDim-th tile.
+int slime_grouped_gemm_bf16_gated_traced(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                                         int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                                         const void* group_ready, unsigned long long group_ready_target,
+                                         const void* group_ready_epoch, void* group_trace, void* tile_counter, void* status,
+                                         void* stream);
 
 // ---- expert-parallel dispatch / combine (ep.cu) ------------------------------
 // cfg_bytes points at a packed EpConfig (see dlslime_b200/ops/ep.py for the field order).
@@ -96,6 +112,34 @@ int slime_ep_route(const void* cfg_bytes, const float* logits, int T, int* topk_
 int slime_ep_dispatch(const void* cfg_bytes, const void* x, long long ldx, int T, const int* topk_idx, const int* slot,
                       int* group_offsets, unsigned int* block_counter, unsigned long long epoch, int max_blocks,
                       void* status, void* stream);
+// Streamed form (rows pushed expert by expert, one arrival word per source rank and local expert, so that the
+// receive side and the grouped GEMM start while later experts are still in flight):
+//   route_ordered    route + push_off [num_experts + 1]: start of each expert's rows in this rank's push order
+//   layout           one block: waits for the counts, writes group_offsets [experts_per_rank + 1]
+//   dispatch_ordered permutation + ordered push of rows quantised before with slime_fp8_quant_1x128 (xq, xs dense);
+//                    perm [max_tokens * topk], pushed [num_experts] (zeroed scratch)
+//   recv_dequant_gated  per local expert: wait for the W arrival words, fp8 -> bf16, publish ready[j] = step;
+//                    deq_done [experts_per_rank] zeroed scratch, ready [experts_per_rank] u64
+int slime_ep_route_ordered(const void* cfg_bytes, const float* logits, int T, int* topk_idx, float* topk_w, int* slot,
+                           unsigned int* send_count, unsigned int* block_counter, unsigned long long epoch, int renormalize,
+                           int* push_off, void* stream);
+int slime_ep_layout(const void* cfg_bytes, int* group_offsets, unsigned long long epoch, void* status, void* stream);
+int slime_ep_dispatch_ordered(const void* cfg_bytes, const void* xq, const float* xs, int T, const int* topk_idx,
+                              const int* slot, const int* push_off, int* perm, unsigned int* pushed,
+                              unsigned long long epoch, int max_blocks, void* status, void* stream);
+int slime_ep_recv_dequant_gated(const void* cfg_bytes, const int* group_offsets, void* y, long long ldy,
+                                unsigned int* deq_done, unsigned long long* ready, unsigned long long epoch,
+                                int max_blocks, void* status, void* stream);
+// permutation + ONE kernel with both roles (two pushing blocks and one receiving block of every three; `blocks` a
+// multiple of 3, 0 = three per SM); the gated grouped GEMM launched behind it starts once all its blocks are running
+int slime_ep_stream_comm(const void* cfg_bytes, const void* xq, const float* xs, int T, const int* topk_idx, const int* slot,
+                         const int* push_off, int* perm, unsigned int* pushed, const int* group_offsets, void* y, long long ldy,
+                         unsigned int* deq_done, unsigned long long* ready, unsigned long long* ready_time,
+                         unsigned long long epoch, int blocks, void* status, void* stream);
+// ready_time (u64 [experts_per_rank], may be null): when each expert's ready word was published (globaltimer ns)
+int slime_ep_recv_dequant_gated_traced(const void* cfg_bytes, const int* group_offsets, void* y, long long ldy,
+                                       unsigned int* deq_done, unsigned long long* ready, unsigned long long* ready_time,
+                                       unsigned long long epoch, int max_blocks, void* status, void* stream);
 int slime_ep_recv_dequant(const void* cfg_bytes, const int* group_offsets, void* y, long long ldy, int expected_rows,
                           unsigned long long epoch, void* status, void* stream);
 int slime_ep_combine_push(const void* cfg_bytes, const void* y, long long ldy, const int* group_offsets,
@@ -121,6 +165,8 @@ unsigned long long slime_nvlink_ep_remote_addr(void* ep, int handle);
 // case the batch's completion word was withheld)
 int slime_nvlink_ep_status(void* ep, unsigned int* out4);
 int slime_nvlink_ep_status_clear(void* ep);
+// process-wide tuning of the batched kernels: work unit in KiB (0 = leave), bulk-copy kernel on / off (negative = leave)
+int slime_nvlink_ep_tune(int unit_kb, int bulk);
 // tuples: n x {local_handle, remote_handle, remote_offset, local_offset, length} as u64.
 int slime_nvlink_ep_transfer(void* ep, const unsigned long long* tuples, int n, int is_write, void* signal,
                              unsigned long long signal_value, int signal_add, int max_blocks, void* stream);

@@ -63,12 +63,26 @@ struct Args {
     int                       ag_local_direct; // tiles of the own shard read ag_src through the third tensor map and wait for nothing
     unsigned long long        ag_dst[8];       // address of the gathered A on every rank
     unsigned long long        ag_flags[8];     // address of the arrival counters (u64 per 128 rows) on every rank
+    // optional per-group readiness words (streamed expert-parallel receive): the rows of group g may be read once
+    // group_ready[g] >= the step number, which is group_ready_target or, when group_ready_epoch is set, the value
+    // found there when the kernel starts (a device-resident step counter, so that a captured step replays)
+    const unsigned long long* group_ready;
+    unsigned long long        group_ready_target;
+    const unsigned long long* group_ready_epoch;
+    // optional dynamic tile scheduler (u32 [2], zero before the first launch; the kernel leaves it zero): CTAs take
+    // tiles from a shared counter instead of every gridDim-th tile, so a CTA that starts late or shares its SM with
+    // other kernels simply takes fewer tiles
+    unsigned int*             tile_counter;
+    // optional trace (u64 [2 * num_groups + gridDim.x], device memory): CTA 0's producer records, per group, when it
+    // began to wait for the group and when the group was ready (globaltimer ns); behind that, every CTA's start time
+    unsigned long long*       group_trace;
     // A operand as e4m3 with 1x128 scales (kernels instantiated with A8): the tile is expanded to bf16 in shared memory
     const float*              a_scale;         // [M_total, K / 128]
     KernelStatus*             status;
     unsigned long long        wait_ns;
 };
 
+constexpr int kTileRing     = 4;     // tile indices in flight between the producer and the roles that follow it
 constexpr int kAgChunkBytes = 4096;  // staging buffer of the in-kernel all-gather push
 constexpr int kAgMaxBufs    = 6;
 constexpr int kSmemLimit    = 227 * 1024;
@@ -79,7 +93,7 @@ struct Smem {
     static constexpr int kBBytes     = BN * kBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kRawBytes   = A8 ? kBM * kBK : 0;  // e4m3 A tile of a stage as it arrives, before expansion
-    static constexpr int kBarBytes   = (3 * STAGES + 4 + kAgMaxBufs) * 8 + 16;
+    static constexpr int kBarBytes   = (3 * STAGES + 4 + kAgMaxBufs + 2 * kTileRing) * 8 + 16 + kTileRing * 4;
     static constexpr int kEpiBytes   = 128 * kEpiRowPitch;  // one padded 128-byte slot per tile row
     static constexpr int kBase       = STAGES * (kStageBytes + kRawBytes) + kEpiBytes + kBarBytes + 1024;  // + alignment slack
     // the push stages its chunks in whatever shared memory the tile ring leaves free
@@ -127,6 +141,14 @@ struct TileWalker {
     }
     __device__ bool next(TileCoord& c)
     {
+        const bool have = at(t, c);
+        t += gridDim.x;
+        return have;
+    }
+    // Coordinates of linear tile `lt`; calls must come with non-decreasing lt. False past the last tile.
+    __device__ bool at(int lt, TileCoord& c)
+    {
+        const int t = lt;
         while (g < a.num_groups) {
             const int tiles_g = g_mtiles * ntiles_n;
             if (t < cum + tiles_g) {
@@ -152,13 +174,71 @@ struct TileWalker {
                 c.row0    = g_begin + mt * kBM;
                 c.row_end = g_end;
                 c.nt      = nt;
-                t += gridDim.x;
                 return true;
             }
             cum += tiles_g;
             advance_group();
         }
         return false;
+    }
+};
+
+// Where a role gets its next tile index from: every gridDim-th tile (static), or the shared-memory ring that the
+// producer fills from the global tile counter (dynamic). One instance per thread that walks tiles.
+struct TileFeed {
+    bool      dynamic;
+    int       t_static;
+    int*      ring;
+    uint64_t* full;
+    uint64_t* empty;
+    int       slot  = 0;
+    uint32_t  phase = 0;
+    __device__ TileFeed(const Args& a, int* r, uint64_t* f, uint64_t* e):
+        dynamic(a.tile_counter != nullptr), t_static(blockIdx.x), ring(r), full(f), empty(e)
+    {
+    }
+    __device__ void advance()
+    {
+        if (++slot == kTileRing) {
+            slot = 0;
+            phase ^= 1;
+        }
+    }
+    // Consumer side: the next tile index, -1 at the end (or when the wait ran out, with ok = false).
+    __device__ int take(KernelStatus* st, unsigned long long lim, bool& ok)
+    {
+        if (!dynamic) {
+            const int t = t_static;
+            t_static += gridDim.x;
+            return t;
+        }
+        if (!mbar_wait(&full[slot], phase, st, 6, slot, lim)) {
+            ok = false;
+            return -1;
+        }
+        const int t = ring[slot];
+        mbar_arrive(&empty[slot]);
+        advance();
+        return t;
+    }
+    // Producer side: claims the next tile index and, in dynamic mode, hands it (or the end mark) to the ring.
+    __device__ int claim(const Args& a)
+    {
+        if (!dynamic) {
+            const int t = t_static;
+            t_static += gridDim.x;
+            return t;
+        }
+        return static_cast<int>(atomicAdd(a.tile_counter, 1u));
+    }
+    __device__ bool publish(int t, KernelStatus* st, unsigned long long lim)
+    {
+        if (!dynamic) return true;
+        if (!mbar_wait(&empty[slot], phase ^ 1, st, 7, slot, lim)) return false;
+        ring[slot] = t;
+        mbar_arrive(&full[slot]);
+        advance();
+        return true;
     }
 };
 
@@ -321,7 +401,10 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint64_t* tfull_bar  = raw_bar + STAGES;    // [2] accumulator ready
     uint64_t* tempty_bar = tfull_bar + 2;       // [2] accumulator drained
     uint64_t* ag_bar     = tempty_bar + 2;      // [kAgMaxBufs] push chunk loaded
-    uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(ag_bar + kAgMaxBufs);
+    uint64_t* tr_full    = ag_bar + kAgMaxBufs; // [kTileRing] tile index published (dynamic scheduler)
+    uint64_t* tr_empty   = tr_full + kTileRing; // [kTileRing] tile index taken by the MMA thread and every epilogue thread
+    uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(tr_empty + kTileRing);
+    int*      tile_ring  = reinterpret_cast<int*>(tmem_slot + 2);
     uint8_t*  ag_bufs    = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(epi_smem + S::kEpiBytes + S::kBarBytes) + 127) & ~uintptr_t(127));
     volatile uint32_t* fail_slot = tmem_slot + 1;  // set by any role whose wait ran out
 
@@ -348,6 +431,10 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         if (AG)
             for (int s = 0; s < kAgMaxBufs; ++s) mbar_init(&ag_bar[s], 1);
+        for (int s = 0; s < kTileRing; ++s) {
+            mbar_init(&tr_full[s], 1);
+            mbar_init(&tr_empty[s], 1 + 128);
+        }
         fence_mbar_init();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
@@ -370,7 +457,35 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int        stage = 0;
             uint32_t   phase = 0;
             bool       ok    = true;
-            while (ok && walk.next(tc)) {
+            int        ready_group = -1;
+            const unsigned long long group_target =
+                args.group_ready == nullptr ? 0ull : (args.group_ready_epoch ? *reinterpret_cast<const volatile unsigned long long*>(args.group_ready_epoch) : args.group_ready_target);
+            TileFeed feed(args, tile_ring, tr_full, tr_empty);
+            bool     ended = false;
+            // behind the per-group pairs, the trace holds one start time per CTA
+            if (args.group_trace != nullptr) args.group_trace[2 * args.num_groups + blockIdx.x] = globaltimer_ns();
+            while (ok) {
+                const int  lt   = feed.claim(args);
+                const bool have = walk.at(lt, tc);
+                if (!feed.publish(have ? lt : -1, st, lim)) {
+                    ok = false;
+                    break;
+                }
+                if (!have) {
+                    ended = true;
+                    break;
+                }
+                if (args.group_ready != nullptr && tc.group != ready_group) {
+                    // the rows of this group are written by a kernel that runs beside this one
+                    if (args.group_trace != nullptr && blockIdx.x == 0) args.group_trace[2 * tc.group] = globaltimer_ns();
+                    if (!wait_flag_ge(args.group_ready + tc.group, group_target, st, 11, tc.group, lim)) {
+                        ok = false;
+                        break;
+                    }
+                    if (args.group_trace != nullptr && blockIdx.x == 0) args.group_trace[2 * tc.group + 1] = globaltimer_ns();
+                    fence_proxy_async();
+                    ready_group = tc.group;
+                }
                 const CUtensorMap* mapA = &tmA;
                 int                arow = tc.row0;
                 bool               gate = args.a_ready != nullptr;
@@ -424,7 +539,10 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     }
                 }
             }
-            if (!ok) *fail_slot = 1;
+            if (!ok) {
+                *fail_slot = 1;
+                if (!ended) feed.publish(-1, nullptr, 1000000ull);  // let the roles behind this one leave too
+            }
         }
     }
     else if (warp == 1) {
@@ -438,7 +556,10 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t   acc_phase = 0;
             bool       ok = true;
             constexpr uint32_t idesc = make_idesc(kFmtBF16, kFmtBF16, kBM, BN);
-            while (ok && walk.next(tc)) {
+            TileFeed           feed(args, tile_ring, tr_full, tr_empty);
+            while (ok) {
+                const int lt = feed.take(st, lim, ok);
+                if (lt < 0 || !walk.at(lt, tc)) break;
                 if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, st, 2, acc, lim)) {
                     ok = false;
                     break;
@@ -528,7 +649,12 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         TileCoord  tc;
         int        acc = 0;
         uint32_t   acc_phase = 0;
-        while (walk.next(tc)) {
+        TileFeed   feed(args, tile_ring, tr_full, tr_empty);
+        bool       feed_ok = true;
+        while (true) {
+            const int lt = feed.take(st, lim, feed_ok);
+            if (!feed_ok) *fail_slot = 1;
+            if (lt < 0 || !walk.at(lt, tc)) break;
             if (!mbar_wait(&tfull_bar[acc], acc_phase, st, 4, acc, lim)) {
                 *fail_slot = 1;
                 break;
@@ -623,6 +749,19 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
     }
+    if (args.tile_counter != nullptr && threadIdx.x == 0) {
+        // the last CTA to leave puts the scheduler's words back to zero for the next launch (every CTA has taken its
+        // final, out-of-range index by now)
+        __threadfence();
+        if (atomicAdd(args.tile_counter + 1, 1u) == gridDim.x - 1) {
+            args.tile_counter[0] = 0;
+            args.tile_counter[1] = 0;
+            __threadfence();
+        }
+    }
+    // Launched beside the kernel that fills its groups (programmatic dependent launch): do not complete before that
+    // kernel has, so that stream order holds for whatever is launched next. A no-op after an ordinary launch.
+    if (args.group_ready != nullptr) griddep_wait();
 }
 
 }  // namespace gemm

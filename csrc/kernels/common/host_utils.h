@@ -73,6 +73,25 @@ inline int make_tmap_2d(CUtensorMap* tm, const void* base, CUtensorMapDataType d
     return 0;
 }
 
+// Launches `kernel` so that it may start before the kernel in front of it in `stream` has finished (programmatic
+// dependent launch; see griddep_launch_dependents in ptx.cuh).
+template<typename... KArgs, typename... Args>
+inline cudaError_t launch_programmatic(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                       Args&&... args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim          = grid;
+    cfg.blockDim         = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream           = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs                                          = attr;
+    cfg.numAttrs                                       = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Multiprocessor count of the current device (cached per device ordinal: a process may drive several GPUs).
 inline int sm_count()
 {

@@ -201,6 +201,23 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned 
 }
 
 // ---------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may start
+// while the kernel before it in the stream is still running, namely once every block of that kernel has executed
+// griddep_launch_dependents() or has exited, so all of them are running or done and cannot be starved by the
+// newcomer. The dependent orders itself against the data it needs with flags; griddep_wait() blocks until the
+// previous kernel has completed and its writes are visible, which a dependent calls at its END so that the usual
+// stream order holds again for whatever follows. Both are no-ops in a kernel launched the ordinary way.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void griddep_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)

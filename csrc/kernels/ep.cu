@@ -59,6 +59,9 @@ struct EpConfig {
     // call waited, total time waited}. Rows 8..15: {rows pushed to peer p so far, calls}. Written by thread 0 of
     // block 0 only; kernels of one buffer run in stream order, so there is nothing to synchronise.
     unsigned long long trace_ptr;
+    // Streamed form: u64 [world][experts_per_rank] in the symmetric region. Word (s, j) on rank p holds the last step
+    // for which every row of source rank s for p's local expert j has landed.
+    unsigned long long off_arrive;
 };
 
 enum TraceRow { kTraceDispatch = 0, kTraceReceive = 1, kTraceCombine = 2, kTraceWait = 3, kTraceBarrier = 4, kTracePeers = 8 };
@@ -89,6 +92,17 @@ __device__ __forceinline__ T* at(const EpConfig& c, int rank, unsigned long long
     return reinterpret_cast<T*>(c.peers[rank] + off);
 }
 
+// Streamed form: the order in which a rank pushes its rows. Step j of the order covers local expert j of every
+// destination, destinations taken round robin starting behind this rank (rank + 1, rank + 2, ..., this rank last), so
+// that every rank's expert 0 is complete first, then every rank's expert 1, ...: the order in which the grouped GEMMs
+// consume them.
+__device__ __forceinline__ int push_order_expert(const EpConfig& c, int o)
+{
+    const int j = o / c.world;
+    const int p = (c.rank + 1 + o % c.world) % c.world;
+    return p * c.experts_per_rank + j;
+}
+
 // ---------------------------------------------------------------------------
 // route: one warp per token
 // ---------------------------------------------------------------------------
@@ -96,7 +110,7 @@ __global__ void __launch_bounds__(256) ep_route_kernel(EpConfig cfg, const float
                                                       int* __restrict__ topk_idx, float* __restrict__ topk_w,
                                                       int* __restrict__ slot, unsigned int* __restrict__ send_count,
                                                       unsigned int* __restrict__ block_counter, unsigned long long epoch,
-                                                      int renormalize)
+                                                      int renormalize, int* __restrict__ push_off)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t    = blockIdx.x * 8 + warp;
@@ -169,7 +183,8 @@ __global__ void __launch_bounds__(256) ep_route_kernel(EpConfig cfg, const float
         }
     }
     // last block broadcasts this rank's count row and resets the counters for the next step
-    __shared__ bool is_last;
+    __shared__ bool         is_last;
+    __shared__ unsigned int s_cnt[kMaxExperts];
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
@@ -181,9 +196,23 @@ __global__ void __launch_bounds__(256) ep_route_kernel(EpConfig cfg, const float
         for (int e = threadIdx.x; e < E; e += blockDim.x) {
             const unsigned int       cnt  = atomicExch(&send_count[e], 0u);
             const unsigned long long word = (epoch << 32) | cnt;
+            s_cnt[e]                      = cnt;
             for (int p = 0; p < cfg.world; ++p) {
                 unsigned long long* dst = at<unsigned long long>(cfg, p, cfg.off_counts) + cfg.rank * E + e;
                 st_release_sys(dst, word);
+            }
+        }
+        if (push_off != nullptr) {
+            // streamed form: where each expert's rows start in this rank's push order (see push_order_expert)
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int acc = 0;
+                for (int o = 0; o < E; ++o) {
+                    const int e = push_order_expert(cfg, o);
+                    push_off[e] = acc;
+                    acc += static_cast<int>(s_cnt[e]);
+                }
+                push_off[E] = acc;
             }
         }
         if (threadIdx.x == 0) {
@@ -192,6 +221,18 @@ __global__ void __launch_bounds__(256) ep_route_kernel(EpConfig cfg, const float
             if (cfg.epoch_ptr) *reinterpret_cast<volatile unsigned long long*>(cfg.epoch_ptr) = epoch;
         }
     }
+}
+
+// Streamed form: the (token, k) pairs of this rank listed in push order. perm[push_off[e] + slot] = t * K + k.
+__global__ void __launch_bounds__(256) ep_perm_kernel(EpConfig cfg, int T, const int* __restrict__ topk_idx,
+                                                     const int* __restrict__ slot, const int* __restrict__ push_off,
+                                                     int* __restrict__ perm)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * cfg.topk) return;
+    const int e = topk_idx[i], s = slot[i];
+    if (e < 0 || e >= cfg.num_experts || s < 0) return;
+    perm[push_off[e] + s] = i;
 }
 
 // ---------------------------------------------------------------------------
@@ -320,6 +361,300 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpConfig cfg, const __
         st_release_sys(at<unsigned long long>(cfg, threadIdx.x, cfg.off_dispatch_done) + cfg.rank, epoch);
         if (threadIdx.x == 0) *block_counter = 0;
     }
+}
+
+// ---------------------------------------------------------------------------
+// Streamed form of dispatch and receive: the same bytes and the same layout, but pushed expert by expert (in
+// push_order_expert order) with one arrival word per (source rank, local expert), so that the receiving rank can
+// start on expert 0 while the rows of the later experts are still crossing NVLink. Three kernels that run at the same
+// time on three streams: ep_dispatch_ordered_kernel (pushes), ep_recv_dequant_gated_kernel (waits per expert for the
+// W arrival words, expands that expert's rows to bf16, then publishes a local "ready" word) and the grouped GEMM,
+// whose TMA producer waits for the ready word of a group before it loads that group's first tile. The layer runs the
+// first two as ONE kernel (ep_stream_comm_kernel: two pushing blocks and one receiving block per SM) and launches the
+// GEMM behind it in the same stream as its programmatic dependent: the GEMM may start once every block of the kernel
+// in front of it is running (or done), so a kernel that waits can never keep the kernel it waits for off the device,
+// and no second stream (whose work could be queued behind a waiting kernel) is involved. The grids are sized so that
+// everything fits on the device together; the GEMM waits for its predecessor's completion at its end. The two roles
+// also exist as kernels of their own (ep_dispatch_ordered_kernel, ep_recv_dequant_gated_kernel), launched the
+// ordinary way, for callers that replay a group of ranks step by step.
+// ---------------------------------------------------------------------------
+
+// Waits for the W count rows of this step; returns false (and reports) when the wait ran out. Fills, per expert,
+// the total rows, the rows of lower ranks and this rank's own count.
+__device__ __forceinline__ bool ep_wait_counts(const EpConfig& cfg, unsigned long long epoch, KernelStatus* st,
+                                               unsigned int* s_total, unsigned int* s_before, unsigned int* s_mine,
+                                               int* s_ok)
+{
+    const int                E = cfg.num_experts, W = cfg.world;
+    const unsigned long long lim    = cfg.wait_ns ? cfg.wait_ns : kDefaultWaitNs;
+    const unsigned long long* counts = at<unsigned long long>(cfg, cfg.rank, cfg.off_counts);
+    if (threadIdx.x == 0) *s_ok = 1;
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        unsigned int total = 0, before = 0, mine = 0;
+        for (int s = 0; s < W; ++s) {
+            const unsigned long long* wp = counts + s * E + e;
+            unsigned long long        v  = ld_acquire_sys(wp);
+            if ((v >> 32) != epoch) {
+                const unsigned long long t0 = globaltimer_ns();
+                while (((v = ld_acquire_sys(wp)) >> 32) != epoch) {
+                    if (globaltimer_ns() - t0 > lim) {
+                        report_status(st, K_TIMEOUT, 22, s, epoch, v >> 32);
+                        *s_ok = 0;
+                        break;
+                    }
+                    __nanosleep(20);
+                }
+            }
+            const unsigned int c = static_cast<unsigned int>(v & 0xffffffffu);
+            total += c;
+            if (s < cfg.rank) before += c;
+            if (s == cfg.rank) mine = c;
+        }
+        s_total[e]  = total;
+        s_before[e] = before;
+        if (s_mine) s_mine[e] = mine;
+    }
+    __syncthreads();
+    return *s_ok != 0;
+}
+
+// One block: waits for the counts and writes the row prefix of this rank's local experts, so that the kernels that
+// walk the groups can be launched without waiting for the dispatch kernel.
+__global__ void __launch_bounds__(256) ep_layout_kernel(EpConfig cfg, int* __restrict__ group_offsets,
+                                                       unsigned long long epoch, KernelStatus* st)
+{
+    __shared__ unsigned int s_total[kMaxExperts];
+    __shared__ unsigned int s_before[kMaxExperts];
+    __shared__ int          s_ok;
+    epoch = resolve_epoch(cfg, epoch);
+    const bool ok = ep_wait_counts(cfg, epoch, st, s_total, s_before, nullptr, &s_ok);
+    if (threadIdx.x == 0) {
+        const int    El = cfg.experts_per_rank, first = cfg.rank * El;
+        unsigned int off = 0;
+        for (int j = 0; j < El; ++j) {
+            group_offsets[j] = static_cast<int>(min(off, static_cast<unsigned int>(cfg.recv_cap)));
+            off += ok ? s_total[first + j] : 0u;
+        }
+        group_offsets[El] = static_cast<int>(min(off, static_cast<unsigned int>(cfg.recv_cap)));
+    }
+}
+
+// One warp per (token, k) pair, in push order. The tokens were quantised once by the stand-alone 1x128 kernel into a
+// local staging buffer (xq, xs); the warp copies the token's e4m3 row, its scales and a source word to their exact
+// row of the owner's packed buffer with 16-byte loads and stores and nothing else, so that the kernel costs the
+// tensor-core kernel it runs beside almost no issue slots. The warp that completes an expert (its pair count reaches
+// this rank's count for the expert) publishes the arrival word on the owner.
+__device__ __forceinline__ void ep_push_role(const EpConfig& cfg, const uint8_t* __restrict__ xq, const float* __restrict__ xs,
+                                             int T, const int* __restrict__ topk_idx, const int* __restrict__ slot,
+                                             const int* __restrict__ perm, const int* __restrict__ push_off,
+                                             unsigned int* __restrict__ pushed, unsigned long long epoch, KernelStatus* st,
+                                             int vb, int nvb)
+{
+    __shared__ unsigned int s_total[kMaxExperts];
+    __shared__ unsigned int s_dst_row[kMaxExperts];  // first the rows of lower ranks, then the destination row
+    __shared__ unsigned int s_mine[kMaxExperts];
+    __shared__ int          s_ok;
+    unsigned int* const     s_before = s_dst_row;
+    const int E = cfg.num_experts, El = cfg.experts_per_rank, K = cfg.topk, H = cfg.hidden;
+    epoch = resolve_epoch(cfg, epoch);
+    const unsigned long long trace_t0 = (cfg.trace_ptr != 0 && vb == 0 && threadIdx.x == 0) ? globaltimer_ns() : 0;
+    if (!ep_wait_counts(cfg, epoch, st, s_total, s_before, s_mine, &s_ok)) return;
+    if ((cfg.trace_ptr != 0 && vb == 0 && threadIdx.x == 0)) trace_waited(cfg, kTraceDispatch, trace_t0);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int    first = (e / El) * El;
+        unsigned int off   = 0;
+        for (int j = first; j < e; ++j) off += s_total[j];
+        s_dst_row[e] = off + s_before[e];  // in place: every thread touches only its own experts' entries
+        // an expert this rank sends nothing to is complete from this rank's side at once
+        if (vb == 0 && s_mine[e] == 0)
+            st_release_sys(at<unsigned long long>(cfg, e / El, cfg.off_arrive) + cfg.rank * El + (e - first), epoch);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gpr = H / 128;               // scales per row
+    const int row_vecs = H / 16;           // 16-byte pieces of a payload row
+    const int scale_vecs = gpr / 4;        // 16-byte pieces of a scale row (hidden is a multiple of 512)
+    const int rows = push_off[E];
+    for (int r = vb * 8 + warp; r < rows; r += nvb * 8) {
+        const int i = perm[r];
+        const int e = (i >= 0 && i < T * K) ? topk_idx[i] : -1;
+        if (e < 0 || e >= E) {
+            if (lane == 0) report_status(st, K_BAD_INDEX, 23, r, T * K, static_cast<unsigned long long>(i));
+            continue;
+        }
+        const int          t   = i / K;
+        const unsigned int row = s_dst_row[e] + static_cast<unsigned int>(slot[i]);
+        const int          p   = e / El;
+        if (row < static_cast<unsigned int>(cfg.recv_cap)) {
+            const uint4* src = reinterpret_cast<const uint4*>(xq + static_cast<long long>(t) * H);
+            uint4*       dst = reinterpret_cast<uint4*>(at<uint8_t>(cfg, p, cfg.off_x) + static_cast<unsigned long long>(row) * H);
+            int v = lane;
+            for (; v + 6 * 32 < row_vecs; v += 7 * 32) {
+                uint4 tmp[7];
+#pragma unroll
+                for (int u = 0; u < 7; ++u) tmp[u] = src[v + u * 32];
+#pragma unroll
+                for (int u = 0; u < 7; ++u) dst[v + u * 32] = tmp[u];
+            }
+            for (; v < row_vecs; v += 32) dst[v] = src[v];
+            if (lane < scale_vecs)
+                reinterpret_cast<uint4*>(at<float>(cfg, p, cfg.off_scale) + static_cast<unsigned long long>(row) * gpr)[lane] =
+                    reinterpret_cast<const uint4*>(xs + static_cast<long long>(t) * gpr)[lane];
+            for (int sv = 32 + lane; sv < scale_vecs; sv += 32)  // rows wider than 16384 elements
+                reinterpret_cast<uint4*>(at<float>(cfg, p, cfg.off_scale) + static_cast<unsigned long long>(row) * gpr)[sv] =
+                    reinterpret_cast<const uint4*>(xs + static_cast<long long>(t) * gpr)[sv];
+            if (lane == 0)
+                at<unsigned long long>(cfg, p, cfg.off_info)[row] =
+                    (static_cast<unsigned long long>(cfg.rank) << 48) | static_cast<unsigned long long>(i);
+        }
+        else if (lane == 0) {
+            report_status(st, K_BAD_INDEX, 21, e, cfg.recv_cap, row);
+        }
+        __syncwarp();
+        if (lane == 0) {
+            fence_acq_rel_sys();  // this row's stores are ordered before the count below, for whoever completes the expert
+            if (atomicAdd(&pushed[e], 1u) + 1u == s_mine[e]) {
+                atomicExch(&pushed[e], 0u);
+                fence_acq_rel_sys();
+                st_release_sys(at<unsigned long long>(cfg, p, cfg.off_arrive) + cfg.rank * El + (e - p * El), epoch);
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256, 5) ep_dispatch_ordered_kernel(EpConfig cfg, const uint8_t* __restrict__ xq,
+                                                                    const float* __restrict__ xs, int T,
+                                                                    const int* __restrict__ topk_idx,
+                                                                    const int* __restrict__ slot, const int* __restrict__ perm,
+                                                                    const int* __restrict__ push_off,
+                                                                    unsigned int* __restrict__ pushed,
+                                                                    unsigned long long epoch, KernelStatus* st)
+{
+    ep_push_role(cfg, xq, xs, T, topk_idx, slot, perm, push_off, pushed, epoch, st, blockIdx.x, gridDim.x);
+}
+
+// Receive side of the streamed form. Every block goes through the local experts in order (in small batches): wait
+// for the W arrival words of each expert of the batch, expand this block's share of the batch's rows, count itself
+// in; the last block publishes ready[j] = step for the batch's experts, which is what the grouped GEMM's producer
+// waits for.
+__device__ __forceinline__ void ep_recv_role(const EpConfig& cfg, const int* __restrict__ group_offsets,
+                                             __nv_bfloat16* __restrict__ y, long long ldy, unsigned int* __restrict__ deq_done,
+                                             unsigned long long* __restrict__ ready, unsigned long long* __restrict__ ready_time,
+                                             unsigned long long epoch, KernelStatus* st, int vb, int nvb)
+{
+    __shared__ int s_ok;
+    epoch = resolve_epoch(cfg, epoch);
+    const int                El = cfg.experts_per_rank, W = cfg.world, gpr = cfg.hidden / 128;
+    const unsigned long long lim = cfg.wait_ns ? cfg.wait_ns : kDefaultWaitNs;
+    const uint8_t*           q   = at<uint8_t>(cfg, cfg.rank, cfg.off_x);
+    const float*             sc  = at<float>(cfg, cfg.rank, cfg.off_scale);
+    const unsigned long long* arrive = at<unsigned long long>(cfg, cfg.rank, cfg.off_arrive);
+    const unsigned long long trace_t0 = (cfg.trace_ptr != 0 && vb == 0 && threadIdx.x == 0) ? globaltimer_ns() : 0;
+    unsigned long long       waited   = 0;
+    // Experts are taken in batches of consecutive experts (at most 32 batches per step), so that the fixed cost of a
+    // batch (polling the arrival words, the block-wide and grid-wide counting) is paid per ~1/32 of the rows, not per
+    // expert: with 256 local experts of ~128 rows each a per-expert round would cost more than the rows themselves.
+    const int batch = (El + 31) / 32;
+    for (int j0 = 0; j0 < El; j0 += batch) {
+        const int j1 = min(El, j0 + batch);
+        if (threadIdx.x == 0) s_ok = 1;
+        __syncthreads();
+        for (int w = threadIdx.x; w < W * (j1 - j0); w += blockDim.x) {
+            const int                src = w / (j1 - j0), j = j0 + w % (j1 - j0);
+            const unsigned long long w0  = trace_t0 ? globaltimer_ns() : 0;
+            if (!wait_flag_ge(arrive + src * El + j, epoch, st, 31, src, lim)) s_ok = 0;
+            if (trace_t0 && threadIdx.x == 0) waited += globaltimer_ns() - w0;
+        }
+        __syncthreads();
+        if (!s_ok) break;  // nothing is published for this or any later expert: the GEMM's own wait reports too
+        const long long g0 = static_cast<long long>(group_offsets[j0]) * gpr, g1 = static_cast<long long>(group_offsets[j1]) * gpr;
+        // four independent 128-element groups per thread and pass: the kernel runs with one block per SM beside the
+        // GEMM, so its throughput comes from loads in flight per thread, not from the number of threads
+        const long long stride = (static_cast<long long>(nvb) * blockDim.x) >> 4;
+        const int       sub    = threadIdx.x & 15;
+        for (long long gid = g0 + ((static_cast<long long>(vb) * blockDim.x + threadIdx.x) >> 4); gid < g1; gid += 4 * stride) {
+            uint2 raw[4];
+            float scl[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const long long g = gid + u * stride;
+                if (g < g1) {
+                    raw[u] = *reinterpret_cast<const uint2*>(q + g * 128 + sub * 8);
+                    scl[u] = sc[g];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const long long g = gid + u * stride;
+                if (g < g1) {
+                    long long oy = g * 128;
+                    if (ldy != cfg.hidden) {
+                        const long long row = g / gpr;
+                        oy                  = row * ldy + (g - row * gpr) * 128;
+                    }
+                    float v[8];
+                    dequant_fp8x8(raw[u], scl[u], v);
+                    *reinterpret_cast<uint4*>(y + oy + sub * 8) = pack_bf16x8(v);
+                }
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(&deq_done[j0], 1u) == nvb - 1) {
+                atomicExch(&deq_done[j0], 0u);
+                __threadfence();
+                for (int j = j0; j < j1; ++j) st_release_sys(ready + j, epoch);
+                if (ready_time != nullptr) {
+                    const unsigned long long now = globaltimer_ns();
+                    for (int j = j0; j < j1; ++j) ready_time[j] = now;
+                }
+            }
+        }
+    }
+    if ((cfg.trace_ptr != 0 && vb == 0 && threadIdx.x == 0)) {
+        unsigned long long* r = reinterpret_cast<unsigned long long*>(cfg.trace_ptr) + 4 * kTraceReceive;
+        r[0] += 1;
+        r[1] = trace_t0;
+        r[2] = waited;
+        r[3] += waited;
+    }
+}
+
+__global__ void __launch_bounds__(256) ep_recv_dequant_gated_kernel(EpConfig cfg, const int* __restrict__ group_offsets,
+                                                                   __nv_bfloat16* __restrict__ y, long long ldy,
+                                                                   unsigned int* __restrict__ deq_done,
+                                                                   unsigned long long* __restrict__ ready,
+                                                                   unsigned long long* __restrict__ ready_time,
+                                                                   unsigned long long epoch, KernelStatus* st)
+{
+    ep_recv_role(cfg, group_offsets, y, ldy, deq_done, ready, ready_time, epoch, st, blockIdx.x, gridDim.x);
+}
+
+// Both roles in ONE kernel, which is what the layer launches: of every three consecutive blocks two push and one
+// receives, so that expert 0 is expanded while the later experts are still being pushed, and the grouped GEMM behind
+// this kernel is its programmatic dependent: it is scheduled as soon as every block of this kernel is running. (With
+// the two roles as two kernels the GEMM, third in the chain, was found to start only when the first kernel had
+// completed.) Grid: 3 blocks per SM, all resident beside the GEMM's one CTA per SM.
+__global__ void __launch_bounds__(256, 5) ep_stream_comm_kernel(EpConfig cfg, const uint8_t* __restrict__ xq,
+                                                               const float* __restrict__ xs, int T,
+                                                               const int* __restrict__ topk_idx, const int* __restrict__ slot,
+                                                               const int* __restrict__ perm, const int* __restrict__ push_off,
+                                                               unsigned int* __restrict__ pushed,
+                                                               const int* __restrict__ group_offsets,
+                                                               __nv_bfloat16* __restrict__ y, long long ldy,
+                                                               unsigned int* __restrict__ deq_done,
+                                                               unsigned long long* __restrict__ ready,
+                                                               unsigned long long* __restrict__ ready_time,
+                                                               unsigned long long epoch, KernelStatus* st)
+{
+    griddep_launch_dependents();  // this block is running: the grouped GEMM behind this kernel may be scheduled
+    const int triple = blockIdx.x / 3, role = blockIdx.x % 3, triples = gridDim.x / 3;  // the grid is a multiple of 3
+    if (role == 2)
+        ep_recv_role(cfg, group_offsets, y, ldy, deq_done, ready, ready_time, epoch, st, triple, triples);
+    else
+        ep_push_role(cfg, xq, xs, T, topk_idx, slot, perm, push_off, pushed, epoch, st, 2 * triple + role, 2 * triples);
 }
 
 // Waits (bounded) until every rank's flag in `off` reached `epoch`. Called by all threads of a block.
@@ -509,9 +844,9 @@ int slime_ep_config_size(void)
     return static_cast<int>(sizeof(EpConfig));
 }
 
-int slime_ep_route(const void* cfg_bytes, const float* logits, int T, int* topk_idx, float* topk_w, int* slot,
-                   unsigned int* send_count, unsigned int* block_counter, unsigned long long epoch, int renormalize,
-                   void* stream)
+static int route_impl(const void* cfg_bytes, const float* logits, int T, int* topk_idx, float* topk_w, int* slot,
+                      unsigned int* send_count, unsigned int* block_counter, unsigned long long epoch, int renormalize,
+                      int* push_off, void* stream)
 {
     EpConfig cfg;
     memcpy(&cfg, cfg_bytes, sizeof(cfg));
@@ -519,7 +854,88 @@ int slime_ep_route(const void* cfg_bytes, const float* logits, int T, int* topk_
     if (T < 0 || T > cfg.max_tokens) return fail("ep route: T=%d exceeds max_tokens=%d", T, cfg.max_tokens);
     const int blocks = T > 0 ? (T + 7) / 8 : 1;
     ep_route_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(cfg, logits, T, topk_idx, topk_w, slot,
-                                                                          send_count, block_counter, epoch, renormalize);
+                                                                          send_count, block_counter, epoch, renormalize,
+                                                                          push_off);
+    SLIME_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+int slime_ep_route(const void* cfg_bytes, const float* logits, int T, int* topk_idx, float* topk_w, int* slot,
+                   unsigned int* send_count, unsigned int* block_counter, unsigned long long epoch, int renormalize,
+                   void* stream)
+{
+    return route_impl(cfg_bytes, logits, T, topk_idx, topk_w, slot, send_count, block_counter, epoch, renormalize, nullptr, stream);
+}
+
+// Streamed form: route that also writes push_off [num_experts + 1], the start of every expert's rows in this rank's
+// push order (by expert id; the last entry is the number of (token, k) pairs that go anywhere).
+int slime_ep_route_ordered(const void* cfg_bytes, const float* logits, int T, int* topk_idx, float* topk_w, int* slot,
+                           unsigned int* send_count, unsigned int* block_counter, unsigned long long epoch, int renormalize,
+                           int* push_off, void* stream)
+{
+    if (push_off == nullptr) return fail("ep route (ordered): push_off is null");
+    return route_impl(cfg_bytes, logits, T, topk_idx, topk_w, slot, send_count, block_counter, epoch, renormalize, push_off, stream);
+}
+
+int slime_ep_layout(const void* cfg_bytes, int* group_offsets, unsigned long long epoch, void* status, void* stream)
+{
+    EpConfig cfg;
+    memcpy(&cfg, cfg_bytes, sizeof(cfg));
+    if (check_cfg(cfg)) return -1;
+    ep_layout_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(cfg, group_offsets, epoch, static_cast<KernelStatus*>(status));
+    SLIME_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+// Streamed dispatch: the permutation kernel followed by the ordered push of rows that were quantised before
+// (xq [T, hidden] e4m3 and xs [T, hidden / 128] scales, dense, from slime_fp8_quant_1x128). perm [max_tokens * topk]
+// and pushed [num_experts] (zero before the first call; the kernel leaves it zero) are scratch of the caller.
+int slime_ep_dispatch_ordered(const void* cfg_bytes, const void* xq, const float* xs, int T, const int* topk_idx,
+                              const int* slot, const int* push_off, int* perm, unsigned int* pushed,
+                              unsigned long long epoch, int max_blocks, void* status, void* stream)
+{
+    EpConfig cfg;
+    memcpy(&cfg, cfg_bytes, sizeof(cfg));
+    if (check_cfg(cfg)) return -1;
+    if (cfg.off_arrive == 0) return fail("ep dispatch (ordered): the buffer has no arrival words");
+    if (T < 0 || T > cfg.max_tokens) return fail("ep dispatch: T=%d exceeds max_tokens=%d", T, cfg.max_tokens);
+    if ((reinterpret_cast<unsigned long long>(xq) | reinterpret_cast<unsigned long long>(xs)) & 15)
+        return fail("ep dispatch (ordered): the staged rows and scales must be 16-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int    pairs = T * cfg.topk;
+    if (pairs > 0) {
+        ep_perm_kernel<<<(pairs + 255) / 256, 256, 0, s>>>(cfg, T, topk_idx, slot, push_off, perm);
+        SLIME_CUDA_OK(cudaGetLastError());
+    }
+    const int grid = grid_for(pairs, max_blocks > 0 ? max_blocks : sm_count() * 2);
+    ep_dispatch_ordered_kernel<<<grid, 256, 0, s>>>(cfg, static_cast<const uint8_t*>(xq), xs, T, topk_idx, slot, perm,
+                                                    push_off, pushed, epoch, static_cast<KernelStatus*>(status));
+    SLIME_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+// Streamed receive: per-expert wait + fp8 -> bf16, publishing ready[j] = step for the grouped GEMM. deq_done
+// [experts_per_rank] is zeroed scratch of the caller; ready [experts_per_rank] u64 keeps the last step per expert.
+int slime_ep_recv_dequant_gated(const void* cfg_bytes, const int* group_offsets, void* y, long long ldy,
+                                unsigned int* deq_done, unsigned long long* ready, unsigned long long epoch,
+                                int max_blocks, void* status, void* stream)
+{
+    return slime_ep_recv_dequant_gated_traced(cfg_bytes, group_offsets, y, ldy, deq_done, ready, nullptr, epoch, max_blocks, status, stream);
+}
+
+// The same with a trace: ready_time (u64 [experts_per_rank], device memory, may be null) receives the time
+// (globaltimer ns) at which each expert's ready word was published.
+int slime_ep_recv_dequant_gated_traced(const void* cfg_bytes, const int* group_offsets, void* y, long long ldy,
+                                       unsigned int* deq_done, unsigned long long* ready, unsigned long long* ready_time,
+                                       unsigned long long epoch, int max_blocks, void* status, void* stream)
+{
+    EpConfig cfg;
+    memcpy(&cfg, cfg_bytes, sizeof(cfg));
+    if (check_cfg(cfg)) return -1;
+    if (cfg.off_arrive == 0) return fail("ep receive (gated): the buffer has no arrival words");
+    const int blocks = max_blocks > 0 ? max_blocks : sm_count();
+    ep_recv_dequant_gated_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        cfg, group_offsets, static_cast<__nv_bfloat16*>(y), ldy, deq_done, ready, ready_time, epoch, static_cast<KernelStatus*>(status));
     SLIME_CUDA_OK(cudaGetLastError());
     return 0;
 }
@@ -606,6 +1022,48 @@ int slime_ep_combine_reduce(const void* cfg_bytes, int T, const int* topk_idx, c
     ep_combine_reduce_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         cfg, T, topk_idx, topk_w, static_cast<__nv_bfloat16*>(out), ldo, epoch, do_signal,
         static_cast<KernelStatus*>(status));
+    SLIME_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+// The streamed form as the layer runs it: the permutation kernel, then ONE kernel in which two of every three blocks
+// push and the third receives (arguments as for slime_ep_dispatch_ordered and slime_ep_recv_dequant_gated_traced).
+// The gated grouped GEMM launched behind it starts as soon as every block of this kernel is running. blocks_per_sm:
+// 3 by default (two pushing, one receiving); must be a multiple of 3.
+int slime_ep_stream_comm(const void* cfg_bytes, const void* xq, const float* xs, int T, const int* topk_idx, const int* slot,
+                         const int* push_off, int* perm, unsigned int* pushed, const int* group_offsets, void* y, long long ldy,
+                         unsigned int* deq_done, unsigned long long* ready, unsigned long long* ready_time,
+                         unsigned long long epoch, int blocks, void* status, void* stream)
+{
+    EpConfig cfg;
+    memcpy(&cfg, cfg_bytes, sizeof(cfg));
+    if (check_cfg(cfg)) return -1;
+    if (cfg.off_arrive == 0) return fail("ep stream comm: the buffer has no arrival words");
+    if (T < 0 || T > cfg.max_tokens) return fail("ep stream comm: T=%d exceeds max_tokens=%d", T, cfg.max_tokens);
+    if ((reinterpret_cast<unsigned long long>(xq) | reinterpret_cast<unsigned long long>(xs)) & 15)
+        return fail("ep stream comm: the staged rows and scales must be 16-byte aligned");
+    if (blocks <= 0) blocks = 3 * sm_count();
+    if (blocks % 3 != 0) return fail("ep stream comm: the grid (%d) must be a multiple of 3", blocks);
+    cudaStream_t s     = static_cast<cudaStream_t>(stream);
+    const int    pairs = T * cfg.topk;
+    if (pairs > 0) {
+        ep_perm_kernel<<<(pairs + 255) / 256, 256, 0, s>>>(cfg, T, topk_idx, slot, push_off, perm);
+        SLIME_CUDA_OK(cudaGetLastError());
+    }
+    // The GEMM that joins this kernel on every SM needs almost all of the SM's shared memory. An SM can only change its
+    // split between L1 and shared memory while it is empty, so this kernel asks for the largest shared-memory split
+    // itself: the GEMM's CTA then fits beside the resident blocks instead of waiting for them to leave.
+    static bool carveout_set[64] = {false};
+    int         dev = 0;
+    SLIME_CUDA_OK(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !carveout_set[dev]) {
+        SLIME_CUDA_OK(cudaFuncSetAttribute(ep_stream_comm_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                           cudaSharedmemCarveoutMaxShared));
+        carveout_set[dev] = true;
+    }
+    ep_stream_comm_kernel<<<blocks, 256, 0, s>>>(cfg, static_cast<const uint8_t*>(xq), xs, T, topk_idx, slot, perm, push_off, pushed,
+                                                 group_offsets, static_cast<__nv_bfloat16*>(y), ldy, deq_done, ready, ready_time,
+                                                 epoch, static_cast<KernelStatus*>(status));
     SLIME_CUDA_OK(cudaGetLastError());
     return 0;
 }

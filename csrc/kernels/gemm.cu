@@ -59,6 +59,11 @@ int launch_bn(const void* A, const void* B, const void* A_local, int rows_local,
     // a fused all-gather kernel keeps the full grid (its extra warps push whatever the tile count is);
     // grouped launches do not know their tile count on the host
     if (!AG && args.num_groups == 1 && tiles < grid) grid = static_cast<int>(tiles);
+    if (args.group_ready != nullptr) {
+        // groups that are filled while this kernel runs: start beside the kernel in front of it in the stream
+        SLIME_CUDA_OK(launch_programmatic(kern, dim3(grid), dim3(threads), S::kTotal, stream, tmA, tmB, tmAL, args));
+        return 0;
+    }
     kern<<<grid, threads, S::kTotal, stream>>>(tmA, tmB, tmAL, args);
     SLIME_CUDA_OK(cudaGetLastError());
     return 0;
@@ -288,15 +293,82 @@ int slime_ag_gemm(int mode, const void* x_local, const void* a_full, const void*
     return fail("ag_gemm: unknown mode %d", mode);
 }
 
+static int grouped_gemm_impl(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                            int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                            const void* row_info, const unsigned long long* scatter_bases8,
+                            unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
+                            const float* row_scale, const unsigned long long* group_ready,
+                            unsigned long long group_ready_target, const unsigned long long* group_ready_epoch,
+                            void* status, void* stream);
+static thread_local unsigned long long* g_group_trace  = nullptr;  // set around one traced launch
+static thread_local unsigned int*       g_tile_counter = nullptr;
+int slime_grouped_gemm_bf16_gated_traced(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                                         int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                                         const void* group_ready, unsigned long long group_ready_target,
+                                         const void* group_ready_epoch, void* group_trace, void* tile_counter, void* status,
+                                         void* stream);
+
 int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
                             int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
                             const void* row_info, const unsigned long long* scatter_bases8,
                             unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
                             const float* row_scale, void* status, void* stream)
 {
+    return grouped_gemm_impl(A, B, C, group_offsets, num_groups, M_cap, N, K, lda, ldb, ldc, epilogue, row_info, scatter_bases8,
+                             scatter_row_bytes, scatter_slots, row_scale, nullptr, 0, nullptr, status, stream);
+}
+
+// The grouped GEMM whose groups become readable while it runs: before the first tile of group g is loaded, the
+// producer waits (bounded) until group_ready[g] >= step, where step is group_ready_target or, if group_ready_epoch
+// is not null, the value stored there when the kernel starts. Whoever fills the rows (the streamed expert-parallel
+// receive) runs beside this kernel and must have been launched before it.
+int slime_grouped_gemm_bf16_gated(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                                  int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                                  const void* group_ready, unsigned long long group_ready_target,
+                                  const void* group_ready_epoch, void* status, void* stream)
+{
+    return slime_grouped_gemm_bf16_gated_traced(A, B, C, group_offsets, num_groups, M_cap, N, K, lda, ldb, ldc, epilogue, group_ready,
+                                                group_ready_target, group_ready_epoch, nullptr, nullptr, status, stream);
+}
+
+// The same with a trace and a dynamic tile scheduler: group_trace (u64 [2 * num_groups], device memory, may be null)
+// receives, per group, when CTA 0's producer began to wait for it and when it was ready (globaltimer ns); tile_counter
+// (u32 [2], zero before the first launch, may be null) makes the CTAs take tiles from a shared counter, so that a CTA
+// which shares its SM with the kernel that fills the groups, or starts late, takes fewer tiles.
+int slime_grouped_gemm_bf16_gated_traced(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                                         int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                                         const void* group_ready, unsigned long long group_ready_target,
+                                         const void* group_ready_epoch, void* group_trace, void* tile_counter, void* status,
+                                         void* stream)
+{
+    if (group_ready == nullptr) return fail("gated grouped gemm: group_ready is null");
+    if (epilogue == kEpiScatterRows) return fail("gated grouped gemm: the scatter epilogue is not offered in this form");
+    g_group_trace  = static_cast<unsigned long long*>(group_trace);
+    g_tile_counter = static_cast<unsigned int*>(tile_counter);
+    const int rc = grouped_gemm_impl(A, B, C, group_offsets, num_groups, M_cap, N, K, lda, ldb, ldc, epilogue, nullptr, nullptr, 0, 0,
+                                     nullptr, static_cast<const unsigned long long*>(group_ready), group_ready_target,
+                                     static_cast<const unsigned long long*>(group_ready_epoch), status, stream);
+    g_group_trace  = nullptr;
+    g_tile_counter = nullptr;
+    return rc;
+}
+
+static int grouped_gemm_impl(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                            int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                            const void* row_info, const unsigned long long* scatter_bases8,
+                            unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
+                            const float* row_scale, const unsigned long long* group_ready,
+                            unsigned long long group_ready_target, const unsigned long long* group_ready_epoch,
+                            void* status, void* stream)
+{
     if (check_common(M_cap, N, K, lda, ldb)) return -1;
     if (num_groups <= 0 || group_offsets == nullptr) return fail("grouped gemm: need group offsets");
     Args a{};
+    a.group_ready        = group_ready;
+    a.group_ready_target = group_ready_target;
+    a.group_ready_epoch  = group_ready_epoch;
+    a.group_trace        = g_group_trace;
+    a.tile_counter       = g_tile_counter;
     a.M_total       = M_cap;
     a.N             = N;
     a.K             = K;

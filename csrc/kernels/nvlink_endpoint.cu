@@ -11,6 +11,7 @@
 // Aligned units move as 16-byte vectors with eight loads in flight per thread;
 // ragged heads and tails fall back to bytes.
 #include <algorithm>
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <string>
@@ -295,14 +296,29 @@ int ensure_staging(Endpoint* ep)
 
 // Work unit of the batched kernels. 64 KiB by default; SLIME_NVLINK_UNIT_KB (16 .. 1024, a multiple of 16) overrides
 // it, e.g. 16 so that four CTAs work on each 64 KiB piece at the same time.
+std::atomic<unsigned long long> g_unit_bytes{0};  // 0 = not decided yet
+std::atomic<int>                g_bulk{-1};       // -1 = not decided yet
+
 unsigned long long unit_bytes_setting()
 {
-    static const unsigned long long v = [] {
+    unsigned long long v = g_unit_bytes.load(std::memory_order_relaxed);
+    if (v == 0) {
         const char* raw = std::getenv("SLIME_NVLINK_UNIT_KB");
         const long  kb  = raw ? std::strtol(raw, nullptr, 10) : 0;
-        return (kb >= 16 && kb <= 1024 && kb % 16 == 0) ? static_cast<unsigned long long>(kb) << 10 : kUnitBytes;
-    }();
+        v = (kb >= 16 && kb <= 1024 && kb % 16 == 0) ? static_cast<unsigned long long>(kb) << 10 : kUnitBytes;
+        g_unit_bytes.store(v, std::memory_order_relaxed);
+    }
     return v;
+}
+
+bool bulk_setting()
+{
+    int v = g_bulk.load(std::memory_order_relaxed);
+    if (v < 0) {
+        v = std::getenv("SLIME_NVLINK_NO_BULK") == nullptr ? 1 : 0;
+        g_bulk.store(v, std::memory_order_relaxed);
+    }
+    return v != 0;
 }
 
 int ensure_slot(StagingSlot& s)
@@ -481,6 +497,20 @@ int slime_nvlink_ep_status_clear(void* h)
     return 0;
 }
 
+// Tuning of the batched kernels for the whole process: unit_kb (16 .. 1024, a multiple of 16; 0 = leave) is the work
+// unit CTAs take from a batch, bulk (0 / 1; negative = leave) picks between the 256-thread load/store kernel and the
+// bulk-copy-engine kernel for batches that are 16-byte aligned throughout. The same as SLIME_NVLINK_UNIT_KB and
+// SLIME_NVLINK_NO_BULK, but changeable between calls (benchmarks sweep it).
+int slime_nvlink_ep_tune(int unit_kb, int bulk)
+{
+    if (unit_kb != 0) {
+        if (unit_kb < 16 || unit_kb > 1024 || unit_kb % 16 != 0) return fail("nvlink endpoint: unit of %d KiB not in [16, 1024] or not a multiple of 16", unit_kb);
+        g_unit_bytes.store(static_cast<unsigned long long>(unit_kb) << 10);
+    }
+    if (bulk >= 0) g_bulk.store(bulk ? 1 : 0);
+    return 0;
+}
+
 // Few, large pieces are a job for the copy engines: no SM is occupied, nothing is staged, and for one contiguous
 // region a DMA copy is a few percent faster than any kernel (it has no tail and no launch-shaped ramp). The kernels
 // take over where the copy engines lose: many pieces, each of which would cost one host call and one DMA set-up.
@@ -621,8 +651,7 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
             SLIME_CUDA_OK(cudaMemcpyAsync(slot->dev, slot->host, sizeof(Segment) * batch, cudaMemcpyHostToDevice, stream));
             a.table = slot->dev;
         }
-        static const bool bulk_off = std::getenv("SLIME_NVLINK_NO_BULK") != nullptr;
-        if (all_aligned && !bulk_off && units > 0) {
+        if (all_aligned && bulk_setting() && units > 0) {
             // three 64 KiB rings fit in one SM's shared memory
             constexpr int kBulkSmem = kBulkBufs * kBulkChunk;
             static bool   configured[64] = {false};  // the attribute belongs to the device's copy of the function

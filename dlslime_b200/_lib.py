@@ -44,6 +44,11 @@ _SIGNATURES = {
                                 c_longlong, c_int, c_void_p, c_void_p],
     "slime_gemm_bf16_gated": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                               c_void_p, c_int, c_ulonglong, c_int, c_void_p, c_void_p],
+    "slime_grouped_gemm_bf16_gated": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
+                                      c_longlong, c_longlong, c_int, c_void_p, c_ulonglong, c_void_p, c_void_p, c_void_p],
+    "slime_grouped_gemm_bf16_gated_traced": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
+                                             c_longlong, c_longlong, c_int, c_void_p, c_ulonglong, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_void_p],
     "slime_grouped_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
                                 c_longlong, c_longlong, c_int, c_void_p, c_void_p, c_ulonglong, c_ulonglong, c_void_p,
                                 c_void_p, c_void_p],

@@ -7,6 +7,11 @@ One forward step on every rank:
           -> grouped down GEMM whose epilogue stores rows into the token owners'
              combine buffers over NVLink -> gate-weighted reduction.
 
+``streamed=True`` runs the first half as three kernels at once (programmatic dependent launches in
+one stream): the rows are pushed expert by expert, the receive side expands an expert as soon as its rows from every rank
+have landed, and the gate/up GEMM's producer waits per expert group, so the tensor cores start on
+expert 0 while the later experts are still crossing NVLink.
+
 Expert weights are random N(0, 0.02) bf16 in the ``nn.Linear`` layout. The layer
 is the flagship workload of ``bench.py``; ``ref_moe_forward`` is its fp32 PyTorch
 oracle.
@@ -57,7 +62,7 @@ class ExpertParallelMoE:
 
     def __init__(self, cfg: MoEConfig, max_tokens: int, *, group=None, seed: int = 0, buffer: EpBuffer | None = None,
                  recv_cap: int | None = None, weights=None, thin_waits: bool = False,
-                 fuse_dequant: bool = False):
+                 fuse_dequant: bool = False, streamed: bool = False):
         self.cfg = cfg
         self.buf = buffer or EpBuffer(cfg.num_experts, cfg.topk, cfg.hidden, max_tokens, group=group, recv_cap=recv_cap)
         self.rank, self.world = self.buf.rank, self.buf.world
@@ -74,6 +79,14 @@ class ExpertParallelMoE:
         # default: with the raw tile next to the bf16 one the ring is 3 stages deep instead of 4 and the expansion sits
         # between the load and the MMA; measured on one GPU the gate/up GEMM takes 3.76 ms instead of 2.73 + 0.13 ms.
         self.fuse_dequant = fuse_dequant
+        # streamed: dispatch, receive and the gate/up GEMM run at the same time (see forward_streamed)
+        self.streamed = streamed and not fuse_dequant
+        # grid of the streamed form's push + receive kernel (0 = three blocks per SM; a multiple of 3)
+        import os
+
+        self.comm_blocks = int(os.environ.get("SLIME_EP_COMM_BLOCKS", "0"))
+        # words of the gated GEMM's dynamic tile scheduler (SLIME_EP_STATIC_TILES=1: every gridDim-th tile instead)
+        self._tile_counter = None if os.environ.get("SLIME_EP_STATIC_TILES") == "1" else torch.zeros(2, dtype=torch.int32, device=dev)
         cap = self.buf.recv_cap
         self.xd = torch.empty((cap, cfg.hidden), dtype=torch.bfloat16, device=dev)
         self.h = torch.empty((cap, cfg.intermediate), dtype=torch.bfloat16, device=dev)
@@ -122,8 +135,87 @@ class ExpertParallelMoE:
             do_signal = False
         self.buf.combine_reduce(out, T, epoch, do_signal=do_signal)
 
+    # -- streamed form: the pieces, so that a single-GPU test can interleave ranks on one stream ---------------------
+    def step_route_ordered(self, logits, T, epoch):
+        self.buf.route_ordered(logits, T, epoch, self.cfg.renormalize)
+
+    def step_layout(self, epoch):
+        self.buf.compute_layout(epoch)
+
+    def step_dispatch_ordered(self, x, epoch, max_blocks=0):
+        self.buf.dispatch_ordered(x, epoch, max_blocks=max_blocks)
+
+    def step_recv_gated(self, epoch, max_blocks=0):
+        self.buf.recv_dequant_gated(self.xd, epoch, max_blocks=max_blocks)
+
+    def step_gate_up_gated(self, epoch):
+        if epoch is None:
+            gemm.grouped_gemm_bf16_gated(self.xd, self.w_gate_up, self.buf.group_offsets, self.buf.group_ready,
+                                         step_ptr=self.buf.epoch_dev.data_ptr(), out=self.h, epilogue=gemm.EPI_SWIGLU,
+                                         trace=self.buf.group_trace, tile_counter=self._tile_counter)
+        else:
+            gemm.grouped_gemm_bf16_gated(self.xd, self.w_gate_up, self.buf.group_offsets, self.buf.group_ready,
+                                         step=epoch, out=self.h, epilogue=gemm.EPI_SWIGLU, trace=self.buf.group_trace,
+                                         tile_counter=self._tile_counter)
+
+    def forward_streamed(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """The same layer with dispatch, receive and the gate/up GEMM overlapped.
+
+        Everything is launched into the caller's stream. The ordered push and the gated receive are ONE kernel (two
+        pushing blocks and one receiving block per SM); the gated GEMM behind it is its programmatic dependent: it may
+        start as soon as every block of that kernel is running, orders itself against the data with the ready words,
+        and does not complete before its predecessor has. So push, receive and GEMM share the device without a second
+        stream, and a kernel that waits can never keep the kernel it waits for from being scheduled.
+        """
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty_like(x)
+        self.buf.stage_quantised(x)
+        self.step_route_ordered(logits, T, None)
+        self.step_layout(None)
+        self.buf.stream_comm(T, self.xd, None, self.comm_blocks)
+        self.step_gate_up_gated(None)
+        self.step_down()
+        self.step_combine(out, T, None)
+        return out
+
+    def autotune(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor | None = None, steps: int = 4) -> dict:
+        """Pick the faster of the two forms of the first half (phases one after the other, or streamed) for this
+        shape and world size by running both, and keep it. Every rank must call this with its own inputs of the step
+        shape; the device times are combined as the maximum over ranks, so all ranks decide alike. Which form wins
+        depends on the regime: streaming hides the NVLink-bound push under compute-bound expert GEMMs (many ranks, many
+        rows per expert) and loses where the GEMMs stream weights from HBM and the extra traffic gets in their way.
+        """
+        import torch.distributed as dist
+
+        if self.fuse_dequant:
+            return {"streamed": False, "reason": "the fused-dequant GEMM has no streamed form"}
+        times = {}
+        for form in (False, True):
+            self.streamed = form
+            for _ in range(2):
+                self.forward(x, logits, out)
+            if dist.is_initialized():
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                self.forward(x, logits, out)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / steps], device=x.device, dtype=torch.float64)
+            if dist.is_initialized() and dist.get_world_size() > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times[form] = float(t.item())
+            self.buf.status.check()
+        self.streamed = times[True] < times[False]
+        return {"streamed": self.streamed, "serial_ms": round(times[False], 4), "streamed_ms": round(times[True], 4)}
+
     def forward(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """x [T, hidden] bf16, router logits [T, num_experts] fp32 -> [T, hidden] bf16."""
+        if self.streamed:
+            return self.forward_streamed(x, logits, out)
         T = x.shape[0]
         if out is None:
             out = torch.empty_like(x)
@@ -213,16 +305,29 @@ class TwoBatchOverlapMoE:
         self.b.buf.status.check()
 
 
-def emulated_forward(layers: list[ExpertParallelMoE], xs, logits):
-    """Run one step of a whole emulated group on one GPU, phase by phase."""
+def emulated_forward(layers: list[ExpertParallelMoE], xs, logits, streamed: bool = False):
+    """Run one step of a whole emulated group on one GPU, phase by phase (``streamed``: through the kernels of the
+    streamed form, one after the other on one stream, so every wait finds its word already set)."""
     outs = [torch.empty_like(x) for x in xs]
     epochs = [layer.buf.next_epoch() for layer in layers]
-    for layer, x, lg, e in zip(layers, xs, logits, epochs):
-        layer.step_route(lg, x.shape[0], e)
-    for layer, x, e in zip(layers, xs, epochs):
-        layer.step_dispatch(x, e)
-    for layer, x, e in zip(layers, xs, epochs):
-        layer.step_experts(x.shape[0], e)
+    if streamed:
+        for layer, x, lg, e in zip(layers, xs, logits, epochs):
+            layer.step_route_ordered(lg, x.shape[0], e)
+        for layer, e in zip(layers, epochs):
+            layer.step_layout(e)
+        for layer, x, e in zip(layers, xs, epochs):
+            layer.step_dispatch_ordered(x, e)
+        for layer, e in zip(layers, epochs):
+            layer.step_recv_gated(e)
+            layer.step_gate_up_gated(e)
+            layer.step_down()
+    else:
+        for layer, x, lg, e in zip(layers, xs, logits, epochs):
+            layer.step_route(lg, x.shape[0], e)
+        for layer, x, e in zip(layers, xs, epochs):
+            layer.step_dispatch(x, e)
+        for layer, x, e in zip(layers, xs, epochs):
+            layer.step_experts(x.shape[0], e)
     for layer, e in zip(layers, epochs):
         layer.buf.signal(1, e)
     for layer, x, out, e in zip(layers, xs, outs, epochs):

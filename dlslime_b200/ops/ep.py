@@ -18,7 +18,7 @@ from .. import _lib
 from ..parallel.symm import SymmetricHeap
 from ._common import default_status, ptr, stream_ptr
 
-_CFG_FMT = "<8i8Q8QQQQ"
+_CFG_FMT = "<8i8Q8QQQQQ"
 
 
 @dataclass
@@ -31,6 +31,7 @@ class EpLayout:
     off_scale: int
     off_info: int
     off_combine: int
+    off_arrive: int
     total: int
 
 
@@ -52,6 +53,7 @@ def ep_layout(world: int, num_experts: int, topk: int, hidden: int, max_tokens: 
         off_scale=take(recv_cap * (hidden // 128) * 4),
         off_info=take(recv_cap * 8),
         off_combine=take(max_tokens * topk * hidden * 2),
+        off_arrive=take(8 * world * (num_experts // world)),
         total=(cur + 255) // 256 * 256,
     )
 
@@ -103,6 +105,16 @@ class EpBuffer:
         self.send_count = torch.zeros(num_experts, dtype=torch.int32, device=dev)
         self.block_counters = torch.zeros(4, dtype=torch.int32, device=dev)
         self.group_offsets = torch.zeros(self.experts_per_rank + 1, dtype=torch.int32, device=dev)
+        # scratch of the streamed form (rows pushed expert by expert; see route_ordered / dispatch_ordered / recv_dequant_gated)
+        self.push_off = torch.zeros(num_experts + 1, dtype=torch.int32, device=dev)
+        self.perm = torch.zeros(max_tokens * topk, dtype=torch.int32, device=dev)
+        self.xq_stage = self.xs_stage = None  # tokens quantised once per step (allocated on first use)
+        # optional timing of the streamed form (enable_stream_trace): when each expert became ready, and when the
+        # GEMM's first CTA began to wait for / got each group
+        self.ready_time = self.group_trace = None
+        self.pushed = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self.deq_done = torch.zeros(self.experts_per_rank, dtype=torch.int32, device=dev)
+        self.group_ready = torch.zeros(self.experts_per_rank, dtype=torch.int64, device=dev)
         # Device-resident step counter for graph-replayable steps (methods called with epoch=None use it).
         self.epoch_dev = torch.zeros(1, dtype=torch.int64, device=dev)
         self.trace = None  # device trace page, see enable_device_trace
@@ -120,7 +132,7 @@ class EpBuffer:
             self.max_tokens, self.recv_cap,
             b + L.off_counts, b + L.off_dispatch_done, b + L.off_combine_done, b + L.off_barrier,
             b + L.off_x, b + L.off_scale, b + L.off_info, b + L.off_combine, *peers, self.wait_ns, epoch_ptr,
-            self.trace.data_ptr() if self.trace is not None else 0)
+            self.trace.data_ptr() if self.trace is not None else 0, b + L.off_arrive)
 
     # -- device trace ---------------------------------------------------------------
     _TRACE_KERNELS = ("dispatch", "receive", "combine", "wait", "barrier")
@@ -225,6 +237,66 @@ class EpBuffer:
                   ptr(self.group_offsets), self._bc1, e, max_blocks,
                   self.status.dev_ptr, stream_ptr())
 
+    # -- streamed form ------------------------------------------------------------------
+    def route_ordered(self, logits: torch.Tensor | None, T: int, epoch: int | None = None, renormalize: bool = False) -> None:
+        """``route`` that also lays out this rank's push order (expert by expert) for ``dispatch_ordered``."""
+        cfg, e = self._mode(epoch, first=True)
+        _lib.call("slime_ep_route_ordered", cfg, ptr(logits), T, ptr(self.topk_idx), ptr(self.topk_w), ptr(self.slot),
+                  ptr(self.send_count), self._bc0, e, int(renormalize), ptr(self.push_off), stream_ptr())
+
+    def compute_layout(self, epoch: int | None = None) -> None:
+        """One block that waits for every rank's counts and writes ``group_offsets``; lets the kernels that walk the
+        expert groups be launched without waiting for the dispatch kernel."""
+        cfg, e = self._mode(epoch)
+        _lib.call("slime_ep_layout", cfg, ptr(self.group_offsets), e, self.status.dev_ptr, stream_ptr())
+
+    def dispatch_ordered(self, x: torch.Tensor, epoch: int | None = None, max_blocks: int = 0) -> None:
+        """Quantise and push every (token, expert) row in push order; each completed (destination, expert) publishes
+        an arrival word on the destination."""
+        T = self._stage_quantised(x)
+        cfg, e = self._mode(epoch)
+        _lib.call("slime_ep_dispatch_ordered", cfg, ptr(self.xq_stage), ptr(self.xs_stage), T, ptr(self.topk_idx), ptr(self.slot),
+                  ptr(self.push_off), ptr(self.perm), ptr(self.pushed), e, max_blocks, self.status.dev_ptr, stream_ptr())
+
+    def _stage_quantised(self, x: torch.Tensor) -> int:
+        T = x.shape[0]
+        assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.shape[1] == self.hidden
+        if self.xq_stage is None:
+            self.xq_stage = torch.empty((self.max_tokens, self.hidden), dtype=torch.float8_e4m3fn, device=self.device)
+            self.xs_stage = torch.empty((self.max_tokens, self.hidden // 128), dtype=torch.float32, device=self.device)
+        # every token is quantised once, here; the push then only copies rows
+        _lib.call("slime_fp8_quant_1x128", ptr(x), ptr(self.xq_stage), ptr(self.xs_stage), T, self.hidden, x.stride(0),
+                  self.hidden, stream_ptr())
+        return T
+
+    def stage_quantised(self, x: torch.Tensor) -> None:
+        """Quantise this step's tokens into the local staging buffer (independent of routing, so it can run first)."""
+        self._stage_quantised(x)
+
+    def stream_comm(self, T: int, out: torch.Tensor, epoch: int | None = None, blocks: int = 0) -> None:
+        """Ordered push of the staged rows and gated receive into ``out`` as ONE kernel (two pushing blocks and one
+        receiving block per SM). The gated grouped GEMM launched next on the same stream starts beside it."""
+        cfg, e = self._mode(epoch)
+        _lib.call("slime_ep_stream_comm", cfg, ptr(self.xq_stage), ptr(self.xs_stage), T, ptr(self.topk_idx), ptr(self.slot),
+                  ptr(self.push_off), ptr(self.perm), ptr(self.pushed), ptr(self.group_offsets), ptr(out), out.stride(0),
+                  ptr(self.deq_done), ptr(self.group_ready), ptr(self.ready_time), e, blocks, self.status.dev_ptr, stream_ptr())
+
+    def recv_dequant_gated(self, out: torch.Tensor, epoch: int | None = None, max_blocks: int = 0) -> None:
+        """Per local expert: wait for its rows from every rank, expand them to bf16 ``out``, publish
+        ``group_ready[j]`` = step for the gated grouped GEMM."""
+        cfg, e = self._mode(epoch)
+        _lib.call("slime_ep_recv_dequant_gated_traced", cfg, ptr(self.group_offsets), ptr(out), out.stride(0), ptr(self.deq_done),
+                  ptr(self.group_ready), ptr(self.ready_time), e, max_blocks, self.status.dev_ptr, stream_ptr())
+
+    def enable_stream_trace(self, on: bool = True) -> None:
+        """Record, in device memory, when the gated receive published each expert (``ready_time`` [experts_per_rank],
+        ``globaltimer`` ns) and when the first CTA of the gated GEMM began to wait for and obtained each group
+        (``group_trace`` [experts_per_rank, 2]). Shows which of the two kernels waits for the other."""
+        epr = self.experts_per_rank
+        self.ready_time = torch.zeros(epr, dtype=torch.int64, device=self.device) if on else None
+        # [epr, 2] wait-start / ready per group, then one start time per CTA of the GEMM (up to 256 CTAs)
+        self.group_trace = torch.zeros(2 * epr + 256, dtype=torch.int64, device=self.device) if on else None
+
     def recv_dequant(self, out: torch.Tensor, epoch: int | None, expected_rows: int) -> None:
         """Wait for every rank's rows, then expand the packed fp8 rows to bf16 ``out`` [recv_cap, hidden]."""
         cfg, e = self._mode(epoch)
@@ -259,6 +331,12 @@ import ctypes as _ct  # noqa: E402
 _v, _i, _ll, _ull = _ct.c_void_p, _ct.c_int, _ct.c_longlong, _ct.c_ulonglong
 _lib.declare("slime_ep_route", [_ct.c_char_p, _v, _i, _v, _v, _v, _v, _v, _ull, _i, _v])
 _lib.declare("slime_ep_dispatch", [_ct.c_char_p, _v, _ll, _i, _v, _v, _v, _v, _ull, _i, _v, _v])
+_lib.declare("slime_ep_route_ordered", [_ct.c_char_p, _v, _i, _v, _v, _v, _v, _v, _ull, _i, _v, _v])
+_lib.declare("slime_ep_layout", [_ct.c_char_p, _v, _ull, _v, _v])
+_lib.declare("slime_ep_dispatch_ordered", [_ct.c_char_p, _v, _v, _i, _v, _v, _v, _v, _v, _ull, _i, _v, _v])
+_lib.declare("slime_ep_recv_dequant_gated", [_ct.c_char_p, _v, _v, _ll, _v, _v, _ull, _i, _v, _v])
+_lib.declare("slime_ep_stream_comm", [_ct.c_char_p, _v, _v, _i, _v, _v, _v, _v, _v, _v, _v, _ll, _v, _v, _v, _ull, _i, _v, _v])
+_lib.declare("slime_ep_recv_dequant_gated_traced", [_ct.c_char_p, _v, _v, _ll, _v, _v, _v, _ull, _i, _v, _v])
 _lib.declare("slime_ep_recv_dequant", [_ct.c_char_p, _v, _v, _ll, _i, _ull, _v, _v])
 _lib.declare("slime_ep_combine_push", [_ct.c_char_p, _v, _ll, _v, _i, _v, _v])
 _lib.declare("slime_ep_signal", [_ct.c_char_p, _i, _ull, _v])

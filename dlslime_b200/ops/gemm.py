@@ -77,6 +77,32 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
     return out
 
 
+def grouped_gemm_bf16_gated(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor, group_ready: torch.Tensor,
+                            *, step: int = 0, step_ptr: int = 0, out: torch.Tensor | None = None,
+                            epilogue: int = EPI_STORE, trace: torch.Tensor | None = None,
+                            tile_counter: torch.Tensor | None = None) -> torch.Tensor:
+    """:func:`grouped_gemm_bf16` (store and SwiGLU epilogues) over groups that are still being filled while the kernel
+    runs: the rows of group ``g`` are read once ``group_ready[g] >= step`` (int64 device tensor, one word per group).
+    ``step_ptr`` (a device address holding the step number) replaces ``step`` for graph-replayable steps. The kernel
+    that fills the rows must be launched first (in front of this one in the stream; this kernel is launched as its
+    programmatic dependent). ``trace`` (int64 [G, 2]) receives when the first CTA began to wait for / obtained each group.
+    ``tile_counter`` (int32 [2], zeros; the kernel leaves it zero) switches the CTAs from every gridDim-th tile to a
+    shared tile counter, which keeps a CTA that shares its SM with the filling kernel from holding the others up."""
+    require_cuda(a, b, group_offsets, group_ready)
+    assert a.dtype == b.dtype == torch.bfloat16 and group_offsets.dtype == torch.int32 and group_ready.dtype == torch.int64
+    assert a.stride(1) == 1 and b.is_contiguous() and b.dim() == 3 and epilogue in (EPI_STORE, EPI_SWIGLU)
+    g, rows_b, k = b.shape
+    m_cap = a.shape[0]
+    n = rows_b // 2 if epilogue == EPI_SWIGLU else rows_b
+    assert group_offsets.numel() == g + 1 and a.shape[1] == k and group_ready.numel() >= g
+    if out is None:
+        out = torch.empty((m_cap, n), dtype=torch.bfloat16, device=a.device)
+    _lib.call("slime_grouped_gemm_bf16_gated_traced", ptr(a), ptr(b), ptr(out), ptr(group_offsets), g, m_cap, n, k, a.stride(0), k,
+              out.stride(0), epilogue, ptr(group_ready), int(step), step_ptr or None, ptr(trace), ptr(tile_counter),
+              default_status().dev_ptr, stream_ptr())
+    return out
+
+
 def grouped_gemm_fp8a(aq: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor,
                       out: torch.Tensor | None = None, epilogue: int = EPI_STORE) -> torch.Tensor:
     """The grouped GEMM with the activations still in their wire format: ``aq [M_cap, K]`` e4m3 and ``a_scale

@@ -40,10 +40,18 @@ _lib.declare("slime_nvlink_ep_handle", [_v, _cp, _i])
 _lib.declare("slime_nvlink_ep_transfer", [_v, _v, _i, _i, _v, _ull, _i, _i, _v])
 _lib.declare("slime_nvlink_ep_status", [_v, ctypes.POINTER(ctypes.c_uint)])
 _lib.declare("slime_nvlink_ep_status_clear", [_v])
+_lib.declare("slime_nvlink_ep_tune", [_i, _i])
 _ll = ctypes.c_longlong
 _lib.declare("slime_nvlink_ep_copy1", [_v, _ll, _ll, _ull, _ull, _ull, _i, _v, _ull, _v])
 
 IMM_RING = 1024  # immediate values a peer may have outstanding before the receiver consumes them
+
+
+def tune(unit_kb: int = 0, bulk: int = -1) -> None:
+    """Process-wide tuning of the batched transfer kernels: ``unit_kb`` is the work unit CTAs take from a batch (16 ..
+    1024 KiB, default 64; smaller units put several CTAs on one piece at the same time), ``bulk`` picks the
+    bulk-copy-engine kernel (1) or the load/store kernel (0) for batches that are 16-byte aligned throughout."""
+    _lib.call("slime_nvlink_ep_tune", int(unit_kb), int(bulk))
 
 
 class NVLinkFuture:

@@ -157,6 +157,35 @@ def check_moe(rank, world):
     dist.barrier()
 
 
+def check_moe_streamed(rank, world):
+    """The streamed form (ordered push, per-expert arrival words, gated receive and GEMM as programmatic dependents) on
+    real ranks: bit-equal to the regular form on the same inputs, steps of both forms mixed."""
+    from dlslime_b200.models.moe import ExpertParallelMoE, MoEConfig, init_expert_weights, ref_moe_forward
+
+    cfg = MoEConfig(num_experts=32, topk=4, hidden=1024, intermediate=256)
+    w = init_expert_weights(cfg, range(rank * (32 // world), (rank + 1) * (32 // world)), "cuda", seed=7)
+    plain = ExpertParallelMoE(cfg, max_tokens=256, weights=w)
+    fast = ExpertParallelMoE(cfg, max_tokens=256, weights=w, streamed=True)
+    w13, w2 = init_expert_weights(cfg, range(cfg.num_experts), "cuda", seed=7)
+    for step in range(5):
+        T = [200, 1, 256, 33, 64, 128, 17, 255][(rank + step) % 8]
+        gen = torch.Generator(device="cuda").manual_seed(3000 * step + rank)
+        x = torch.randn((T, cfg.hidden), generator=gen, device="cuda").to(torch.bfloat16)
+        lg = torch.randn((T, cfg.num_experts), generator=gen, device="cuda")
+        a = plain(x, lg)
+        b = fast(x, lg)
+        if step == 3:
+            b = fast(x, lg)  # twice in a row, no host synchronisation between the steps
+        torch.cuda.synchronize()
+        fast.buf.status.check()
+        assert torch.equal(a, b), f"rank {rank} step {step}: streamed and regular forms differ"
+        ref, idx, _ = ref_moe_forward(cfg, x, lg, w13, w2)
+        err = (b.float() - ref.float()).abs()
+        tol = ref.float().abs() * 2 ** -6 + ref.float().abs().mean() * 2 ** -5
+        assert (err <= tol).all(), f"rank {rank} step {step}: max err {err.max().item()}"
+    dist.barrier()
+
+
 def check_moe_tbo(rank, world):
     """Two half-batches on two streams: same results as the fp32 oracle, for token counts that split unevenly."""
     from dlslime_b200.models.moe import MoEConfig, TwoBatchOverlapMoE, init_expert_weights, ref_moe_forward
@@ -265,7 +294,7 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    which = sys.argv[1:] or ["endpoint", "allgather", "alltoall", "moe", "moe_tbo", "ag_gemm", "ag_gemm_fp8", "kv"]
+    which = sys.argv[1:] or ["endpoint", "allgather", "alltoall", "moe", "moe_streamed", "moe_tbo", "ag_gemm", "ag_gemm_fp8", "kv"]
     for name in which:
         globals()[f"check_{name}"](rank, world)
         if rank == 0:
