@@ -182,7 +182,9 @@ def case_allgather(rank, world):
     from dlslime_b200.ops.allgather import AllGatherLLBuffer
 
     hidden = 7168
-    ag = AllGatherLLBuffer(1024, hidden, torch.bfloat16)
+    # SLIME_AG_MULTICAST = always | never | auto: multimem stores through the switch, plain peer stores, or by size
+    ag = AllGatherLLBuffer(1024, hidden, torch.bfloat16, multicast=None)
+    emit(rank, case="ll_allgather_setup", multicast_heap=bool(ag.use_multicast), policy=os.environ.get("SLIME_AG_MULTICAST", "auto"))
     for T in (1, 16, 128, 1024):
         x = torch.randn(T, hidden, device="cuda").to(torch.bfloat16)
         ref = torch.empty(world * T, hidden, device="cuda", dtype=torch.bfloat16)
@@ -213,7 +215,7 @@ def case_allgather(rank, world):
             if rank == 0:
                 print("graph timing skipped:", e, flush=True)
         nbytes = T * hidden * 2 * (world - 1)
-        emit(rank, case="ll_allgather", T=T, world=world, us=round(ms * 1e3, 2), nccl_us=round(base * 1e3, 2), speedup=round(base / ms, 2),
+        emit(rank, case="ll_allgather", multicast=bool(ag._through_multicast(T * hidden * 2)), T=T, world=world, us=round(ms * 1e3, 2), nccl_us=round(base * 1e3, 2), speedup=round(base / ms, 2),
              graph_us=round(g_ms * 1e3, 2), nccl_graph_us=round(g_base * 1e3, 2),
              recv_gbs_per_rank=round(nbytes / ms / 1e6, 1), frac_of_nvlink=round(nbytes / ms / 1e6 / NVLINK_GBS, 3))
 

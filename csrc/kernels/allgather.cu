@@ -7,6 +7,8 @@
 //          16-byte peer stores), then the last CTA publishes flags[half][rank] =
 //          step on every rank (release at system scope);
 //   wait   block until flags[half][r] >= step for every r (bounded).
+// When the buffer lives in a multicast-capable heap (symm_vmm.cu) the push is `multimem.st` to the multicast mapping:
+// every 16 bytes and the flag leave the GPU once and the NVSwitch delivers them to all ranks.
 // The gathered tensor is data[half] of the local buffer: no extra copy. The issue /
 // wait split is the `_hook` form of the reference's removed op
 // (AllGatherInterLLBuffer.all_gather_ll / all_gather_ll_hook,
@@ -30,6 +32,9 @@ struct AgConfig {
     // and stores the new value when its last CTA is done, wait passes 0), which makes a call replayable from
     // a CUDA graph.
     unsigned long long step_ptr;
+    // Address of the NVLink multicast mapping of the whole region (0 = none). When set, the push is ONE multimem
+    // store per 16 bytes, replicated by the switch into every rank's buffer, and the flag one multimem store too.
+    unsigned long long mc_base;
 };
 
 __global__ void __launch_bounds__(256) ag_push_kernel(AgConfig cfg, const uint4* __restrict__ src, unsigned long long nvec,
@@ -42,10 +47,25 @@ __global__ void __launch_bounds__(256) ag_push_kernel(AgConfig cfg, const uint4*
                                     + static_cast<unsigned long long>(cfg.rank) * stride_bytes;
     const unsigned long long tid    = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
-    for (unsigned long long i = tid; i < nvec; i += stride) {
-        const uint4 v = src[i];
+    if (cfg.mc_base != 0) {
+        // four independent loads in flight per thread; each value leaves this GPU once
+        uint4* mc = reinterpret_cast<uint4*>(cfg.mc_base + base);
+        unsigned long long i = tid;
+        for (; i + 3 * stride < nvec; i += 4 * stride) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = src[i + u * stride];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) multimem_st_v4(mc + i + u * stride, v[u]);
+        }
+        for (; i < nvec; i += stride) multimem_st_v4(mc + i, src[i]);
+    }
+    else {
+        for (unsigned long long i = tid; i < nvec; i += stride) {
+            const uint4 v = src[i];
 #pragma unroll 1
-        for (int p = 0; p < cfg.world; ++p) reinterpret_cast<uint4*>(cfg.peers[p] + base)[i] = v;
+            for (int p = 0; p < cfg.world; ++p) reinterpret_cast<uint4*>(cfg.peers[p] + base)[i] = v;
+        }
     }
     __shared__ bool is_last;
     __syncthreads();
@@ -56,7 +76,14 @@ __global__ void __launch_bounds__(256) ag_push_kernel(AgConfig cfg, const uint4*
     }
     __syncthreads();
     if (!is_last) return;
-    if (threadIdx.x < cfg.world) {
+    if (cfg.mc_base != 0) {
+        if (threadIdx.x == 0) {
+            fence_acq_rel_sys();
+            multimem_st_release_sys_u64(reinterpret_cast<unsigned long long*>(cfg.mc_base + cfg.off_flags) + half * cfg.world + cfg.rank, step);
+            *block_counter = 0;
+        }
+    }
+    else if (threadIdx.x < cfg.world) {
         fence_acq_rel_sys();
         unsigned long long* f = reinterpret_cast<unsigned long long*>(cfg.peers[threadIdx.x] + cfg.off_flags) + half * cfg.world + cfg.rank;
         st_release_sys(f, step);

@@ -201,6 +201,33 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned 
 }
 
 // ---------------------------------------------------------------------------
+// multimem: stores and reductions on an address of an NVLink multicast mapping. The NVSwitch replicates a
+// multimem.st into the memory every device bound at that offset (one store on the sender's links, whatever the
+// group size) and combines all replicas for a multimem.ld_reduce.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, const uint4& v)
+{
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+// One 64-bit word with release semantics at system scope, delivered to every replica: a flag behind multimem data.
+__device__ __forceinline__ void multimem_st_release_sys_u64(void* mc_addr, unsigned long long v)
+{
+    asm volatile("multimem.st.release.sys.global.u64 [%0], %1;" ::"l"(mc_addr), "l"(v) : "memory");
+}
+// Sum of the bf16x2 pairs of all replicas, eight bf16 at a time, accumulated in fp32 inside the switch.
+__device__ __forceinline__ uint4 multimem_ld_reduce_add_bf16x8(const void* mc_addr)
+{
+    uint4 r;
+    asm volatile("multimem.ld_reduce.weak.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(mc_addr)
+                 : "memory");
+    return r;
+}
+
+// ---------------------------------------------------------------------------
 // Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may start
 // while the kernel before it in the stream is still running, namely once every block of that kernel has executed
 // griddep_launch_dependents() or has exited, so all of them are running or done and cannot be starved by the

@@ -22,13 +22,13 @@ from ._common import default_status, ptr, stream_ptr
 _v, _i, _ull = ctypes.c_void_p, ctypes.c_int, ctypes.c_ulonglong
 _lib.declare("slime_ag_push", [ctypes.c_char_p, _v, _ull, _ull, _ull, _v, _i, _i, _v, _v])
 _lib.declare("slime_ag_wait", [ctypes.c_char_p, _ull, _v, _v])
-_CFG_FMT = "<2i3Q8QQQ"
+_CFG_FMT = "<2i3Q8QQQQ"
 
 
 class AllGatherLLBuffer:
     def __init__(self, max_bs: int, msg_size: int, dtype: torch.dtype, world_size: int | None = None,
                  rank: int | None = None, *, group=None, heap: SymmetricHeap | None = None, base_off: int | None = None,
-                 wait_ns: int = 0):
+                 wait_ns: int = 0, multicast: bool | None = None):
         self.dtype, self.msg_size, self.max_bs = dtype, msg_size, max_bs
         self.itemsize = torch.empty((), dtype=dtype).element_size()
         self.slot_bytes = (max_bs * msg_size * self.itemsize + 255) // 256 * 256
@@ -37,8 +37,19 @@ class AllGatherLLBuffer:
             import torch.distributed as dist
 
             world = dist.get_world_size(group) if dist.is_initialized() else 1
-            heap = SymmetricHeap(2 * world * self.slot_bytes + 4096, group=group)
+            # multicast=None: a multicast-capable heap where the group's GPUs offer one, else plain peer pointers
+            heap = SymmetricHeap(2 * world * self.slot_bytes + 4096, group=group, multicast=multicast)
         self.heap, self.world = heap, heap.world
+        self.use_multicast = bool(getattr(heap, "mc_ptr", 0)) and multicast is not False
+        # Which calls go through the multicast mapping. A multimem store leaves the GPU once instead of once per peer,
+        # but the switch also delivers it to the sender's own region, over the sender's own links: small messages,
+        # which are bound by the number of stores issued, win; large ones, which are bound by what every rank has to
+        # receive, pay world / (world - 1) and lose. SLIME_AG_MULTICAST = always | never | auto (default: groups of
+        # four or more ranks, contributions up to SLIME_AG_MULTICAST_MAX_BYTES = 4 MiB).
+        import os
+
+        self._mc_policy = os.environ.get("SLIME_AG_MULTICAST", "auto")
+        self._mc_max_bytes = int(os.environ.get("SLIME_AG_MULTICAST_MAX_BYTES", str(4 << 20)))
         self.rank = heap.rank if rank is None else rank
         assert world is None or world == self.world
         total = 2 * self.world * self.slot_bytes + 4096
@@ -53,13 +64,15 @@ class AllGatherLLBuffer:
         self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")
         self._counter_ptr = self.counter.data_ptr()
         self.status = default_status()
-        self._cfg = self._pack()
+        self._cfg = self._pack(False)
+        self._cfg_mc = self._pack(True) if self.use_multicast else None
         self._views: dict = {}
 
-    def _pack(self) -> bytes:
+    def _pack(self, with_mc: bool = False) -> bytes:
         peers = list(self.heap.peer_ptrs) + [0] * (8 - self.world)
+        mc = getattr(self.heap, "mc_ptr", 0) if (with_mc and self.use_multicast) else 0
         return struct.pack(_CFG_FMT, self.rank, self.world, self.off_data, self.off_flags, self.slot_bytes, *peers, self.wait_ns,
-                           self.step_dev.data_ptr())
+                           self.step_dev.data_ptr(), mc)
 
     @classmethod
     def emulated_group(cls, world: int, max_bs: int, msg_size: int, dtype: torch.dtype, wait_ns: int = 0):
@@ -73,7 +86,7 @@ class AllGatherLLBuffer:
 
     def connect_full_mesh(self, infos) -> None:
         self.heap.connect(infos)
-        self._cfg = self._pack()
+        self._cfg = self._pack(False)
 
     def get_local_buffer(self) -> torch.Tensor:
         return self.heap.view(self.off_data, (2, self.world, self.slot_bytes), torch.uint8, rank=self.rank)
@@ -94,9 +107,17 @@ class AllGatherLLBuffer:
             raise ValueError(f"batch of {bs} exceeds max_bs={self.max_bs}")
         self.step += 1
         nbytes = x.numel() * self.itemsize
-        _lib.call("slime_ag_push", self._cfg, x.data_ptr(), nbytes, nbytes, 1, self._counter_ptr, int(do_wait),
+        cfg = self._cfg_mc if self._through_multicast(nbytes) else self._cfg
+        _lib.call("slime_ag_push", cfg, x.data_ptr(), nbytes, nbytes, 1, self._counter_ptr, int(do_wait),
                   max_blocks, self.status.dev_ptr, torch.cuda.current_stream().cuda_stream)
         return self.step, bs
+
+    def _through_multicast(self, nbytes: int) -> bool:
+        if self._cfg_mc is None or self._mc_policy == "never":
+            return False
+        if self._mc_policy == "always":
+            return True
+        return self.world >= 4 and nbytes <= self._mc_max_bytes
 
     def all_gather_ll(self, x: torch.Tensor) -> torch.Tensor:
         """Gather ``x`` [bs, msg_size] from every rank -> [world * bs, msg_size] (a view of the buffer).

@@ -103,6 +103,43 @@ def check_allgather(rank, world):
     dist.barrier()
 
 
+def check_allgather_multicast(rank, world):
+    """The same all-gather on a heap bound to an NVLink multicast object: the push is `multimem.st` (one store per 16
+    bytes for the whole group). Skipped, on every rank alike, where the GPUs offer no multicast. The heap is closed
+    (unmapped, unbound, released) before any rank leaves the check."""
+    from dlslime_b200.ops.allgather import AllGatherLLBuffer
+    from dlslime_b200.parallel.symm import SymmetricHeap
+
+    hidden = 7168
+    slot = (1024 * hidden * 2 + 255) // 256 * 256
+    heap = SymmetricHeap(2 * world * slot + 4096, multicast=None)
+    if not heap.mc_ptr:
+        if rank == 0:
+            print("multicast not available here; check skipped", flush=True)
+        heap.close()
+        dist.barrier()
+        return
+    try:
+        ag = AllGatherLLBuffer(1024, hidden, torch.bfloat16, heap=heap)
+        assert ag.use_multicast
+        ag._mc_policy = "always"  # every size through the multicast mapping, whatever the size policy would pick
+        # the multicast mapping really replicates: a word stored through it shows up in this rank's own region
+        for step, bs in enumerate([1, 16, 128, 1024, 16, 1, 1024, 128]):
+            x = torch.randn((bs, hidden), device="cuda").to(torch.bfloat16) + rank
+            ref = torch.empty((world * bs, hidden), dtype=torch.bfloat16, device="cuda")
+            dist.all_gather_into_tensor(ref, x)
+            out = ag.all_gather_ll(x) if step % 2 == 0 else ag.all_gather_ll_hook(x)()
+            torch.cuda.synchronize()
+            ag.status.check()
+            assert torch.equal(out, ref), f"multicast all-gather mismatch at bs={bs}"
+            dist.barrier()  # nobody starts the step after next (which reuses this half) while a peer still compares
+    finally:
+        torch.cuda.synchronize()
+        dist.barrier()
+        heap.close()
+        dist.barrier()
+
+
 def check_alltoall(rank, world):
     from dlslime_b200.ops.alltoall import AllToAllLLBuffer
 
@@ -294,7 +331,7 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    which = sys.argv[1:] or ["endpoint", "allgather", "alltoall", "moe", "moe_streamed", "moe_tbo", "ag_gemm", "ag_gemm_fp8", "kv"]
+    which = sys.argv[1:] or ["endpoint", "allgather", "allgather_multicast", "alltoall", "moe", "moe_streamed", "moe_tbo", "ag_gemm", "ag_gemm_fp8", "kv"]
     for name in which:
         globals()[f"check_{name}"](rank, world)
         if rank == 0:
