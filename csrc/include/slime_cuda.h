@@ -194,6 +194,8 @@ int slime_ag_wait(const void* cfg_bytes, unsigned long long step, void* status, 
 // ---- paged KV-cache transfer / pack / unpack (kv_transfer.cu) -----------------
 // Moves K and V of one layer for n_tasks pages between a token-major plane pair and a paged plane
 // pair (addresses as integers; the paged side may be peer memory). to_paged: token-major -> paged.
+// threads per CTA of the transfer kernel for the whole process (32 .. 256, a multiple of 32; default 256)
+int slime_kv_tune(int threads);
 int slime_kv_transfer(unsigned long long tok_k, unsigned long long tok_v, unsigned long long page_k,
                       unsigned long long page_v, const int* tok_off, const int* blk, const int* ntok, int n_tasks,
                       int page_tokens, unsigned long long row_bytes, unsigned long long tok_rows,

@@ -73,6 +73,23 @@ inline int make_tmap_2d(CUtensorMap* tm, const void* base, CUtensorMapDataType d
     return 0;
 }
 
+// For copy kernels that are meant to run beside the tensor-core GEMMs. A GEMM CTA needs almost all of an SM's shared
+// memory, and an SM can only change its split between L1 and shared memory while it is empty: a small kernel that
+// leaves the split at "mostly L1" keeps the GEMM's CTA off its SM until its last block there has left (seen as GEMM
+// CTAs starting hundreds of microseconds late). Asking for the largest shared-memory split costs a streaming copy
+// kernel nothing. Once per device and kernel.
+template<typename K>
+inline cudaError_t prefer_max_shared_carveout(K kernel, bool (&done)[64])
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess) done[dev] = true;
+    return e;
+}
+
 // Launches `kernel` so that it may start before the kernel in front of it in `stream` has finished (programmatic
 // dependent launch; see griddep_launch_dependents in ptx.cuh).
 template<typename... KArgs, typename... Args>

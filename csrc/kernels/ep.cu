@@ -1054,13 +1054,7 @@ int slime_ep_stream_comm(const void* cfg_bytes, const void* xq, const float* xs,
     // split between L1 and shared memory while it is empty, so this kernel asks for the largest shared-memory split
     // itself: the GEMM's CTA then fits beside the resident blocks instead of waiting for them to leave.
     static bool carveout_set[64] = {false};
-    int         dev = 0;
-    SLIME_CUDA_OK(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !carveout_set[dev]) {
-        SLIME_CUDA_OK(cudaFuncSetAttribute(ep_stream_comm_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                           cudaSharedmemCarveoutMaxShared));
-        carveout_set[dev] = true;
-    }
+    SLIME_CUDA_OK(prefer_max_shared_carveout(ep_stream_comm_kernel, carveout_set));
     ep_stream_comm_kernel<<<blocks, 256, 0, s>>>(cfg, static_cast<const uint8_t*>(xq), xs, T, topk_idx, slot, perm, push_off, pushed,
                                                  group_offsets, static_cast<__nv_bfloat16*>(y), ldy, deq_done, ready, ready_time,
                                                  epoch, static_cast<KernelStatus*>(status));

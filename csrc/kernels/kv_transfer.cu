@@ -63,15 +63,16 @@ __global__ void __launch_bounds__(256) kv_transfer_kernel(KvArgs a)
         const uint4* src = reinterpret_cast<const uint4*>(a.to_paged ? tok_addr : page_addr);
         uint4*       dst = reinterpret_cast<uint4*>(a.to_paged ? page_addr : tok_addr);
         const unsigned long long nv = static_cast<unsigned long long>(n) * a.row_bytes / 16;
+        const unsigned long long nt = blockDim.x;
         unsigned long long       i  = threadIdx.x;
-        for (; i + 7ull * 256 < nv; i += 8ull * 256) {
+        for (; i + 7ull * nt < nv; i += 8ull * nt) {
             uint4 v[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = src[i + j * 256];
+            for (int j = 0; j < 8; ++j) v[j] = src[i + j * nt];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) dst[i + j * 256] = v[j];
+            for (int j = 0; j < 8; ++j) dst[i + j * nt] = v[j];
         }
-        for (; i < nv; i += 256) dst[i] = src[i];
+        for (; i < nv; i += nt) dst[i] = src[i];
     }
     if (a.done_flag != nullptr) {
         __shared__ bool is_last;
@@ -88,9 +89,21 @@ __global__ void __launch_bounds__(256) kv_transfer_kernel(KvArgs a)
     }
 }
 
+int g_kv_threads = 256;
+
 }  // namespace
 
 extern "C" {
+
+// Threads per CTA of the transfer kernel (32 .. 256, a multiple of 32; default 256) for the whole process. A transfer
+// that runs beside a GEMM is best spread thin: one small CTA on every SM slows every GEMM CTA a little, a few large
+// CTAs slow a few GEMM CTAs a lot, and the GEMM ends with its slowest CTA.
+int slime_kv_tune(int threads)
+{
+    if (threads < 32 || threads > 256 || threads % 32 != 0) return fail("kv transfer: %d threads per CTA not in [32, 256] or not a multiple of 32", threads);
+    g_kv_threads = threads;
+    return 0;
+}
 
 int slime_kv_transfer(unsigned long long tok_k, unsigned long long tok_v, unsigned long long page_k,
                       unsigned long long page_v, const int* tok_off, const int* blk, const int* ntok, int n_tasks,
@@ -115,7 +128,9 @@ int slime_kv_transfer(unsigned long long tok_k, unsigned long long tok_v, unsign
     const long long cap = max_blocks > 0 ? max_blocks : sm_count() * 4;
     if (grid > cap) grid = cap;
     if (grid < 1) grid = 1;
-    kv_transfer_kernel<<<static_cast<int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    static bool carveout[64] = {false};  // runs beside the prefill GEMMs: see prefer_max_shared_carveout
+    SLIME_CUDA_OK(prefer_max_shared_carveout(kv_transfer_kernel, carveout));
+    kv_transfer_kernel<<<static_cast<int>(grid), g_kv_threads, 0, static_cast<cudaStream_t>(stream)>>>(a);
     SLIME_CUDA_OK(cudaGetLastError());
     return 0;
 }

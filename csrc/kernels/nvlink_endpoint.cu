@@ -658,6 +658,8 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
             const int     dev_slot = ep->device >= 0 && ep->device < 64 ? ep->device : 0;
             if (!configured[dev_slot]) {
                 SLIME_CUDA_OK(cudaFuncSetAttribute(p2p_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmem));
+                SLIME_CUDA_OK(cudaFuncSetAttribute(p2p_bulk_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                                   cudaSharedmemCarveoutMaxShared));  // see prefer_max_shared_carveout
                 configured[dev_slot] = true;
             }
             long long grid = static_cast<long long>(std::min<unsigned long long>(units, static_cast<unsigned long long>(sm_count()) * 3));
@@ -668,6 +670,8 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
             long long grid = static_cast<long long>(std::min<unsigned long long>(units, static_cast<unsigned long long>(sm_count()) * 8));
             if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
             if (grid < 1) grid = 1;
+            static bool carveout[64] = {false};  // transfers run beside compute kernels: see prefer_max_shared_carveout
+            SLIME_CUDA_OK(prefer_max_shared_carveout(p2p_scatter_gather_kernel, carveout));
             p2p_scatter_gather_kernel<<<static_cast<int>(grid), kThreads, 0, stream>>>(a, inl);
         }
         SLIME_CUDA_OK(cudaGetLastError());

@@ -163,6 +163,22 @@ int slime_ipc_get_handle(const void* ptr, unsigned char* ipc_handle_out64, unsig
             range_fn = reinterpret_cast<RangeFn>(p);
     }
     if (!range_fn) return fail("cuMemGetAddressRange entry point not available");
+    // The export must run with the device that owns the memory current; callers (agent threads, for one) may have
+    // another device current, so the owner is looked up and made current for the two calls.
+    int                   cur = 0, owner = -1;
+    cudaPointerAttributes attr{};
+    SLIME_CUDA_OK(cudaGetDevice(&cur));
+    if (cudaPointerGetAttributes(&attr, ptr) == cudaSuccess && attr.type == cudaMemoryTypeDevice) owner = attr.device;
+    cudaGetLastError();
+    struct Restore {
+        int dev;
+        bool on;
+        ~Restore() { if (on) cudaSetDevice(dev); }
+    } restore{cur, false};
+    if (owner >= 0 && owner != cur) {
+        SLIME_CUDA_OK(cudaSetDevice(owner));
+        restore.on = true;
+    }
     CUdeviceptr base = 0;
     size_t      size = 0;
     CUresult    r    = range_fn(&base, &size, reinterpret_cast<CUdeviceptr>(ptr));

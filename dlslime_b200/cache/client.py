@@ -139,6 +139,8 @@ class CacheClient:
         """Connect a PeerAgent to the service's; returns the service's description. Idempotent per client."""
         info = self.server_peer_agent()
         self.peer_agent = self._agent_for(info, peer_agent, alias=alias, ctrl=ctrl, scope=scope, device=local_device)
+        if peer_device is None and str(link_type or "").lower() == "nvlink" and str(info.get("device") or "").startswith("cuda"):
+            peer_device = info["device"]  # the GPU that holds the slabs, not just any GPU the service's host lists
         link = self.peer_agent.connect_to(str(info["peer_agent_id"]), local_device=local_device, peer_device=peer_device,
                                           ib_port=ib_port, qp_num=qp_num, link_type=link_type)
         link.wait(timeout=timeout_sec)

@@ -80,8 +80,10 @@ class PagedKVCache:
 class PrefillSender:
     """Prefill side: per-layer push of a batch's KV pages into a decode rank's paged cache."""
 
-    def __init__(self, shape: KVShape, dst_cache: PagedKVCache, max_tokens: int, comm_blocks: int = 32):
+    def __init__(self, shape: KVShape, dst_cache: PagedKVCache, max_tokens: int, comm_blocks: int = 32, comm_threads: int = 256):
         self.shape, self.dst, self.max_tokens = shape, dst_cache, max_tokens
+        if comm_threads != 256:
+            kv.tune(comm_threads)
         self.kv_stage = torch.empty((shape.layers, 2, max_tokens, shape.row), dtype=shape.dtype, device="cuda")
         self.comm_stream = torch.cuda.Stream(priority=-1)  # transfer CTAs should be placed ahead of the next GEMM's
         self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")

@@ -43,6 +43,12 @@ def build_page_tasks(prompt_lens, page_tokens: int, dst_blocks, src_starts=None,
     return mk(tok_off), mk(dst_blocks), mk(ntok)
 
 
+def tune(threads: int) -> None:
+    """Threads per CTA of the transfer kernel for the whole process (32 .. 256). With ``max_blocks`` = one CTA per SM and
+    64 threads a transfer that runs beside a GEMM is spread evenly over the SMs instead of slowing a few of them."""
+    _lib.call("slime_kv_tune", int(threads))
+
+
 def kv_move(tok_k: int, tok_v: int, page_k: int, page_v: int, tok_off: torch.Tensor, blk: torch.Tensor,
             ntok: torch.Tensor | None, *, page_tokens: int, row_bytes: int, tok_rows: int, page_blocks: int,
             to_paged: bool = True, done_flag: int | None = None, done_value: int = 0, counter: torch.Tensor | None = None,

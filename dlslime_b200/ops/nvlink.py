@@ -82,12 +82,16 @@ class NVLinkFuture:
         t0 = time.monotonic()
         polls = 0
         while not self.done():
-            if timeout is not None and time.monotonic() - t0 > timeout:
-                return 402
             polls += 1
-            if self._status is not None and polls % 1024 == 0 and self._status() != 0:
+            if polls % 64:
+                continue  # a tight poll of the mapped word: small transfers complete within microseconds
+            now = time.monotonic()
+            if timeout is not None and now - t0 > timeout:
+                return 402
+            if self._status is not None and polls % 4096 == 0 and self._status() != 0:
                 return 402  # a copy of this endpoint gave up: its completion word was withheld
-            time.sleep(0)
+            if now - t0 > 200e-6:
+                time.sleep(0)  # long transfer: let other threads of the process run between polls
         return 0
 
 

@@ -43,47 +43,72 @@ def _norm_link(link: Optional[str]) -> Optional[str]:
 
 
 class _NVLinkAdapter:
-    """Gives the kernel-driven NVLink endpoint the method names the agent uses for every transport."""
+    """Gives the kernel-driven NVLink endpoint the method names the agent uses for every transport.
 
-    def __init__(self):
+    Every call runs with the agent's GPU as the current CUDA device: the agent creates and connects endpoints from its
+    own threads (executor, mailbox), where the current device is whatever the process default is, and an endpoint whose
+    mailbox, IPC export or copy kernels end up on another GPU than its regions does not work.
+    """
+
+    def __init__(self, device_index: int | None = None):
+        import torch
+
         from ..ops.nvlink import NVLinkEndpoint
 
-        self.ep = NVLinkEndpoint()
+        self._torch = torch
+        self.device_index = torch.cuda.current_device() if device_index is None else int(device_index)
+        with torch.cuda.device(self.device_index):
+            self.ep = NVLinkEndpoint()
+
+    def _on_device(self):
+        return self._torch.cuda.device(self.device_index)
 
     def kind(self):
         return "nvlink"
 
     def register_memory_region(self, name, ptr, offset, length):
-        return self.ep.register_memory_region(ptr, offset, length, name)
+        with self._on_device():
+            return self.ep.register_memory_region(ptr, offset, length, name)
 
     def register_remote_memory_region(self, name, info):
-        return self.ep.register_remote_memory_region(info, name)
+        with self._on_device():
+            return self.ep.register_remote_memory_region(info, name)
 
     def get_mr_handle(self, name):
         return self.ep.get_mr_handle(name)
 
+    def get_remote_mr_handle(self, name):
+        return self.ep.get_remote_mr_handle(name)
+
     def mr_info(self):
-        return self.ep.mr_info()
+        with self._on_device():
+            return self.ep.mr_info()
 
     def endpoint_info(self):
-        info = self.ep.endpoint_info()
+        with self._on_device():
+            info = self.ep.endpoint_info()
         info["kind"] = "nvlink"
         return info
 
     def connect(self, info):
-        return self.ep.connect(info)
+        with self._on_device():
+            return self.ep.connect(info)
 
     def read(self, assign, stream=None):
-        return self.ep.read(assign, stream)
+        with self._on_device():
+            return self.ep.read(assign, stream)
 
     def write(self, assign, stream=None):
-        return self.ep.write(assign, stream)
+        with self._on_device():
+            return self.ep.write(assign, stream)
 
     def write_with_imm(self, assign, imm_data=0, stream=None):
-        return self.ep.write_with_imm(assign, imm_data, stream)
+        with self._on_device():
+            return self.ep.write_with_imm(assign, imm_data, stream)
 
     def imm_recv(self, stream=None):
-        return self.ep.imm_recv()
+        with self._on_device():
+            return self.ep.imm_recv()
 
     def send(self, chunk, stream=None):
         raise NotImplementedError("two-sided send over NVLink: use write_with_imm / imm_recv")
@@ -91,7 +116,8 @@ class _NVLinkAdapter:
     recv = send
 
     def shutdown(self):
-        self.ep.close()
+        with self._on_device():
+            self.ep.close()
 
     def cancel_all(self):
         pass
@@ -381,7 +407,8 @@ class PeerAgent:
             ep = _slime_c.TcpEndpoint(self._bind_host, 0, conn.qp_num)
             ep.set_pool(self._pool_for(conn.local_key))
         elif link == "NVLink":
-            ep = _NVLinkAdapter()
+            dev = conn.local_key.device or self._preferred_device or ""
+            ep = _NVLinkAdapter(int(dev.split(":")[1]) if dev.startswith("cuda:") else None)
             with self._regions_lock:
                 for r in self._logical_regions.values():
                     ep.register_memory_region(r.name, r.ptr, r.offset, r.length)
