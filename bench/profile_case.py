@@ -12,6 +12,9 @@
     python bench/profile_case.py kv          # paged KV pack + unpack, 4096 pages of 64 tokens x 512 B rows (K and V)
     python bench/profile_case.py allgather   # all-gather push of 1024 x 7168 bf16 to 4 emulated ranks on one GPU
     python bench/profile_case.py alltoall    # all-to-all of 4 x 512 x 7168 bf16 among 4 emulated ranks on one GPU
+    python bench/profile_case.py ag_gemm_fused      # fused all-gather -> GEMM of rank 0 in a group of 4 emulated ranks (CTA pairs)
+    python bench/profile_case.py ag_gemm_fp8_fused  # the same in block-scaled fp8
+    python bench/profile_case.py moe_stream  # MoE step, streamed form: push + receive kernel and the gated GEMM (T=1024, 32 experts)
 
 Each case holds well under 4 GB on the device and exits by itself in seconds.
 """
@@ -167,7 +170,59 @@ def alltoall_case():
     assert torch.equal(outs[1], torch.cat([x[bs:2 * bs] for x in xs], dim=0))
 
 
+def ag_gemm_fused_case():
+    """Rank 0's fused kernel in a group of four ranks that live on this one GPU: the other ranks push their shards with
+    the push-only kernel first, so every arrival counter the fused kernel waits for is already complete, while its own
+    push warps still copy rank 0's shard into all four regions beside the tensor-core tiles."""
+    from dlslime_b200.ops.ag_gemm import AllGatherGemm
+
+    world, rows, k, n = 4, 1024, 8192, 7168
+    group = AllGatherGemm.emulated_group(world, rows, k)
+    xs = [torch.randn(rows, k, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+    out = torch.empty(world * rows, n, device="cuda", dtype=torch.bfloat16)
+    for step in (1, 2, 3):
+        for g, x in zip(group[1:], xs[1:]):
+            g.push(x, step)
+        group[0]._call(3, xs[0], w, out, step)
+    torch.cuda.synchronize()
+    group[0].status.check()
+    ref = torch.cat(xs, 0)[:256].float() @ w.float().t()
+    assert ((out[:256].float() - ref).abs() <= ref.abs() * 2 ** -6 + ref.abs().mean() * 2 ** -6).all()
+
+
+def ag_gemm_fp8_fused_case():
+    from dlslime_b200.ops import quant
+    from dlslime_b200.ops.ag_gemm import AllGatherGemmFp8
+
+    world, rows, k, n = 4, 1024, 8192, 7168
+    group = AllGatherGemmFp8.emulated_group(world, rows, k)
+    xs = [quant.fp8_quant_1x128(torch.randn(rows, k, device="cuda").to(torch.bfloat16)) for _ in range(world)]
+    wq, sb = quant.fp8_quant_128x128((torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16))
+    out = torch.empty(world * rows, n, device="cuda", dtype=torch.bfloat16)
+    for step in (1, 2, 3):
+        for g, (xq, sx) in zip(group[1:], xs[1:]):
+            g.push(xq, sx, step)
+        group[0]._call(2, xs[0][0], xs[0][1], wq, sb, out, step)
+    torch.cuda.synchronize()
+    group[0].status.check()
+
+
+def moe_stream_case():
+    from dlslime_b200.models.moe import ExpertParallelMoE, MoEConfig
+
+    cfg = MoEConfig(num_experts=32, topk=8, hidden=7168, intermediate=2048)
+    layer = ExpertParallelMoE(cfg, max_tokens=1024, streamed=True)
+    x = torch.randn(1024, cfg.hidden, device="cuda").to(torch.bfloat16)
+    lg = torch.randn(1024, cfg.num_experts, device="cuda")
+    for _ in range(3):
+        layer(x, lg)
+    torch.cuda.synchronize()
+    layer.buf.status.check()
+
+
 if __name__ == "__main__":
-    {"alltoall": alltoall_case, "kv": kv_case, "allgather": allgather_case, "gemm": gemm_case, "gemm_pair": gemm_pair_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "grouped_stream": grouped_stream_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
+    {"ag_gemm_fused": ag_gemm_fused_case, "ag_gemm_fp8_fused": ag_gemm_fp8_fused_case, "moe_stream": moe_stream_case,
+     "alltoall": alltoall_case, "kv": kv_case, "allgather": allgather_case, "gemm": gemm_case, "gemm_pair": gemm_pair_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "grouped_stream": grouped_stream_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
     torch.cuda.synchronize()
     print("done", sys.argv[1])

@@ -12,9 +12,9 @@ Like the reference's backend (``dlslime/csrc/torch/slime_backend.h:105-208`` in 
 endpoint per peer at construction, exchanges their ``endpoint_info()`` through the c10d store (keys
 ``SLIME_ENDPOINT_<rank>_<peer>``), connects the full mesh, and implements ``send`` / ``recv`` only; every
 collective raises "not supported" (use NCCL or gloo for those, as pipeline-parallel users do). Differences:
-every tensor of the list is transferred (not just the first), ``wait(timeout)`` honours its timeout, and CUDA
-tensors are staged through pinned host memory because the transport underneath is the TCP endpoint (for
-GPU-to-GPU traffic inside a node the NVLink ops of this package are the fast path).
+every tensor of the list is transferred (not just the first) and ``wait(timeout)`` honours its timeout. CUDA tensors
+between GPUs of one host go device to device over NVLink (``torch_direct.py``: the receiver exports its tensor, the
+sender copies into it; no host bounce); other CUDA tensors are staged through pinned host memory.
 """
 
 from __future__ import annotations
@@ -213,9 +213,18 @@ def _create(store, rank, size, timeout):
     if implementation() == "cpp":
         mod, _ = _load_cpp()
         ms = int(timeout.total_seconds() * 1000) if isinstance(timeout, timedelta) else 300_000
-        return mod.create_backend(store, rank, size, ms, _slime_c.bridge_table(), os.environ.get("SLIME_BACKEND_TRANSPORT", ""),
-                                  "127.0.0.1")
-    return SlimeProcessGroup(store, rank, size, timeout)
+        inner = mod.create_backend(store, rank, size, ms, _slime_c.bridge_table(), os.environ.get("SLIME_BACKEND_TRANSPORT", ""),
+                                   "127.0.0.1")
+    else:
+        inner = SlimeProcessGroup(store, rank, size, timeout)
+    # CUDA tensors between GPUs of one host go device to device over NVLink (torch_direct.py); SLIME_BACKEND_DIRECT=off
+    # keeps every tensor on the staged path of the backend above
+    mode = os.environ.get("SLIME_BACKEND_DIRECT", "auto")
+    if mode == "off" or (mode == "auto" and not torch.cuda.is_available()):
+        return inner
+    from .torch_direct import DirectGroup
+
+    return DirectGroup(inner, store, rank, size, timeout if isinstance(timeout, timedelta) else None, mode=mode)
 
 
 def register() -> None:

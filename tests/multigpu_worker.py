@@ -287,6 +287,33 @@ def check_ag_gemm_fp8(rank, world):
         dist.barrier()
 
 
+def check_torch_backend(rank, world):
+    """CUDA tensors through a second process group of the "dlslime" backend: device to device between GPUs (pairs
+    r, r ^ 1), producer kernels in front of the send, consumer kernels behind the receive."""
+    import dlslime_b200.torch_backend  # noqa: F401  (registers the backend)
+
+    g = dist.new_group(backend="dlslime")
+    peer = rank ^ 1
+    if peer < world:
+        x = torch.randn(1 << 22, device="cuda") * (rank + 1)
+        y = torch.empty_like(x)
+        ws = [dist.isend(x, peer, group=g), dist.irecv(y, peer, group=g)]
+        ws[1].wait(), ws[0].wait()
+        z = y * 2  # consumer kernel right behind the receive
+        torch.cuda.synchronize()
+        sums = torch.stack([x.double().sum(), y.double().sum()]).float()
+        allsums = [torch.empty_like(sums) for _ in range(world)]
+        dist.all_gather(allsums, sums)  # NCCL, default group
+        assert abs(allsums[peer][0].item() - sums[1].item()) <= 1e-3 * max(1.0, abs(sums[1].item())), "payload differs from what the peer sent"
+        assert torch.allclose(z, y * 2)
+        pg = g if type(g).__name__ == "DirectGroup" else None
+        if pg is not None:
+            assert pg.counters["direct_sends"] >= 1 and pg.counters["staged_fallbacks"] == 0, pg.counters
+    else:
+        dist.all_gather([torch.empty(2, device="cuda") for _ in range(world)], torch.zeros(2, device="cuda"))
+    dist.barrier()
+
+
 def check_kv(rank, world):
     """Ranks [0, world/2) play prefill and push into the paged cache of rank + world/2."""
     from dlslime_b200.models.pd_kv import KVShape, PagedKVCache, PrefillSender, wait_layers
@@ -331,7 +358,7 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    which = sys.argv[1:] or ["endpoint", "allgather", "allgather_multicast", "alltoall", "moe", "moe_streamed", "moe_tbo", "ag_gemm", "ag_gemm_fp8", "kv"]
+    which = sys.argv[1:] or ["endpoint", "allgather", "allgather_multicast", "alltoall", "moe", "moe_streamed", "moe_tbo", "ag_gemm", "ag_gemm_fp8", "kv", "torch_backend"]
     for name in which:
         globals()[f"check_{name}"](rank, world)
         if rank == 0:

@@ -23,4 +23,4 @@ def _launch(n, *checks, timeout=600):
 def test_endpoint_allgather_moe_on_all_gpus():
     n = torch.cuda.device_count()
     n = 8 if n >= 8 else 4 if n >= 4 else 2
-    _launch(n, "endpoint", "allgather", "allgather_multicast", "alltoall", "moe", "moe_streamed", "moe_tbo", "ag_gemm", "ag_gemm_fp8", "kv")
+    _launch(n, "endpoint", "allgather", "allgather_multicast", "alltoall", "moe", "moe_streamed", "moe_tbo", "ag_gemm", "ag_gemm_fp8", "kv", "torch_backend")

@@ -44,7 +44,7 @@ def main():
         pg.recv(got, 0, 0).wait()
         pg.send(several, 0, 0).wait()
     assert torch.all(got[0] == float(peer)) and torch.all(got[1] == float(peer) + 0.5)
-    if "--cuda" in sys.argv:  # device tensors are staged through host memory; both ranks may share one GPU
+    if "--cuda" in sys.argv:  # device tensors go device to device (CUDA IPC); both ranks may share one GPU
         dev = torch.device("cuda", 0)
         x = torch.arange(4096, dtype=torch.float32, device=dev) * (rank + 1)
         y = torch.empty(4096, dtype=torch.float32, device=dev)
@@ -56,6 +56,28 @@ def main():
             dist.send(x, dst=0)
         torch.cuda.synchronize()
         assert torch.equal(y, torch.arange(4096, dtype=torch.float32, device=dev) * (peer + 1))
+        # a larger tensor produced by a kernel right before the send, and an exchange with both sends posted first
+        big = torch.randn(1 << 22, device=dev)
+        big.mul_(rank + 1.5)
+        back = torch.empty_like(big)
+        ws = [dist.isend(big, peer), dist.irecv(back, peer)]
+        ws[1].wait(), ws[0].wait()
+        torch.cuda.synchronize()
+        ref = [None, None]
+        ref[rank] = big
+        chk = torch.empty(2, device=dev)
+        chk[0], chk[1] = big.double().sum().float(), back.double().sum().float()
+        sums = chk.cpu().tolist()
+        other = torch.empty(2)
+        mine = torch.tensor(sums)
+        if rank == 0:
+            dist.send(mine, dst=1); dist.recv(other, src=1)
+        else:
+            dist.recv(other, src=0); dist.send(mine, dst=0)
+        assert abs(other[0].item() - sums[1]) <= 1e-3 * max(1.0, abs(sums[1])), "the received tensor is not what the peer sent"
+        if os.environ.get("SLIME_BACKEND_DIRECT", "auto") == "auto":
+            c = pg.counters
+            assert c["direct_sends"] >= 2 and c["direct_recvs"] >= 2 and c["staged_fallbacks"] == 0, c
     # wait(timeout) is honoured: a receive that nobody sends ends with status 402 instead of blocking
     import time
     from datetime import timedelta
