@@ -321,12 +321,20 @@ bool bulk_setting()
     return v != 0;
 }
 
-int ensure_slot(StagingSlot& s)
+// All staging slots are set up by the first batch that needs a table: one pinned block and one device block cut into
+// kStagingSlots tables. (Allocating slot by slot put a cudaHostAlloc and a cudaMalloc, both synchronous and
+// milliseconds long, into each of the first kStagingSlots large batches of an endpoint.)
+int ensure_slots(Endpoint* ep)
 {
-    if (s.host) return 0;
-    SLIME_CUDA_OK(cudaHostAlloc(reinterpret_cast<void**>(&s.host), sizeof(Segment) * kStagingEntries, cudaHostAllocPortable));
-    SLIME_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&s.dev), sizeof(Segment) * kStagingEntries));
-    SLIME_CUDA_OK(cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
+    if (ep->slots[0].host) return 0;
+    Segment *host = nullptr, *dev = nullptr;
+    SLIME_CUDA_OK(cudaHostAlloc(reinterpret_cast<void**>(&host), sizeof(Segment) * kStagingEntries * kStagingSlots, cudaHostAllocPortable));
+    SLIME_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&dev), sizeof(Segment) * kStagingEntries * kStagingSlots));
+    for (int i = 0; i < kStagingSlots; ++i) {
+        ep->slots[i].host = host + static_cast<size_t>(i) * kStagingEntries;
+        ep->slots[i].dev  = dev + static_cast<size_t>(i) * kStagingEntries;
+        SLIME_CUDA_OK(cudaEventCreateWithFlags(&ep->slots[i].done, cudaEventDisableTiming));
+    }
     return 0;
 }
 
@@ -344,11 +352,10 @@ int slime_nvlink_ep_destroy(void* h)
     Endpoint* ep = static_cast<Endpoint*>(h);
     if (!ep) return 0;
     for (auto& kv : ep->opened) cudaIpcCloseMemHandle(kv.second);
-    for (auto& s : ep->slots) {
-        if (s.host) cudaFreeHost(s.host);
-        if (s.dev) cudaFree(s.dev);
+    if (ep->slots[0].host) cudaFreeHost(ep->slots[0].host);  // one block each for all slots
+    if (ep->slots[0].dev) cudaFree(ep->slots[0].dev);
+    for (auto& s : ep->slots)
         if (s.done) cudaEventDestroy(s.done);
-    }
     if (ep->counters) cudaFree(ep->counters);
     if (ep->status_host) slime_status_free(ep->status_host);
     delete ep;
@@ -609,9 +616,9 @@ int slime_nvlink_ep_transfer(void* h, const unsigned long long* tuples, int n, i
             seg_out = inl.seg;
         }
         else {
+            if (ensure_slots(ep)) return -1;
             slot = &ep->slots[ep->next_slot];
             ep->next_slot = (ep->next_slot + 1) % kStagingSlots;
-            if (ensure_slot(*slot)) return -1;
             SLIME_CUDA_OK(cudaEventSynchronize(slot->done));  // previous user of this slot has been consumed
             seg_out = slot->host;
         }

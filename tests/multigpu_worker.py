@@ -290,14 +290,19 @@ def check_ag_gemm_fp8(rank, world):
 def check_torch_backend(rank, world):
     """CUDA tensors through a second process group of the "dlslime" backend: device to device between GPUs (pairs
     r, r ^ 1), producer kernels in front of the send, consumer kernels behind the receive."""
-    import dlslime_b200.torch_backend  # noqa: F401  (registers the backend)
+    from datetime import timedelta
 
-    g = dist.new_group(backend="dlslime")
+    from dlslime_b200 import torch_backend
+
+    # The group object is built the way init_process_group("dlslime") builds it, on a prefix of the default store.
+    # (dist.new_group cannot attach a Python process group to a default group that was bound to a device.)
+    store = dist.PrefixStore("slime_torch_backend_check", dist.distributed_c10d._get_default_store())
+    g = torch_backend._create(store, rank, world, timedelta(seconds=60))
     peer = rank ^ 1
     if peer < world:
         x = torch.randn(1 << 22, device="cuda") * (rank + 1)
         y = torch.empty_like(x)
-        ws = [dist.isend(x, peer, group=g), dist.irecv(y, peer, group=g)]
+        ws = [g.send([x], peer, 0), g.recv([y], peer, 0)]
         ws[1].wait(), ws[0].wait()
         z = y * 2  # consumer kernel right behind the receive
         torch.cuda.synchronize()
@@ -312,6 +317,7 @@ def check_torch_backend(rank, world):
     else:
         dist.all_gather([torch.empty(2, device="cuda") for _ in range(world)], torch.zeros(2, device="cuda"))
     dist.barrier()
+    g.shutdown()
 
 
 def check_kv(rank, world):
