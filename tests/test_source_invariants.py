@@ -60,3 +60,26 @@ def test_c_api_header_and_library_agree():
     assert len(names) > 40
     missing = [n for n in sorted(names) if not hasattr(lib, n)]
     assert not missing, missing
+
+
+def test_baseline_arms_import_nothing_of_the_package():
+    """The reference arm and the tuned arm of bench.py must not load this repository's package or libraries: their
+    modules import only the standard library, torch and each other, and bench.py imports the package inside run_ours
+    only."""
+    import ast
+
+    for name in ("reference_arm.py", "tuned_arm.py", "torch_moe.py"):
+        tree = ast.parse((ROOT / "baseline" / name).read_text())
+        for node in ast.walk(tree):
+            mods = []
+            if isinstance(node, ast.Import):
+                mods = [a.name for a in node.names]
+            elif isinstance(node, ast.ImportFrom):
+                mods = [node.module or ""]
+            assert not any(m.split(".")[0] == "dlslime_b200" for m in mods), (name, mods)
+    tree = ast.parse((ROOT / "bench.py").read_text())
+    for fn in [n for n in tree.body if isinstance(n, (ast.FunctionDef, ast.ClassDef))]:
+        uses = [n for n in ast.walk(fn) if isinstance(n, ast.ImportFrom) and (n.module or "").startswith("dlslime_b200")]
+        assert not uses or fn.name == "run_ours", fn.name
+    top = [n for n in tree.body if isinstance(n, (ast.Import, ast.ImportFrom))]
+    assert not any("dlslime_b200" in ast.dump(n) for n in top)
