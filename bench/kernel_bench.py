@@ -91,7 +91,12 @@ def cmd_grouped(a):
 
     hbm, tf, tag = peaks()
     g, rows, k, inter = a.experts, a.rows, 7168, 2048
-    offs = torch.arange(0, g + 1, dtype=torch.int32, device="cuda") * rows
+    if a.ragged:  # group sizes as a uniform router produces them: multinomial around the mean, same total
+        gen = torch.Generator().manual_seed(0)
+        sizes = torch.bincount(torch.randint(0, g, (g * rows,), generator=gen), minlength=g)
+        offs = torch.cat([torch.zeros(1, dtype=torch.long), sizes.cumsum(0)]).to(torch.int32).cuda()
+    else:
+        offs = torch.arange(0, g + 1, dtype=torch.int32, device="cuda") * rows
     x = torch.randn(g * rows, k, device="cuda").to(torch.bfloat16)
     w13 = (torch.randn(g, 2 * inter, k, device="cuda") * 0.02).to(torch.bfloat16)
     w2 = (torch.randn(g, k, inter, device="cuda") * 0.02).to(torch.bfloat16)
@@ -100,6 +105,8 @@ def cmd_grouped(a):
     f1, f2 = 2.0 * g * rows * k * 2 * inter, 2.0 * g * rows * inter * k
     b1, _ = timeit(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU), a.iters)
     b2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y), a.iters)
+    p1, _ = timeit(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair=True), a.iters)
+    p2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair=True), a.iters)
 
     def cublas_loop():
         for e in range(g):
@@ -108,7 +115,10 @@ def cmd_grouped(a):
             torch.matmul(hh, w2[e].t(), out=y[e * rows:(e + 1) * rows])
 
     b3, _ = timeit(cublas_loop, max(3, a.iters // 2))
-    print(json.dumps({"kernel": "grouped_swiglu_ffn", "experts": g, "rows_per_expert": rows,
+    print(json.dumps({"kernel": "grouped_swiglu_ffn", "experts": g, "rows_per_expert": rows, "ragged": bool(a.ragged),
+                      "pair_gate_up_ms": round(p1, 4), "pair_gate_up_tflops": round(f1 / p1 / 1e9, 1),
+                      "pair_down_ms": round(p2, 4), "pair_down_tflops": round(f2 / p2 / 1e9, 1),
+                      "pair_frac_of_peak": round((f1 + f2) / (p1 + p2) / 1e9 / tf, 3),
                       "gate_up_ms": round(b1, 4), "gate_up_tflops": round(f1 / b1 / 1e9, 1),
                       "down_ms": round(b2, 4), "down_tflops": round(f2 / b2 / 1e9, 1),
                       "frac_of_peak": round((f1 + f2) / (b1 + b2) / 1e9 / tf, 3), "peak": tag,
@@ -140,6 +150,7 @@ if __name__ == "__main__":
     ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--experts", type=int, default=32)
     ap.add_argument("--rows", type=int, default=1024)
+    ap.add_argument("--ragged", action="store_true", help="grouped: multinomial group sizes instead of equal ones")
     ap.add_argument("--rows-q", type=int, default=32768)
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()

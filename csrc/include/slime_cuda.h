@@ -86,6 +86,12 @@ int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* gr
                             const void* row_info, const unsigned long long* scatter_bases8,
                             unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
                             const float* row_scale, void* status, void* stream);
+// The same on CTA pairs (clusters of two CTAs, 256-row tiles): faster where groups hold several hundred rows or more.
+int slime_grouped_gemm_bf16_pair(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                                 int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                                 const void* row_info, const unsigned long long* scatter_bases8,
+                                 unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
+                                 const float* row_scale, void* status, void* stream);
 // The same GEMM (epilogues 0 and 1) over groups that become readable while it runs: the rows of group g are loaded
 // once group_ready[g] (u64, device memory) >= step, step being group_ready_target or *group_ready_epoch when that
 // pointer is not null. The kernel that fills the rows must have been launched before this one (another stream).

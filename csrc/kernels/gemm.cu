@@ -2,7 +2,7 @@
 // synthetic prefill stand-in), a grouped GEMM over device-side row groups (the
 // expert FFN), its SwiGLU-fused variant, and a variant whose epilogue scatters
 // weighted rows to arbitrary (possibly peer) addresses.
-#include "common/gemm_tc2.cuh"
+#include "common/gemm_tc2g.cuh"
 #include "common/host_utils.h"
 #include "slime_cuda.h"
 
@@ -170,6 +170,27 @@ int launch_pair(const void* A, const void* B, const void* A_local, const Args& a
     }
 }
 
+// The grouped GEMM on CTA pairs: 256-row tiles per group, every epilogue of the single-CTA kernel.
+template<int EPI>
+int launch_pair_grouped(const void* A, const void* B, const Args& args, long long lda, long long ldb, cudaStream_t stream)
+{
+    constexpr int kPairStages = 6;
+    using S = SmemPair<kBN, kPairStages, false>;
+    CUtensorMap tmA, tmB;
+    const unsigned long long rowsB_total = static_cast<unsigned long long>(args.rowsB) * args.num_groups;
+    if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.M_total, args.K, lda, kBM, kBK)) return -1;
+    if (make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rowsB_total, args.K, ldb, kBN / 2, kBK)) return -1;
+    auto kern = gemm_bf16_pair_grouped_kernel<kBN, kPairStages, EPI>;
+    static bool configured = false;
+    if (!configured) {
+        SLIME_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+        configured = true;
+    }
+    kern<<<2 * (sm_count() / 2), kThreads, S::kTotal, stream>>>(tmA, tmB, args);
+    SLIME_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
 int check_common(int M, int N, int K, long long lda, long long ldb)
 {
     if (M <= 0 || N <= 0 || K <= 0) return fail("gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
@@ -302,6 +323,7 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, const int* g
                             void* status, void* stream);
 static thread_local unsigned long long* g_group_trace  = nullptr;  // set around one traced launch
 static thread_local unsigned int*       g_tile_counter = nullptr;
+static thread_local bool                g_on_pairs     = false;  // set around one launch on CTA pairs
 int slime_grouped_gemm_bf16_gated_traced(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
                                          int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
                                          const void* group_ready, unsigned long long group_ready_target,
@@ -316,6 +338,20 @@ int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* gr
 {
     return grouped_gemm_impl(A, B, C, group_offsets, num_groups, M_cap, N, K, lda, ldb, ldc, epilogue, row_info, scatter_bases8,
                              scatter_row_bytes, scatter_slots, row_scale, nullptr, 0, nullptr, status, stream);
+}
+
+// The same on CTA pairs (256-row tiles; pays off for groups of several hundred rows and more).
+int slime_grouped_gemm_bf16_pair(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                                 int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                                 const void* row_info, const unsigned long long* scatter_bases8,
+                                 unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
+                                 const float* row_scale, void* status, void* stream)
+{
+    g_on_pairs   = true;
+    const int rc = grouped_gemm_impl(A, B, C, group_offsets, num_groups, M_cap, N, K, lda, ldb, ldc, epilogue, row_info, scatter_bases8,
+                                     scatter_row_bytes, scatter_slots, row_scale, nullptr, 0, nullptr, status, stream);
+    g_on_pairs   = false;
+    return rc;
 }
 
 // The grouped GEMM whose groups become readable while it runs: before the first tile of group g is loaded, the
@@ -381,11 +417,11 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, const int* g
     switch (epilogue) {
         case kEpiStore:
             a.rowsB = N;
-            return launch<kEpiStore>(A, B, a, lda, ldb, s);
+            return g_on_pairs ? launch_pair_grouped<kEpiStore>(A, B, a, lda, ldb, s) : launch<kEpiStore>(A, B, a, lda, ldb, s);
         case kEpiSwiGLU:
             if (N % (kBN / 2) != 0) return fail("grouped gemm: SwiGLU needs N to be a multiple of %d", kBN / 2);
             a.rowsB = 2 * N;
-            return launch<kEpiSwiGLU>(A, B, a, lda, ldb, s);
+            return g_on_pairs ? launch_pair_grouped<kEpiSwiGLU>(A, B, a, lda, ldb, s) : launch<kEpiSwiGLU>(A, B, a, lda, ldb, s);
         case kEpiScatterRows:
             if (row_info == nullptr || scatter_bases8 == nullptr) return fail("grouped gemm: scatter epilogue needs row_info and bases");
             if (scatter_row_bytes % 16 != 0) return fail("grouped gemm: scatter rows must be 16-byte aligned");
@@ -395,7 +431,8 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, const int* g
             for (int i = 0; i < 8; ++i) a.scatter_base[i] = scatter_bases8[i];
             a.scatter_row_bytes = scatter_row_bytes;
             a.scatter_slots     = scatter_slots;
-            return launch<kEpiScatterRows>(A, B, a, lda, ldb, s);
+            return g_on_pairs ? launch_pair_grouped<kEpiScatterRows>(A, B, a, lda, ldb, s)
+                              : launch<kEpiScatterRows>(A, B, a, lda, ldb, s);
         default:
             return fail("grouped gemm: unknown epilogue %d", epilogue);
     }

@@ -53,6 +53,7 @@ _SIGNATURES = {
                                 c_longlong, c_longlong, c_int, c_void_p, c_void_p, c_ulonglong, c_ulonglong, c_void_p,
                                 c_void_p, c_void_p],
 }
+_SIGNATURES["slime_grouped_gemm_bf16_pair"] = _SIGNATURES["slime_grouped_gemm_bf16"]
 
 
 class SlimeCudaError(RuntimeError):

@@ -87,6 +87,12 @@ class ExpertParallelMoE:
         self.comm_blocks = int(os.environ.get("SLIME_EP_COMM_BLOCKS", "0"))
         # words of the gated GEMM's dynamic tile scheduler (SLIME_EP_STATIC_TILES=1: every gridDim-th tile instead)
         self._tile_counter = None if os.environ.get("SLIME_EP_STATIC_TILES") == "1" else torch.zeros(2, dtype=torch.int32, device=dev)
+        # pair_gemm: the expert GEMMs on CTA pairs (256-row tiles). They win where a local expert sees several hundred
+        # rows per step (many ranks), and lose to the single-CTA kernel's 128-row tiles on small groups;
+        # SLIME_EP_PAIR_GEMM=0|1 overrides the rule, autotune() measures.
+        rows_per_expert = max_tokens * cfg.topk * self.world // max(1, cfg.num_experts)
+        forced = os.environ.get("SLIME_EP_PAIR_GEMM")
+        self.pair_gemm = rows_per_expert >= 512 if forced is None else forced == "1"
         cap = self.buf.recv_cap
         self.xd = torch.empty((cap, cfg.hidden), dtype=torch.bfloat16, device=dev)
         self.h = torch.empty((cap, cfg.intermediate), dtype=torch.bfloat16, device=dev)
@@ -115,13 +121,14 @@ class ExpertParallelMoE:
             gemm.grouped_gemm_fp8a(self.buf.recv_x, self.buf.recv_scale, self.w_gate_up, self.buf.group_offsets, out=self.h,
                                    epilogue=gemm.EPI_SWIGLU)
             return
-        gemm.grouped_gemm_bf16(self.xd, self.w_gate_up, self.buf.group_offsets, out=self.h, epilogue=gemm.EPI_SWIGLU)
+        gemm.grouped_gemm_bf16(self.xd, self.w_gate_up, self.buf.group_offsets, out=self.h, epilogue=gemm.EPI_SWIGLU,
+                               pair=self.pair_gemm)
 
     def step_down(self):
         c = self.cfg
         gemm.grouped_gemm_bf16(self.h, self.w_down, self.buf.group_offsets, epilogue=gemm.EPI_SCATTER_ROWS,
                                row_info=self.buf.recv_info, scatter_bases=self._bases,
-                               scatter_row_bytes=c.hidden * 2, scatter_slots=self.max_tokens * c.topk)
+                               scatter_row_bytes=c.hidden * 2, scatter_slots=self.max_tokens * c.topk, pair=self.pair_gemm)
 
     def step_experts(self, T, epoch):
         self.step_recv(T, epoch)
@@ -180,9 +187,9 @@ class ExpertParallelMoE:
         return out
 
     def autotune(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor | None = None, steps: int = 4) -> dict:
-        """Pick the faster of the two forms of the first half (phases one after the other, or streamed) for this
-        shape and world size by running both, and keep it. Every rank must call this with its own inputs of the step
-        shape; the device times are combined as the maximum over ranks, so all ranks decide alike. Which form wins
+        """Pick the faster expert GEMM (single CTAs or CTA pairs) and then the faster of the two forms of the first
+        half (phases one after the other, or streamed) for this shape and world size by running them, and keep both.
+        Every rank must call this with its own inputs of the step shape; the device times are combined as the maximum over ranks, so all ranks decide alike. Which form wins
         depends on the regime: streaming hides the NVLink-bound push under compute-bound expert GEMMs (many ranks, many
         rows per expert) and loses where the GEMMs stream weights from HBM and the extra traffic gets in their way.
         """
@@ -191,8 +198,13 @@ class ExpertParallelMoE:
         if self.fuse_dequant:
             return {"streamed": False, "reason": "the fused-dequant GEMM has no streamed form"}
         times = {}
-        for form in (False, True):
-            self.streamed = form
+        for form in ("single", "pair", True):
+            if form is True:
+                self.pair_gemm = times["pair"] < times["single"]
+                times[False] = min(times["pair"], times["single"])
+            self.streamed = form is True
+            if form is not True:
+                self.pair_gemm = form == "pair"
             for _ in range(2):
                 self.forward(x, logits, out)
             if dist.is_initialized():
@@ -210,7 +222,9 @@ class ExpertParallelMoE:
             times[form] = float(t.item())
             self.buf.status.check()
         self.streamed = times[True] < times[False]
-        return {"streamed": self.streamed, "serial_ms": round(times[False], 4), "streamed_ms": round(times[True], 4)}
+        return {"streamed": self.streamed, "pair_gemm": self.pair_gemm, "serial_ms": round(times[False], 4),
+                "serial_single_cta_ms": round(times["single"], 4), "serial_cta_pair_ms": round(times["pair"], 4),
+                "streamed_ms": round(times[True], 4)}
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """x [T, hidden] bf16, router logits [T, num_experts] fp32 -> [T, hidden] bf16."""

@@ -30,19 +30,20 @@ def test_gemm_bf16(m, n, k):
     _check(out, ref, k)
 
 
-def test_grouped_gemm_store_and_swiglu():
+@pytest.mark.parametrize("pair", [False, True])
+def test_grouped_gemm_store_and_swiglu(pair):
     from dlslime_b200.ops import gemm
     from dlslime_b200.ops._common import default_status
 
     torch.manual_seed(5)
-    sizes = [0, 5, 128, 131, 300, 1, 0, 64]
+    sizes = [0, 5, 128, 131, 300, 1, 0, 64] + ([256, 700, 513] if pair else [])
     g, k, n = len(sizes), 512, 256
     offs = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device="cuda")
     total = sum(sizes)
     a = torch.randn(total + 50, k, device="cuda", dtype=torch.bfloat16)  # extra rows past the last group are ignored
     w = (torch.randn(g, n, k, device="cuda") * 0.05).to(torch.bfloat16)
     out = torch.full((total + 50, n), 7.0, device="cuda", dtype=torch.bfloat16)
-    gemm.grouped_gemm_bf16(a, w, offs, out=out)
+    gemm.grouped_gemm_bf16(a, w, offs, out=out, pair=pair)
     torch.cuda.synchronize()
     default_status().check()
     start = 0
@@ -56,7 +57,7 @@ def test_grouped_gemm_store_and_swiglu():
     # SwiGLU: weights hold N gate rows then N up rows per group
     n_int = 128
     w2 = (torch.randn(g, 2 * n_int, k, device="cuda") * 0.05).to(torch.bfloat16)
-    h = gemm.grouped_gemm_bf16(a, w2, offs, epilogue=gemm.EPI_SWIGLU)
+    h = gemm.grouped_gemm_bf16(a, w2, offs, epilogue=gemm.EPI_SWIGLU, pair=pair)
     torch.cuda.synchronize()
     default_status().check()
     start = 0
@@ -69,15 +70,16 @@ def test_grouped_gemm_store_and_swiglu():
         start += sz
 
 
-def test_grouped_gemm_scatter_rows():
+@pytest.mark.parametrize("pair", [False, True])
+def test_grouped_gemm_scatter_rows(pair):
     from dlslime_b200.ops import gemm
     from dlslime_b200.ops._common import default_status
 
     torch.manual_seed(6)
-    sizes = [40, 0, 200]
+    sizes = [40, 0, 200] + ([517] if pair else [])
     g, k, n = len(sizes), 256, 512
     total = sum(sizes)
-    offs = torch.tensor([0, 40, 40, 240], dtype=torch.int32, device="cuda")
+    offs = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device="cuda")
     a = torch.randn(total, k, device="cuda", dtype=torch.bfloat16)
     w = (torch.randn(g, n, k, device="cuda") * 0.05).to(torch.bfloat16)
     dst = torch.zeros(total, n, device="cuda", dtype=torch.bfloat16)
@@ -90,7 +92,7 @@ def test_grouped_gemm_scatter_rows():
     bases[0] = dst.data_ptr()
     scale = torch.rand(total, device="cuda") + 0.5
     gemm.grouped_gemm_bf16(a, w, offs, epilogue=gemm.EPI_SCATTER_ROWS, row_info=row_info, scatter_bases=bases,
-                           scatter_row_bytes=n * 2, scatter_slots=total, row_scale=scale)
+                           scatter_row_bytes=n * 2, scatter_slots=total, row_scale=scale, pair=pair)
     torch.cuda.synchronize()
     default_status().check()
     ref = torch.zeros(total, n, device="cuda")
