@@ -51,6 +51,45 @@ def timeit(fn, iters=10, warmup=3):
     return times[0], times[len(times) // 2]
 
 
+_sampler = None
+
+
+def sustained(fn, flops, secs=1.5):
+    """The same kernel back to back for ``secs`` seconds (no L2 flush: the operands are larger than L2), with the SM
+    clock and board power sampled meanwhile: a large GEMM runs against the power limit, so what a kernel sustains is
+    set by the energy it needs per FLOP, and the burst figure of a single launch does not show it.
+    ``tensor_eff_at_clock`` = FLOP/s / (SMs x 8192 FLOP/clk x median SM clock)."""
+    global _sampler
+    import importlib.util
+    import time
+
+    if _sampler is None:
+        spec = importlib.util.spec_from_file_location("_root_bench", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        _sampler = mod.ClockSampler(torch.cuda.current_device())
+        time.sleep(0.3)
+    for _ in range(3):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+    n = max(10, int(secs * 1e3 / max(e0.elapsed_time(e1), 1e-3)))
+    t0 = time.time()
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = e0.elapsed_time(e1) / n
+    w = _sampler.window(t0 + 0.3 * (t1 - t0), t1)  # the clock has settled after the first third
+    clk = w.get("sm_mhz") or 0
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    time.sleep(0.5)
+    return {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "sm_mhz": clk, "power_w_max": w.get("power_w_max"),
+            "reasons": w.get("reasons"), "tensor_eff_at_clock": round(flops / (ms * 1e-3) / (sms * 8192 * clk * 1e6), 3) if clk else None}
+
+
 def cmd_gemm(a):
     from dlslime_b200.ops import gemm
 
@@ -61,12 +100,23 @@ def cmd_gemm(a):
     flops = 2.0 * a.m * a.n * a.k
     best, med = timeit(lambda: gemm.gemm_bf16(x, w, out=out, pair=False), a.iters)
     b2, m2 = timeit(lambda: torch.matmul(x, w.t(), out=out), a.iters)
-    bp, mp = timeit(lambda: gemm.gemm_bf16_pair(x, w, out=out), a.iters)
+    bp, mp = timeit(lambda: gemm.gemm_bf16_pair(x, w, out=out, wide=False), a.iters)
+    bw, mw = timeit(lambda: gemm.gemm_bf16_pair(x, w, out=out, wide=True), a.iters)
+    extra = {}
+    if a.sustained:
+        extra["sustained"] = {"cublas": sustained(lambda: torch.matmul(x, w.t(), out=out), flops),
+                              "pair_wide": sustained(lambda: gemm.gemm_bf16_pair(x, w, out=out, wide=True), flops),
+                              "pair": sustained(lambda: gemm.gemm_bf16_pair(x, w, out=out, wide=False), flops),
+                              "cublas_again": sustained(lambda: torch.matmul(x, w.t(), out=out), flops)}
     print(json.dumps({"kernel": "gemm_bf16_tc", "m": a.m, "n": a.n, "k": a.k, "ms_best": round(best, 4), "ms_median": round(med, 4),
+                      "wide_ms_best": round(bw, 4), "wide_ms_median": round(mw, 4), "wide_tflops_best": round(flops / bw / 1e9, 1),
+                      "wide_frac_of_peak": round(flops / bw / 1e9 / tf, 3), "auto_picks_wide": gemm._wide_tiles_pay(a.m, a.n), **extra,
                       "tflops_best": round(flops / best / 1e9, 1), "frac_of_peak": round(flops / best / 1e9 / tf, 3), "peak": tag,
                       "pair_ms_best": round(bp, 4), "pair_ms_median": round(mp, 4), "pair_tflops_best": round(flops / bp / 1e9, 1),
                       "pair_frac_of_peak": round(flops / bp / 1e9 / tf, 3),
                       "cublas_ms_best": round(b2, 4), "cublas_tflops_best": round(flops / b2 / 1e9, 1)}))
+    if _sampler is not None:
+        _sampler.stop()
 
 
 def cmd_gemm_fp8(a):
@@ -107,6 +157,19 @@ def cmd_grouped(a):
     b2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y), a.iters)
     p1, _ = timeit(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair=True), a.iters)
     p2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair=True), a.iters)
+    q1, _ = timeit(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair="wide"), a.iters)
+    q2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair="wide"), a.iters)
+
+    extra = {}
+    if a.sustained:
+        extra["sustained_gate_up"] = {
+            "single": sustained(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU), f1),
+            "pair": sustained(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair=True), f1),
+            "wide": sustained(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair="wide"), f1)}
+        extra["sustained_down"] = {
+            "single": sustained(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y), f2),
+            "pair": sustained(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair=True), f2),
+            "wide": sustained(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair="wide"), f2)}
 
     def cublas_loop():
         for e in range(g):
@@ -119,10 +182,15 @@ def cmd_grouped(a):
                       "pair_gate_up_ms": round(p1, 4), "pair_gate_up_tflops": round(f1 / p1 / 1e9, 1),
                       "pair_down_ms": round(p2, 4), "pair_down_tflops": round(f2 / p2 / 1e9, 1),
                       "pair_frac_of_peak": round((f1 + f2) / (p1 + p2) / 1e9 / tf, 3),
+                      "wide_gate_up_ms": round(q1, 4), "wide_gate_up_tflops": round(f1 / q1 / 1e9, 1),
+                      "wide_down_ms": round(q2, 4), "wide_down_tflops": round(f2 / q2 / 1e9, 1),
+                      "wide_frac_of_peak": round((f1 + f2) / (q1 + q2) / 1e9 / tf, 3),
                       "gate_up_ms": round(b1, 4), "gate_up_tflops": round(f1 / b1 / 1e9, 1),
                       "down_ms": round(b2, 4), "down_tflops": round(f2 / b2 / 1e9, 1),
                       "frac_of_peak": round((f1 + f2) / (b1 + b2) / 1e9 / tf, 3), "peak": tag,
-                      "cublas_loop_ms": round(b3, 4), "cublas_loop_tflops": round((f1 + f2) / b3 / 1e9, 1)}))
+                      "cublas_loop_ms": round(b3, 4), "cublas_loop_tflops": round((f1 + f2) / b3 / 1e9, 1), **extra}))
+    if _sampler is not None:
+        _sampler.stop()
 
 
 def cmd_quant(a):
@@ -150,6 +218,7 @@ if __name__ == "__main__":
     ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--experts", type=int, default=32)
     ap.add_argument("--rows", type=int, default=1024)
+    ap.add_argument("--sustained", action="store_true", help="gemm, grouped: also loop each kernel for seconds and sample clock and power")
     ap.add_argument("--ragged", action="store_true", help="grouped: multinomial group sizes instead of equal ones")
     ap.add_argument("--rows-q", type=int, default=32768)
     ap.add_argument("--iters", type=int, default=10)

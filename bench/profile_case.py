@@ -3,6 +3,8 @@
 
     python bench/profile_case.py gemm        # 4096 x 4096 x 4096 bf16 GEMM, 3 launches
     python bench/profile_case.py gemm_pair   # the same product on CTA pairs (cta_group::2), 3 launches
+    python bench/profile_case.py gemm_wide   # 8192^3 on CTA pairs with 256 x 512 tiles (operands larger than L2), 2 launches
+    python bench/profile_case.py grouped_pair  # grouped SwiGLU gate/up + down GEMM on CTA pairs, 8 experts x 1024 rows, 2 launches each
     python bench/profile_case.py gemm_fp8    # the same shape in block-scaled fp8 (e4m3), 3 launches
     python bench/profile_case.py grouped     # grouped SwiGLU gate/up + down GEMM, 8 experts x 512 rows, 2 launches each
     python bench/profile_case.py grouped_stream  # the same GEMMs with 16 experts x 128 rows: weight streaming, HBM-bound
@@ -44,6 +46,31 @@ def gemm_pair_case():
     out = torch.empty(4096, 4096, device="cuda", dtype=torch.bfloat16)
     for _ in range(3):
         gemm.gemm_bf16_pair(a, b, out=out)
+
+
+def gemm_wide_case():
+    from dlslime_b200.ops import gemm
+
+    a = torch.randn(8192, 8192, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(8192, 8192, device="cuda") * 0.02).to(torch.bfloat16)
+    out = torch.empty(8192, 8192, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):
+        gemm.gemm_bf16_pair(a, b, out=out, wide=True)
+
+
+def grouped_pair_case():
+    from dlslime_b200.ops import gemm
+
+    g, rows, k, inter = 8, 1024, 7168, 2048
+    offs = torch.arange(0, g + 1, dtype=torch.int32, device="cuda") * rows
+    x = torch.randn(g * rows, k, device="cuda").to(torch.bfloat16)
+    w13 = (torch.randn(g, 2 * inter, k, device="cuda") * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(g, k, inter, device="cuda") * 0.02).to(torch.bfloat16)
+    h = torch.empty(g * rows, inter, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty(g * rows, k, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):
+        gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair=True)
+        gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair=True)
 
 
 def gemm_fp8_case():
@@ -223,6 +250,7 @@ def moe_stream_case():
 
 if __name__ == "__main__":
     {"ag_gemm_fused": ag_gemm_fused_case, "ag_gemm_fp8_fused": ag_gemm_fp8_fused_case, "moe_stream": moe_stream_case,
-     "alltoall": alltoall_case, "kv": kv_case, "allgather": allgather_case, "gemm": gemm_case, "gemm_pair": gemm_pair_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "grouped_stream": grouped_stream_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
+     "alltoall": alltoall_case, "kv": kv_case, "allgather": allgather_case, "gemm": gemm_case, "gemm_pair": gemm_pair_case, "gemm_wide": gemm_wide_case,
+     "grouped_pair": grouped_pair_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "grouped_stream": grouped_stream_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
     torch.cuda.synchronize()
     print("done", sys.argv[1])

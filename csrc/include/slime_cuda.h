@@ -59,6 +59,9 @@ int slime_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
 // (a_ready[row / a_ready_rows] >= a_ready_target); m tiles start at m_tile_rotate.
 int slime_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                          long long ldc, void* status, void* stream);
+// CTA pairs with 256 x 512 tiles, tiles ordered in bands of columns that keep their B rows in L2.
+int slime_gemm_bf16_wide(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                         long long ldc, void* status, void* stream);
 int slime_gemm_fp8_blockscaled(const void* Aq, const float* sa, const void* Bq, const float* sb, void* C, int M, int N, int K,
                                long long lda, long long ldb, long long ldc, void* status, void* stream);
 int slime_ag_gemm_fp8(int mode, const void* xq_local, const float* sx_local, const void* aq_full, const float* sa_full,
@@ -88,6 +91,12 @@ int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* gr
                             const float* row_scale, void* status, void* stream);
 // The same on CTA pairs (clusters of two CTAs, 256-row tiles): faster where groups hold several hundred rows or more.
 int slime_grouped_gemm_bf16_pair(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                                 int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                                 const void* row_info, const unsigned long long* scatter_bases8,
+                                 unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
+                                 const float* row_scale, void* status, void* stream);
+// The same on CTA pairs with 256 x 512 tiles (two accumulator blocks that share the A tile).
+int slime_grouped_gemm_bf16_wide(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
                                  int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
                                  const void* row_info, const unsigned long long* scatter_bases8,
                                  unsigned long long scatter_row_bytes, unsigned long long scatter_slots,

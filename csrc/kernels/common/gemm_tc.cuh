@@ -25,7 +25,7 @@ namespace gemm {
 constexpr int kBM      = 128;
 constexpr int kBK      = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kThreads = 192;
-constexpr int kEpiRowPitch = 144;  // 128 payload bytes + 16 so that 32 rows spread over all shared-memory banks
+constexpr int kEpiRowPitch = 128;  // one 128-byte slot per tile row; the 16-byte pieces of a slot are XOR-swizzled with the row
 
 enum Epilogue : int {
     kEpiStore  = 0,  // C = acc (bf16)
@@ -94,7 +94,7 @@ struct Smem {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kRawBytes   = A8 ? kBM * kBK : 0;  // e4m3 A tile of a stage as it arrives, before expansion
     static constexpr int kBarBytes   = (3 * STAGES + 4 + kAgMaxBufs + 2 * kTileRing) * 8 + 16 + kTileRing * 4;
-    static constexpr int kEpiBytes   = 128 * kEpiRowPitch;  // one padded 128-byte slot per tile row
+    static constexpr int kEpiBytes   = 128 * kEpiRowPitch;  // one 128-byte slot per tile row
     static constexpr int kBase       = STAGES * (kStageBytes + kRawBytes) + kEpiBytes + kBarBytes + 1024;  // + alignment slack
     // the push stages its chunks in whatever shared memory the tile ring leaves free
     static constexpr int kAgBufs = !AG ? 0 : ((kSmemLimit - kBase - 128) / kAgChunkBytes > kAgMaxBufs ? kAgMaxBufs : (kSmemLimit - kBase - 128) / kAgChunkBytes);
@@ -247,6 +247,35 @@ __device__ __forceinline__ float silu(float x)
     return x / (1.0f + __expf(-x));
 }
 
+// One 64-column piece of 32 result rows leaves the SM: every lane has its row's 128 bytes (packed bf16) in registers,
+// writes them to its slot, and the warp then stores row by row, eight lanes per row and 16 bytes per lane, so that
+// every store instruction writes four whole 128-byte lines (local or peer memory). Piece p of row r sits at
+// p ^ (r & 7) inside the slot, which keeps both the row-wise writes and the line-wise reads free of bank conflicts
+// without padding. `dst` is this lane's row address for the piece, `do_store` whether its row is written at all,
+// `cols` how many of the 64 columns exist (a multiple of 8). Must be called by all 32 lanes.
+// (One bulk copy per row and piece, which this replaces, costs about 32 cycles of the SM's copy engine each: 1024 of
+// them per 128 x 512 tile took as long as a quarter of the main loop.)
+__device__ __forceinline__ void epi_store_piece(uint8_t* my_slot, const uint8_t* warp_slots, const uint32_t (&o)[32],
+                                                unsigned long long dst, bool do_store, int cols, int lane)
+{
+    uint4* sp = reinterpret_cast<uint4*>(my_slot);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sp[i ^ (lane & 7)] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+    __syncwarp();
+    const int sub = lane >> 3, piece = lane & 7;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int                r  = i * 4 + sub;
+        const unsigned long long d  = __shfl_sync(0xffffffffu, dst, r);
+        const int                ok = __shfl_sync(0xffffffffu, do_store ? 1 : 0, r);
+        if (ok && piece * 8 < cols) {
+            const uint4 v = *reinterpret_cast<const uint4*>(warp_slots + r * kEpiRowPitch + ((piece ^ (r & 7)) << 4));
+            *reinterpret_cast<uint4*>(d + static_cast<unsigned long long>(piece) * 16) = v;
+        }
+    }
+    __syncwarp();  // the slots may be overwritten by the next piece
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -354,14 +383,12 @@ __device__ __forceinline__ bool ag_push_bulk(const Args& a, uint8_t* bufs, uint6
             }
         }
         if (chunks < 3) {
-            tma_store_wait<0>();
             signal_unit(u);
         }
         else {
             pending = u;
         }
     }
-    tma_store_wait<0>();
     if (pending >= 0) signal_unit(pending);
     return true;
 }
@@ -681,11 +708,10 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             else {
                 drow = reinterpret_cast<unsigned long long>(args.C + static_cast<long long>(row) * args.ldc + col0);
             }
-            // Rows leave through shared memory: the thread packs 64 output columns (128 bytes) of its
-            // row into its private, padded slot and hands them to the bulk-copy engine, which writes
-            // one contiguous 128-byte piece per row (local or peer memory) instead of scattered
-            // 16-byte stores.
+            // Rows leave through shared memory: the thread packs 64 output columns (128 bytes) of its row into its
+            // private, padded slot; the warp then writes whole 128-byte lines row by row (see epi_store_piece).
             uint8_t* my_slot = epi_smem + (quad * 32 + lane) * kEpiRowPitch;
+            const uint8_t* warp_slots = epi_smem + quad * 32 * kEpiRowPitch;
 #pragma unroll 1
             for (int c = 0; c < kBNOut; c += 64) {
                 uint32_t o[32];
@@ -715,17 +741,10 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             o[hb * 16 + i] = pack_bf16(__uint_as_float(v[2 * i]) * scale, __uint_as_float(v[2 * i + 1]) * scale);
                     }
                 }
-                tma_store_wait_read<0>();  // the previous piece has left this slot
-                uint4* sp = reinterpret_cast<uint4*>(my_slot);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) sp[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-                fence_proxy_async_smem();
                 int cols = args.N - (col0 + c);
                 if (cols > 64) cols = 64;
                 if (cols > kBNOut - c) cols = kBNOut - c;  // tile widths that are not a multiple of 64
-                if (do_store && cols > 0)
-                    bulk_store_s2g(reinterpret_cast<void*>(drow + static_cast<unsigned long long>(c) * 2), my_slot, cols * 2);
-                tma_store_commit();
+                epi_store_piece(my_slot, warp_slots, o, drow + static_cast<unsigned long long>(c) * 2, do_store, cols, lane);
             }
             tc_fence_before_sync();
             mbar_arrive(&tempty_bar[acc]);
@@ -734,7 +753,6 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 acc_phase ^= 1;
             }
         }
-        tma_store_wait<0>();  // every row this thread handed to the copy engine has been written
     }
 
     // teardown: everyone meets, then the allocating warp frees TMEM

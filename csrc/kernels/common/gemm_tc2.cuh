@@ -45,10 +45,11 @@ struct PairTile {
     int nt;
 };
 
-// Tiles t = cluster, cluster + n_clusters, ... ; m fastest (or shard-major for the all-gather form).
+// Tiles t = cluster, cluster + n_clusters, ... ; shard-major for the all-gather form, else in bands of tile columns
+// whose B rows (at most ~40 MB) stay in L2 while A streams past once per band; inside a band the column runs fastest.
 struct PairWalker {
     const Args& a;
-    int         mtiles, ntiles, total, t, step;
+    int         mtiles, ntiles, total, t, step, band;
     __device__ PairWalker(const Args& args, int bn, int cluster, int n_clusters): a(args)
     {
         mtiles = (a.M_total + kPairBM - 1) / kPairBM;
@@ -56,6 +57,9 @@ struct PairWalker {
         total  = mtiles * ntiles;
         t      = cluster;
         step   = n_clusters;
+        const long long per_col = static_cast<long long>(bn) * a.K * 2;
+        const long long b       = (40ll << 20) / (per_col > 0 ? per_col : 1);
+        band                    = b < 1 ? 1 : (b > ntiles ? ntiles : static_cast<int>(b));
     }
     __device__ bool next(PairTile& c)
     {
@@ -71,8 +75,12 @@ struct PairWalker {
             mt                  = shard * per + rem % per;
         }
         else {
-            mt = t % mtiles;
-            nt = t / mtiles;
+            const int per_band = mtiles * band;
+            const int b        = t / per_band;
+            const int r        = t - b * per_band;
+            const int width    = (b + 1) * band <= ntiles ? band : ntiles - b * band;  // the last band may be narrower
+            mt                 = r / width;
+            nt                 = b * band + r % width;
         }
         c.row0 = mt * kPairBM;
         c.nt   = nt;
@@ -256,6 +264,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const int      col0  = tc.nt * BN;
             const unsigned long long drow = reinterpret_cast<unsigned long long>(args.C + static_cast<long long>(row) * args.ldc + col0);
             uint8_t* my_slot = epi_smem + (quad * 32 + lane) * kEpiRowPitch;
+            const uint8_t* warp_slots = epi_smem + quad * 32 * kEpiRowPitch;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 64) {
                 uint32_t o[32];
@@ -267,16 +276,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 #pragma unroll
                     for (int i = 0; i < 16; ++i) o[hb * 16 + i] = pack_bf16(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
                 }
-                tma_store_wait_read<0>();
-                uint4* sp = reinterpret_cast<uint4*>(my_slot);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) sp[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-                fence_proxy_async_smem();
                 int cols = args.N - (col0 + c);
                 if (cols > 64) cols = 64;
                 if (cols > BN - c) cols = BN - c;
-                if (valid && cols > 0) bulk_store_s2g(reinterpret_cast<void*>(drow + static_cast<unsigned long long>(c) * 2), my_slot, cols * 2);
-                tma_store_commit();
+                epi_store_piece(my_slot, warp_slots, o, drow + static_cast<unsigned long long>(c) * 2, valid, cols, lane);
             }
             tc_fence_before_sync();
             if (crank == 0)
@@ -288,7 +291,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 acc_phase ^= 1;
             }
         }
-        tma_store_wait<0>();
     }
 
     // teardown: both CTAs meet (no CTA may leave while its peer still reads its shared memory or signals its

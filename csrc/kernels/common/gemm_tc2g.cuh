@@ -237,6 +237,7 @@ gemm_bf16_pair_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __g
                 drow = reinterpret_cast<unsigned long long>(args.C + static_cast<long long>(row) * args.ldc + col0);
             }
             uint8_t* my_slot = epi_smem + (quad * 32 + lane) * kEpiRowPitch;
+            const uint8_t* warp_slots = epi_smem + quad * 32 * kEpiRowPitch;
 #pragma unroll 1
             for (int c = 0; c < kBNOut; c += 64) {
                 uint32_t o[32];
@@ -266,17 +267,10 @@ gemm_bf16_pair_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __g
                             o[hb * 16 + i] = pack_bf16(__uint_as_float(v[2 * i]) * scale, __uint_as_float(v[2 * i + 1]) * scale);
                     }
                 }
-                tma_store_wait_read<0>();  // the previous piece has left this slot
-                uint4* sp = reinterpret_cast<uint4*>(my_slot);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) sp[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-                fence_proxy_async_smem();
                 int cols = args.N - (col0 + c);
                 if (cols > 64) cols = 64;
                 if (cols > kBNOut - c) cols = kBNOut - c;
-                if (do_store && cols > 0)
-                    bulk_store_s2g(reinterpret_cast<void*>(drow + static_cast<unsigned long long>(c) * 2), my_slot, cols * 2);
-                tma_store_commit();
+                epi_store_piece(my_slot, warp_slots, o, drow + static_cast<unsigned long long>(c) * 2, do_store, cols, lane);
             }
             tc_fence_before_sync();
             if (crank == 0)
@@ -288,7 +282,6 @@ gemm_bf16_pair_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __g
                 acc_phase ^= 1;
             }
         }
-        tma_store_wait<0>();
     }
 
     // teardown: both CTAs meet (no CTA may leave while its peer still reads its shared memory or signals its

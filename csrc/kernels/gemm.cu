@@ -2,7 +2,7 @@
 // synthetic prefill stand-in), a grouped GEMM over device-side row groups (the
 // expert FFN), its SwiGLU-fused variant, and a variant whose epilogue scatters
 // weighted rows to arbitrary (possibly peer) addresses.
-#include "common/gemm_tc2g.cuh"
+#include "common/gemm_tc2w.cuh"
 #include "common/host_utils.h"
 #include "slime_cuda.h"
 
@@ -191,6 +191,33 @@ int launch_pair_grouped(const void* A, const void* B, const Args& args, long lon
     return 0;
 }
 
+// CTA pairs with 256 x 512 tiles (two accumulator blocks): plain (num_groups == 1, no offsets) and grouped GEMMs.
+template<int EPI>
+int launch_pair_wide(const void* A, const void* B, const Args& args, long long lda, long long ldb, cudaStream_t stream)
+{
+    constexpr int kWideStages = 4;
+    using S = SmemWide<kBN, kWideStages>;
+    CUtensorMap tmA, tmB;
+    const unsigned long long rowsB_total = static_cast<unsigned long long>(args.rowsB) * args.num_groups;
+    if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.M_total, args.K, lda, kBM, kBK)) return -1;
+    if (make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rowsB_total, args.K, ldb, kBN / 2, kBK)) return -1;
+    auto kern = gemm_bf16_pair_wide_kernel<kBN, kWideStages, EPI>;
+    static bool configured = false;
+    if (!configured) {
+        SLIME_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+        configured = true;
+    }
+    int clusters = sm_count() / 2;
+    if (args.group_offsets == nullptr) {
+        constexpr int kTileOut = EPI == kEpiSwiGLU ? kBN : 2 * kBN;
+        const long    tiles    = static_cast<long>((args.M_total + kPairBM - 1) / kPairBM) * ((args.N + kTileOut - 1) / kTileOut);
+        if (tiles < clusters) clusters = static_cast<int>(tiles);
+    }
+    kern<<<2 * clusters, kWideThreads, S::kTotal, stream>>>(tmA, tmB, args);
+    SLIME_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
 int check_common(int M, int N, int K, long long lda, long long ldb)
 {
     if (M <= 0 || N <= 0 || K <= 0) return fail("gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
@@ -236,6 +263,24 @@ int slime_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, in
     a.ldc        = ldc;
     a.status     = static_cast<KernelStatus*>(status);
     return launch_pair<false>(A, B, nullptr, a, lda, ldb, static_cast<cudaStream_t>(stream));
+}
+
+// The same on CTA pairs with 256 x 512 tiles and a tile order that keeps a band of B rows in L2.
+int slime_gemm_bf16_wide(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                         long long ldc, void* status, void* stream)
+{
+    if (check_common(M, N, K, lda, ldb)) return -1;
+    if (ldc % 8 != 0) return fail("gemm: ldc must be a multiple of 8 elements");
+    Args a{};
+    a.M_total    = M;
+    a.N          = N;
+    a.K          = K;
+    a.rowsB      = N;
+    a.num_groups = 1;
+    a.C          = static_cast<__nv_bfloat16*>(C);
+    a.ldc        = ldc;
+    a.status     = static_cast<KernelStatus*>(status);
+    return launch_pair_wide<kEpiStore>(A, B, a, lda, ldb, static_cast<cudaStream_t>(stream));
 }
 
 int slime_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
@@ -323,7 +368,7 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, const int* g
                             void* status, void* stream);
 static thread_local unsigned long long* g_group_trace  = nullptr;  // set around one traced launch
 static thread_local unsigned int*       g_tile_counter = nullptr;
-static thread_local bool                g_on_pairs     = false;  // set around one launch on CTA pairs
+static thread_local int                 g_on_pairs     = 0;  // set around one launch on CTA pairs: 1 = 256 x 256 tiles, 2 = 256 x 512
 int slime_grouped_gemm_bf16_gated_traced(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
                                          int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
                                          const void* group_ready, unsigned long long group_ready_target,
@@ -347,10 +392,25 @@ int slime_grouped_gemm_bf16_pair(const void* A, const void* B, void* C, const in
                                  unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
                                  const float* row_scale, void* status, void* stream)
 {
-    g_on_pairs   = true;
+    g_on_pairs   = 1;
     const int rc = grouped_gemm_impl(A, B, C, group_offsets, num_groups, M_cap, N, K, lda, ldb, ldc, epilogue, row_info, scatter_bases8,
                                      scatter_row_bytes, scatter_slots, row_scale, nullptr, 0, nullptr, status, stream);
-    g_on_pairs   = false;
+    g_on_pairs   = 0;
+    return rc;
+}
+
+// The same on CTA pairs with 256 x 512 tiles: a quarter less traffic from L2 into shared memory per FLOP, which is
+// what counts once the kernel runs against the power limit.
+int slime_grouped_gemm_bf16_wide(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                                 int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                                 const void* row_info, const unsigned long long* scatter_bases8,
+                                 unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
+                                 const float* row_scale, void* status, void* stream)
+{
+    g_on_pairs   = 2;
+    const int rc = grouped_gemm_impl(A, B, C, group_offsets, num_groups, M_cap, N, K, lda, ldb, ldc, epilogue, row_info, scatter_bases8,
+                                     scatter_row_bytes, scatter_slots, row_scale, nullptr, 0, nullptr, status, stream);
+    g_on_pairs   = 0;
     return rc;
 }
 
@@ -417,11 +477,13 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, const int* g
     switch (epilogue) {
         case kEpiStore:
             a.rowsB = N;
-            return g_on_pairs ? launch_pair_grouped<kEpiStore>(A, B, a, lda, ldb, s) : launch<kEpiStore>(A, B, a, lda, ldb, s);
+            return g_on_pairs == 2 ? launch_pair_wide<kEpiStore>(A, B, a, lda, ldb, s)
+                   : g_on_pairs ? launch_pair_grouped<kEpiStore>(A, B, a, lda, ldb, s) : launch<kEpiStore>(A, B, a, lda, ldb, s);
         case kEpiSwiGLU:
             if (N % (kBN / 2) != 0) return fail("grouped gemm: SwiGLU needs N to be a multiple of %d", kBN / 2);
             a.rowsB = 2 * N;
-            return g_on_pairs ? launch_pair_grouped<kEpiSwiGLU>(A, B, a, lda, ldb, s) : launch<kEpiSwiGLU>(A, B, a, lda, ldb, s);
+            return g_on_pairs == 2 ? launch_pair_wide<kEpiSwiGLU>(A, B, a, lda, ldb, s)
+                   : g_on_pairs ? launch_pair_grouped<kEpiSwiGLU>(A, B, a, lda, ldb, s) : launch<kEpiSwiGLU>(A, B, a, lda, ldb, s);
         case kEpiScatterRows:
             if (row_info == nullptr || scatter_bases8 == nullptr) return fail("grouped gemm: scatter epilogue needs row_info and bases");
             if (scatter_row_bytes % 16 != 0) return fail("grouped gemm: scatter rows must be 16-byte aligned");
@@ -431,8 +493,9 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, const int* g
             for (int i = 0; i < 8; ++i) a.scatter_base[i] = scatter_bases8[i];
             a.scatter_row_bytes = scatter_row_bytes;
             a.scatter_slots     = scatter_slots;
-            return g_on_pairs ? launch_pair_grouped<kEpiScatterRows>(A, B, a, lda, ldb, s)
-                              : launch<kEpiScatterRows>(A, B, a, lda, ldb, s);
+            return g_on_pairs == 2 ? launch_pair_wide<kEpiScatterRows>(A, B, a, lda, ldb, s)
+                   : g_on_pairs ? launch_pair_grouped<kEpiScatterRows>(A, B, a, lda, ldb, s)
+                                : launch<kEpiScatterRows>(A, B, a, lda, ldb, s);
         default:
             return fail("grouped gemm: unknown epilogue %d", epilogue);
     }

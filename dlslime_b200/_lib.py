@@ -54,6 +54,8 @@ _SIGNATURES = {
                                 c_void_p, c_void_p],
 }
 _SIGNATURES["slime_grouped_gemm_bf16_pair"] = _SIGNATURES["slime_grouped_gemm_bf16"]
+_SIGNATURES["slime_grouped_gemm_bf16_wide"] = _SIGNATURES["slime_grouped_gemm_bf16"]
+_SIGNATURES["slime_gemm_bf16_wide"] = _SIGNATURES["slime_gemm_bf16_pair"]
 
 
 class SlimeCudaError(RuntimeError):

@@ -87,12 +87,12 @@ class ExpertParallelMoE:
         self.comm_blocks = int(os.environ.get("SLIME_EP_COMM_BLOCKS", "0"))
         # words of the gated GEMM's dynamic tile scheduler (SLIME_EP_STATIC_TILES=1: every gridDim-th tile instead)
         self._tile_counter = None if os.environ.get("SLIME_EP_STATIC_TILES") == "1" else torch.zeros(2, dtype=torch.int32, device=dev)
-        # pair_gemm: the expert GEMMs on CTA pairs (256-row tiles). They win where a local expert sees several hundred
-        # rows per step (many ranks), and lose to the single-CTA kernel's 128-row tiles on small groups;
-        # SLIME_EP_PAIR_GEMM=0|1 overrides the rule, autotune() measures.
+        # pair_gemm: the expert GEMMs on CTA pairs (True: 256 x 256 tiles, "wide": 256 x 512). They win where a local
+        # expert sees several hundred rows per step (many ranks), and lose to the single-CTA kernel's 128-row tiles on
+        # small groups; SLIME_EP_PAIR_GEMM=0|1|wide overrides the rule, autotune() measures.
         rows_per_expert = max_tokens * cfg.topk * self.world // max(1, cfg.num_experts)
         forced = os.environ.get("SLIME_EP_PAIR_GEMM")
-        self.pair_gemm = rows_per_expert >= 512 if forced is None else forced == "1"
+        self.pair_gemm = (rows_per_expert >= 512) if forced is None else {"0": False, "1": True}.get(forced, forced)
         cap = self.buf.recv_cap
         self.xd = torch.empty((cap, cfg.hidden), dtype=torch.bfloat16, device=dev)
         self.h = torch.empty((cap, cfg.intermediate), dtype=torch.bfloat16, device=dev)
@@ -187,7 +187,7 @@ class ExpertParallelMoE:
         return out
 
     def autotune(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor | None = None, steps: int = 4) -> dict:
-        """Pick the faster expert GEMM (single CTAs or CTA pairs) and then the faster of the two forms of the first
+        """Pick the fastest expert GEMM (single CTAs, CTA pairs, CTA pairs with wide tiles) and then the faster of the two forms of the first
         half (phases one after the other, or streamed) for this shape and world size by running them, and keep both.
         Every rank must call this with its own inputs of the step shape; the device times are combined as the maximum over ranks, so all ranks decide alike. Which form wins
         depends on the regime: streaming hides the NVLink-bound push under compute-bound expert GEMMs (many ranks, many
@@ -198,13 +198,15 @@ class ExpertParallelMoE:
         if self.fuse_dequant:
             return {"streamed": False, "reason": "the fused-dequant GEMM has no streamed form"}
         times = {}
-        for form in ("single", "pair", True):
+        kinds = {"single": False, "pair": True, "wide": "wide"}
+        for form in (*kinds, True):
             if form is True:
-                self.pair_gemm = times["pair"] < times["single"]
-                times[False] = min(times["pair"], times["single"])
+                best = min(kinds, key=lambda k: times[k])
+                self.pair_gemm = kinds[best]
+                times[False] = times[best]
             self.streamed = form is True
             if form is not True:
-                self.pair_gemm = form == "pair"
+                self.pair_gemm = kinds[form]
             for _ in range(2):
                 self.forward(x, logits, out)
             if dist.is_initialized():
@@ -224,6 +226,7 @@ class ExpertParallelMoE:
         self.streamed = times[True] < times[False]
         return {"streamed": self.streamed, "pair_gemm": self.pair_gemm, "serial_ms": round(times[False], 4),
                 "serial_single_cta_ms": round(times["single"], 4), "serial_cta_pair_ms": round(times["pair"], 4),
+                "serial_cta_pair_wide_ms": round(times["wide"], 4),
                 "streamed_ms": round(times[True], 4)}
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

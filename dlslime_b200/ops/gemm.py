@@ -14,8 +14,23 @@ from ._common import default_status, ptr, require_cuda, stream_ptr
 EPI_STORE, EPI_SWIGLU, EPI_SCATTER_ROWS = 0, 1, 2
 
 
-def gemm_bf16_pair(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``out[M, N] = a[M, K] @ b[N, K].T`` on CTA pairs (256-row tiles, ``tcgen05`` ``cta_group::2``)."""
+def _wide_tiles_pay(m: int, n: int, sms: int = 148) -> bool:
+    """Whether the 256 x 512 tiling wastes no more of its last wave than the 256-row tilings of width 256 / 224 / 192
+    (cost model: waves x (tile width + a per-tile overhead in columns); the wide tiles get 10 % for the power they save)."""
+    pairs = max(1, sms // 2)
+    mt = -(-m // 256)
+
+    def cost(width, overhead):
+        tiles = mt * -(-n // width)
+        return -(-tiles // pairs) * (width + overhead)
+
+    return cost(512, 24) <= 1.10 * min(cost(w, 12) for w in (256, 224, 192))
+
+
+def gemm_bf16_pair(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, wide: bool | None = None) -> torch.Tensor:
+    """``out[M, N] = a[M, K] @ b[N, K].T`` on CTA pairs (256-row tiles, ``tcgen05`` ``cta_group::2``). ``wide``: tiles
+    of 256 x 512 (two accumulator blocks share the A tile; less traffic into shared memory per FLOP and an L2-friendly
+    tile order), default: where the tile count fits the grid as well as the narrower tilings do."""
     require_cuda(a, b)
     assert a.dtype == b.dtype == torch.bfloat16 and a.stride(1) == 1 and b.stride(1) == 1
     m, k = a.shape
@@ -23,7 +38,9 @@ def gemm_bf16_pair(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = 
     assert k == kb
     if out is None:
         out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
-    _lib.call("slime_gemm_bf16_pair", ptr(a), ptr(b), ptr(out), m, n, k, a.stride(0), b.stride(0), out.stride(0),
+    if wide is None:
+        wide = _wide_tiles_pay(m, n)
+    _lib.call("slime_gemm_bf16_wide" if wide else "slime_gemm_bf16_pair", ptr(a), ptr(b), ptr(out), m, n, k, a.stride(0), b.stride(0), out.stride(0),
               default_status().dev_ptr, stream_ptr())
     return out
 
@@ -49,7 +66,7 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
 def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor, out: torch.Tensor | None = None,
                       epilogue: int = EPI_STORE, row_info: torch.Tensor | None = None, scatter_bases=None,
                       scatter_row_bytes: int = 0, scatter_slots: int = 0,
-                      row_scale: torch.Tensor | None = None, pair: bool = False) -> torch.Tensor | None:
+                      row_scale: torch.Tensor | None = None, pair: bool | str = False) -> torch.Tensor | None:
     """Grouped GEMM over consecutive row groups of ``a``.
 
     ``a`` is ``[M_cap, K]``; ``group_offsets`` is an int32 device tensor of
@@ -63,7 +80,8 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
 
     ``pair`` runs the kernel on CTA pairs (256-row tiles, a third less traffic between L2 and the SMs): the faster form
     for groups of several hundred rows and more, the slower one for small groups (the last tile of a group computes
-    up to 255 unused rows instead of up to 127).
+    up to 255 unused rows instead of up to 127). ``pair="wide"``: CTA pairs with 256 x 512 tiles, another quarter less
+    traffic per FLOP, which is what raises the clock under the power limit.
     """
     require_cuda(a, b, group_offsets)
     assert a.dtype == b.dtype == torch.bfloat16 and group_offsets.dtype == torch.int32
@@ -75,7 +93,8 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
     if epilogue != EPI_SCATTER_ROWS and out is None:
         out = torch.empty((m_cap, n), dtype=torch.bfloat16, device=a.device)
     ldc = out.stride(0) if out is not None else n
-    _lib.call("slime_grouped_gemm_bf16_pair" if pair else "slime_grouped_gemm_bf16", ptr(a), ptr(b), ptr(out),
+    entry = "slime_grouped_gemm_bf16_wide" if pair == "wide" else "slime_grouped_gemm_bf16_pair" if pair else "slime_grouped_gemm_bf16"
+    _lib.call(entry, ptr(a), ptr(b), ptr(out),
               ptr(group_offsets), g, m_cap, n, k, a.stride(0), k, ldc, epilogue, ptr(row_info), scatter_bases, scatter_row_bytes, scatter_slots, ptr(row_scale),
               default_status().dev_ptr, stream_ptr())
     return out

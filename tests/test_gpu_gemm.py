@@ -30,7 +30,7 @@ def test_gemm_bf16(m, n, k):
     _check(out, ref, k)
 
 
-@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("pair", [False, True, "wide"])
 def test_grouped_gemm_store_and_swiglu(pair):
     from dlslime_b200.ops import gemm
     from dlslime_b200.ops._common import default_status
@@ -70,7 +70,7 @@ def test_grouped_gemm_store_and_swiglu(pair):
         start += sz
 
 
-@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("pair", [False, True, "wide"])
 def test_grouped_gemm_scatter_rows(pair):
     from dlslime_b200.ops import gemm
     from dlslime_b200.ops._common import default_status
@@ -107,16 +107,20 @@ def test_grouped_gemm_scatter_rows(pair):
     _check(dst, expect, k)
 
 
-@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 512, 512), (1000, 4096, 4096), (8192, 3584, 512), (4096, 1152, 256), (300, 4128, 192)])
-def test_gemm_bf16_cta_pair(m, n, k):
-    """The cta_group::2 kernel (256-row tiles on two SMs): same product, ragged edges in M and N, all three tile widths."""
+@pytest.mark.parametrize("wide", [False, True])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 512, 512), (1000, 4096, 4096), (8192, 3584, 512), (4096, 1152, 256), (300, 4128, 192),
+                                   (2048, 8192, 8192)])
+def test_gemm_bf16_cta_pair(m, n, k, wide):
+    """The cta_group::2 kernels (256-row tiles on two SMs; ``wide``: 256 x 512 tiles in two accumulator blocks): same
+    product, ragged edges in M and N (a tile whose second block lies outside N), all tile widths, several bands of
+    tile columns (the last one narrower)."""
     from dlslime_b200.ops import gemm
     from dlslime_b200.ops._common import default_status
 
     torch.manual_seed(m + n + k + 1)
     a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
     b = (torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16)
-    out = gemm.gemm_bf16_pair(a, b)
+    out = gemm.gemm_bf16_pair(a, b, wide=wide)
     torch.cuda.synchronize()
     default_status().check()
     ref = a.float() @ b.float().t()
