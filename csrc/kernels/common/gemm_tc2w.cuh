@@ -12,8 +12,9 @@
 //
 // Price: the two blocks fill all 512 tensor-memory columns, so the accumulators are not double buffered and the
 // drain of a tile is exposed. To keep it short there are eight epilogue warps, four per block: both blocks drain at
-// once, every block is handed back as soon as it is empty (the next tile's first MMAs go to block 0), and each
-// scheduler has two warps to hide the latencies of the other.
+// once, a warp first pulls its whole block into registers (packed to bf16) and hands the block back before it
+// stores anything, so what the tensor pipe waits for is the tensor-memory reads alone; the stores run under the
+// next tile's main loop.
 //
 // Shared memory per stage and CTA: A 128 x 64 (16 KB), then this CTA's half of the B rows of block 0 and of block 1
 // (BN/2 x 64 each). Four stages.
@@ -289,10 +290,13 @@ gemm_bf16_pair_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
             }
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + j * kAccStride;
+            // Drain first, store afterwards: the whole block goes to registers as packed bf16 (kBNOut / 2 words), the
+            // block is handed back to the MMA warp, and only then do the rows leave through shared memory, under the
+            // next tile's main loop.
+            uint32_t packed[kBNOut / 2];
             if (col0 < args.N) {
-#pragma unroll 1
+#pragma unroll
                 for (int c = 0; c < kBNOut; c += 64) {
-                    uint32_t o[32];
                     if (EPI == kEpiSwiGLU) {
 #pragma unroll
                         for (int hb = 0; hb < 2; ++hb) {
@@ -304,7 +308,7 @@ gemm_bf16_pair_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
                             for (int i = 0; i < 16; ++i) {
                                 const float h0 = silu(__uint_as_float(g[2 * i])) * __uint_as_float(u[2 * i]);
                                 const float h1 = silu(__uint_as_float(g[2 * i + 1])) * __uint_as_float(u[2 * i + 1]);
-                                o[hb * 16 + i] = pack_bf16(h0, h1);
+                                packed[c / 2 + hb * 16 + i] = pack_bf16(h0, h1);
                             }
                         }
                     }
@@ -315,14 +319,10 @@ gemm_bf16_pair_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            o[i]      = pack_bf16(__uint_as_float(v0[2 * i]) * scale, __uint_as_float(v0[2 * i + 1]) * scale);
-                            o[16 + i] = pack_bf16(__uint_as_float(v1[2 * i]) * scale, __uint_as_float(v1[2 * i + 1]) * scale);
+                            packed[c / 2 + i]      = pack_bf16(__uint_as_float(v0[2 * i]) * scale, __uint_as_float(v0[2 * i + 1]) * scale);
+                            packed[c / 2 + 16 + i] = pack_bf16(__uint_as_float(v1[2 * i]) * scale, __uint_as_float(v1[2 * i + 1]) * scale);
                         }
                     }
-                    int cols = args.N - (col0 + c);
-                    if (cols > 64) cols = 64;
-                    if (cols > kBNOut - c) cols = kBNOut - c;
-                    epi_store_piece(my_slot, warp_slots, o, drow + static_cast<unsigned long long>(c) * 2, do_store, cols, lane);
                 }
             }
             tc_fence_before_sync();
@@ -330,6 +330,18 @@ gemm_bf16_pair_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
                 mbar_arrive(&tempty_bar[j]);
             else
                 mbar_arrive_cluster(leader_tempty);
+            if (col0 < args.N) {
+#pragma unroll
+                for (int c = 0; c < kBNOut; c += 64) {
+                    uint32_t o[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = packed[c / 2 + i];
+                    int cols = args.N - (col0 + c);
+                    if (cols > 64) cols = 64;
+                    if (cols > kBNOut - c) cols = kBNOut - c;
+                    epi_store_piece(my_slot, warp_slots, o, drow + static_cast<unsigned long long>(c) * 2, do_store, cols, lane);
+                }
+            }
             tile_phase ^= 1;
         }
     }
