@@ -161,6 +161,14 @@ def cmd_grouped(a):
     q2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair="wide"), a.iters)
 
     extra = {}
+    row_tiles = int(((offs[1:] - offs[:-1] + 127) // 128).sum().item())
+    t1, t2 = gemm.pick_grouped_tile_n(row_tiles, inter, swiglu=True), gemm.pick_grouped_tile_n(row_tiles, k)
+    if (t1, t2) != (256, 256):  # few tiles: the width that fills the waves of the grid
+        n1, _ = timeit(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, tile_n=t1), a.iters)
+        n2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, tile_n=t2), a.iters)
+        wbytes = (w13.numel() + w2.numel()) * 2
+        extra["picked_tile_n"] = {"gate_up": t1, "down": t2, "gate_up_ms": round(n1, 4), "down_ms": round(n2, 4),
+                                  "weights_tbs": round(wbytes / (n1 + n2) / 1e9, 2), "weights_tbs_tile_256": round(wbytes / (b1 + b2) / 1e9, 2)}
     if a.sustained:
         extra["sustained_gate_up"] = {
             "single": sustained(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU), f1),

@@ -69,9 +69,21 @@ int launch_bn(const void* A, const void* B, const void* A_local, int rows_local,
     return 0;
 }
 
+thread_local int g_tile_n = 0;  // set around one grouped launch on single CTAs: tile width 128 / 192 / 224 (0 = 256)
+
 template<int EPI>
 int launch(const void* A, const void* B, const Args& args, long long lda, long long ldb, cudaStream_t stream)
 {
+    // A grouped launch with few tiles (decode-size steps on many ranks: 32 experts x 16 tile columns = 3.46 waves of 148)
+    // is quantised by the wave count; the caller, who knows the expected number of row tiles, may ask for a narrower tile.
+    if (args.group_ready == nullptr) {
+        switch (g_tile_n) {
+            case 128: return launch_bn<128, EPI, false>(A, B, nullptr, 0, args, lda, ldb, kThreads, stream);
+            case 192: return launch_bn<192, EPI, false>(A, B, nullptr, 0, args, lda, ldb, kThreads, stream);
+            case 224: return launch_bn<224, EPI, false>(A, B, nullptr, 0, args, lda, ldb, kThreads, stream);
+            default: break;
+        }
+    }
     if (EPI == kEpiStore && args.num_groups == 1) {
         switch (pick_bn(args.M_total, args.N)) {
             case 224: return launch_bn<224, kEpiStore, false>(A, B, nullptr, 0, args, lda, ldb, kThreads, stream);
@@ -385,6 +397,22 @@ int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* gr
                              scatter_row_bytes, scatter_slots, row_scale, nullptr, 0, nullptr, status, stream);
 }
 
+// The same on single CTAs with a tile width of 128, 192 or 224 columns instead of 256 (SwiGLU: half of it in output
+// columns), for launches whose tile count would otherwise leave most of the last wave empty.
+int slime_grouped_gemm_bf16_tile(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                                 int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                                 const void* row_info, const unsigned long long* scatter_bases8,
+                                 unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
+                                 const float* row_scale, int tile_n, void* status, void* stream)
+{
+    if (tile_n != 0 && tile_n != 128 && tile_n != 192 && tile_n != 224 && tile_n != 256) return fail("grouped gemm: tile width %d is not offered", tile_n);
+    g_tile_n     = tile_n == 256 ? 0 : tile_n;
+    const int rc = grouped_gemm_impl(A, B, C, group_offsets, num_groups, M_cap, N, K, lda, ldb, ldc, epilogue, row_info, scatter_bases8,
+                                     scatter_row_bytes, scatter_slots, row_scale, nullptr, 0, nullptr, status, stream);
+    g_tile_n     = 0;
+    return rc;
+}
+
 // The same on CTA pairs (256-row tiles; pays off for groups of several hundred rows and more).
 int slime_grouped_gemm_bf16_pair(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
                                  int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
@@ -480,7 +508,7 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, const int* g
             return g_on_pairs == 2 ? launch_pair_wide<kEpiStore>(A, B, a, lda, ldb, s)
                    : g_on_pairs ? launch_pair_grouped<kEpiStore>(A, B, a, lda, ldb, s) : launch<kEpiStore>(A, B, a, lda, ldb, s);
         case kEpiSwiGLU:
-            if (N % (kBN / 2) != 0) return fail("grouped gemm: SwiGLU needs N to be a multiple of %d", kBN / 2);
+            if (N % 32 != 0) return fail("grouped gemm: SwiGLU needs N to be a multiple of 32");
             a.rowsB = 2 * N;
             return g_on_pairs == 2 ? launch_pair_wide<kEpiSwiGLU>(A, B, a, lda, ldb, s)
                    : g_on_pairs ? launch_pair_grouped<kEpiSwiGLU>(A, B, a, lda, ldb, s) : launch<kEpiSwiGLU>(A, B, a, lda, ldb, s);

@@ -93,6 +93,11 @@ class ExpertParallelMoE:
         rows_per_expert = max_tokens * cfg.topk * self.world // max(1, cfg.num_experts)
         forced = os.environ.get("SLIME_EP_PAIR_GEMM")
         self.pair_gemm = (rows_per_expert >= 512) if forced is None else {"0": False, "1": True}.get(forced, forced)
+        # tile width of the single-CTA expert GEMMs (0 = 256). Narrower tiles were measured for the decode-size step on
+        # many ranks (32 experts x 32 rows: 512 tiles = 3.46 waves of the grid) and do not pay: those GEMMs stream weights
+        # from HBM, the CTAs do not wait for one another between waves, and a short last wave still fills the memory
+        # system (5.66 TB/s of weights with 256-wide tiles, 5.53 with the widths that fill the waves).
+        self.tile_n_gate_up = self.tile_n_down = int(os.environ.get("SLIME_EP_TILE_N", "0"))
         cap = self.buf.recv_cap
         self.xd = torch.empty((cap, cfg.hidden), dtype=torch.bfloat16, device=dev)
         self.h = torch.empty((cap, cfg.intermediate), dtype=torch.bfloat16, device=dev)
@@ -122,13 +127,14 @@ class ExpertParallelMoE:
                                    epilogue=gemm.EPI_SWIGLU)
             return
         gemm.grouped_gemm_bf16(self.xd, self.w_gate_up, self.buf.group_offsets, out=self.h, epilogue=gemm.EPI_SWIGLU,
-                               pair=self.pair_gemm)
+                               pair=self.pair_gemm, tile_n=self.tile_n_gate_up)
 
     def step_down(self):
         c = self.cfg
         gemm.grouped_gemm_bf16(self.h, self.w_down, self.buf.group_offsets, epilogue=gemm.EPI_SCATTER_ROWS,
                                row_info=self.buf.recv_info, scatter_bases=self._bases,
-                               scatter_row_bytes=c.hidden * 2, scatter_slots=self.max_tokens * c.topk, pair=self.pair_gemm)
+                               scatter_row_bytes=c.hidden * 2, scatter_slots=self.max_tokens * c.topk, pair=self.pair_gemm,
+                               tile_n=self.tile_n_down)
 
     def step_experts(self, T, epoch):
         self.step_recv(T, epoch)

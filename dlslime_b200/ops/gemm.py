@@ -63,10 +63,26 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
     return out
 
 
+def pick_grouped_tile_n(row_tiles: int, n_out: int, swiglu: bool = False, sms: int = 148) -> int:
+    """Tile width (256, 224, 192 or 128 columns of the weight; SwiGLU: half as many output columns) for a grouped GEMM on
+    single CTAs that is expected to have ``row_tiles`` 128-row tiles in total: the width whose tile count wastes the least
+    of the last wave of the persistent grid (cost = waves x (width + a per-tile overhead in columns); ties go to the wider
+    tile). Only for compute-bound launches: a weight-streaming launch (few rows per group) gains nothing from full waves,
+    since its CTAs never wait for one another and a short last wave still saturates HBM (measured)."""
+    best, best_cost = 256, None
+    for width in (256, 224, 192, 128):
+        out = width // 2 if swiglu else width
+        tiles = max(1, row_tiles) * -(-n_out // out)
+        cost = -(-tiles // sms) * (width + 16)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = width, cost
+    return best
+
+
 def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor, out: torch.Tensor | None = None,
                       epilogue: int = EPI_STORE, row_info: torch.Tensor | None = None, scatter_bases=None,
                       scatter_row_bytes: int = 0, scatter_slots: int = 0,
-                      row_scale: torch.Tensor | None = None, pair: bool | str = False) -> torch.Tensor | None:
+                      row_scale: torch.Tensor | None = None, pair: bool | str = False, tile_n: int = 0) -> torch.Tensor | None:
     """Grouped GEMM over consecutive row groups of ``a``.
 
     ``a`` is ``[M_cap, K]``; ``group_offsets`` is an int32 device tensor of
@@ -81,7 +97,8 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
     ``pair`` runs the kernel on CTA pairs (256-row tiles, a third less traffic between L2 and the SMs): the faster form
     for groups of several hundred rows and more, the slower one for small groups (the last tile of a group computes
     up to 255 unused rows instead of up to 127). ``pair="wide"``: CTA pairs with 256 x 512 tiles, another quarter less
-    traffic per FLOP, which is what raises the clock under the power limit.
+    traffic per FLOP, which is what raises the clock under the power limit. ``tile_n`` (single CTAs only): tile width 128,
+    192 or 224 instead of 256, see :func:`pick_grouped_tile_n`.
     """
     require_cuda(a, b, group_offsets)
     assert a.dtype == b.dtype == torch.bfloat16 and group_offsets.dtype == torch.int32
@@ -93,6 +110,11 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
     if epilogue != EPI_SCATTER_ROWS and out is None:
         out = torch.empty((m_cap, n), dtype=torch.bfloat16, device=a.device)
     ldc = out.stride(0) if out is not None else n
+    if not pair and tile_n not in (0, 256):
+        _lib.call("slime_grouped_gemm_bf16_tile", ptr(a), ptr(b), ptr(out), ptr(group_offsets), g, m_cap, n, k, a.stride(0), k, ldc,
+                  epilogue, ptr(row_info), scatter_bases, scatter_row_bytes, scatter_slots, ptr(row_scale), int(tile_n),
+                  default_status().dev_ptr, stream_ptr())
+        return out
     entry = "slime_grouped_gemm_bf16_wide" if pair == "wide" else "slime_grouped_gemm_bf16_pair" if pair else "slime_grouped_gemm_bf16"
     _lib.call(entry, ptr(a), ptr(b), ptr(out),
               ptr(group_offsets), g, m_cap, n, k, a.stride(0), k, ldc, epilogue, ptr(row_info), scatter_bases, scatter_row_bytes, scatter_slots, ptr(row_scale),

@@ -70,6 +70,44 @@ def test_grouped_gemm_store_and_swiglu(pair):
         start += sz
 
 
+@pytest.mark.parametrize("tile_n", [128, 192, 224])
+def test_grouped_gemm_narrow_tiles(tile_n):
+    """The single-CTA grouped GEMM with tile widths other than 256: store, SwiGLU (an output width that the half tile does
+    not divide) and scatter epilogues against the fp32 product."""
+    import ctypes
+
+    from dlslime_b200.ops import gemm
+    from dlslime_b200.ops._common import default_status
+
+    torch.manual_seed(tile_n)
+    sizes = [3, 0, 130, 257, 64]
+    g, k, n = len(sizes), 384, 448
+    total = sum(sizes)
+    offs = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device="cuda")
+    a = torch.randn(total, k, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(g, n, k, device="cuda") * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(g, 2 * n, k, device="cuda") * 0.05).to(torch.bfloat16)
+    out = gemm.grouped_gemm_bf16(a, w, offs, tile_n=tile_n)
+    h = gemm.grouped_gemm_bf16(a, w2, offs, epilogue=gemm.EPI_SWIGLU, tile_n=tile_n)
+    dst = torch.zeros(total, n, device="cuda", dtype=torch.bfloat16)
+    perm = torch.randperm(total, device="cuda")
+    bases = (ctypes.c_ulonglong * 8)()
+    bases[0] = dst.data_ptr()
+    gemm.grouped_gemm_bf16(a, w, offs, epilogue=gemm.EPI_SCATTER_ROWS, row_info=perm.to(torch.int64), scatter_bases=bases,
+                           scatter_row_bytes=n * 2, scatter_slots=total, tile_n=tile_n)
+    torch.cuda.synchronize()
+    default_status().check()
+    start = 0
+    for gi, sz in enumerate(sizes):
+        if sz:
+            x = a[start:start + sz].float()
+            ref = x @ w[gi].float().t()
+            _check(out[start:start + sz], ref, k)
+            _check(dst[perm[start:start + sz]], ref, k)
+            _check(h[start:start + sz], torch.nn.functional.silu(x @ w2[gi, :n].float().t()) * (x @ w2[gi, n:].float().t()), k)
+        start += sz
+
+
 @pytest.mark.parametrize("pair", [False, True, "wide"])
 def test_grouped_gemm_scatter_rows(pair):
     from dlslime_b200.ops import gemm
