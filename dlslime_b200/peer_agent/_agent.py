@@ -722,21 +722,33 @@ class PeerAgent:
     def _is_named(a: Any) -> bool:
         return isinstance(a, (tuple, list)) and len(a) in (4, 5) and isinstance(a[0], str)
 
-    def _endpoint_assign(self, conn: DirectedConnection, a) -> tuple:
+    def _endpoint_assign(self, conn: DirectedConnection, a, local_handles: Optional[dict] = None,
+                         remote_handles: Optional[dict] = None) -> tuple:
         """``(region, local_off, remote_off, len)`` or ``(local_region, remote_region, local_off, remote_off, len)``
-        -> the endpoint tuple ``(local_handle, remote_handle, remote_off, local_off, len)``."""
+        -> the endpoint tuple ``(local_handle, remote_handle, remote_off, local_off, len)``. The two dicts memoise the
+        handles of one call: a region is resolved (and a remote one checked against the directory) once per call, not
+        once per piece."""
         if len(a) == 4:
             local_name = remote_name = a[0]
             local_off, remote_off, length = a[1], a[2], a[3]
         else:
             local_name, remote_name, local_off, remote_off, length = a
-        return (self.get_handle(conn, local_name), self.get_handle(conn, remote_name, remote=True), int(remote_off), int(local_off), int(length))
+        local_handles = {} if local_handles is None else local_handles
+        remote_handles = {} if remote_handles is None else remote_handles
+        lh = local_handles.get(local_name)
+        if lh is None:
+            lh = local_handles[local_name] = self.get_handle(conn, local_name)
+        rh = remote_handles.get(remote_name)
+        if rh is None:
+            rh = remote_handles[remote_name] = self.get_handle(conn, remote_name, remote=True)
+        return (lh, rh, int(remote_off), int(local_off), int(length))
 
     def _maybe_endpoint_assign(self, conn: DirectedConnection, assign):
         if self._is_named(assign):
             return [self._endpoint_assign(conn, assign)]
         if isinstance(assign, (list, tuple)) and assign and self._is_named(assign[0]):
-            return [self._endpoint_assign(conn, a) for a in assign]
+            local_handles, remote_handles = {}, {}
+            return [self._endpoint_assign(conn, a, local_handles, remote_handles) for a in assign]
         return assign
 
     def _io(self, op: str, peer_alias: str, assign, stream, local_nic, remote_nic, **kw):
