@@ -478,7 +478,7 @@ def run_ours(args, rank, world, local):
         "weights_gb": (layer.w_gate_up.numel() + layer.w_down.numel()) * 2 / 1e9,
         "notes": {"dequant": "in the gate/up GEMM's A-tile loader" if args.fuse_dequant else "separate pass",
                   "phases": "dispatch, receive and gate/up GEMM at the same time (per-expert arrival words)" if layer.streamed else "one after the other",
-                  "expert_gemm": {False: "single CTAs, 128 x 256 tiles", True: "CTA pairs, 256 x 256 tiles", "wide": "CTA pairs, 256 x 512 tiles"}[layer.pair_gemm],
+                  "expert_gemm": {False: "single CTAs, 128 x 256 tiles", True: "CTA pairs, 256 x 256 tiles", "wide": "CTA pairs, 256 x 512 tiles", "swap": "CTA pairs, operands swapped: 256 weight rows x up to 256 tokens"}[layer.pair_gemm],
                   "phases_autotune": tuned,
                   "transport": "in-kernel stores and bulk copies to NVLink peer memory"},
     })

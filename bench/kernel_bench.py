@@ -159,6 +159,8 @@ def cmd_grouped(a):
     p2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair=True), a.iters)
     q1, _ = timeit(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair="wide"), a.iters)
     q2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair="wide"), a.iters)
+    s1, _ = timeit(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair="swap"), a.iters)
+    s2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair="swap"), a.iters)
 
     extra = {}
     row_tiles = int(((offs[1:] - offs[:-1] + 127) // 128).sum().item())
@@ -173,11 +175,13 @@ def cmd_grouped(a):
         extra["sustained_gate_up"] = {
             "single": sustained(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU), f1),
             "pair": sustained(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair=True), f1),
-            "wide": sustained(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair="wide"), f1)}
+            "wide": sustained(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair="wide"), f1),
+            "swap": sustained(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair="swap"), f1)}
         extra["sustained_down"] = {
             "single": sustained(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y), f2),
             "pair": sustained(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair=True), f2),
-            "wide": sustained(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair="wide"), f2)}
+            "wide": sustained(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair="wide"), f2),
+            "swap": sustained(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair="swap"), f2)}
 
     def cublas_loop():
         for e in range(g):
@@ -190,6 +194,9 @@ def cmd_grouped(a):
                       "pair_gate_up_ms": round(p1, 4), "pair_gate_up_tflops": round(f1 / p1 / 1e9, 1),
                       "pair_down_ms": round(p2, 4), "pair_down_tflops": round(f2 / p2 / 1e9, 1),
                       "pair_frac_of_peak": round((f1 + f2) / (p1 + p2) / 1e9 / tf, 3),
+                      "swap_gate_up_ms": round(s1, 4), "swap_gate_up_tflops": round(f1 / s1 / 1e9, 1),
+                      "swap_down_ms": round(s2, 4), "swap_down_tflops": round(f2 / s2 / 1e9, 1),
+                      "swap_frac_of_peak": round((f1 + f2) / (s1 + s2) / 1e9 / tf, 3),
                       "wide_gate_up_ms": round(q1, 4), "wide_gate_up_tflops": round(f1 / q1 / 1e9, 1),
                       "wide_down_ms": round(q2, 4), "wide_down_tflops": round(f2 / q2 / 1e9, 1),
                       "wide_frac_of_peak": round((f1 + f2) / (q1 + q2) / 1e9 / tf, 3),

@@ -101,6 +101,12 @@ int slime_grouped_gemm_bf16_pair(const void* A, const void* B, void* C, const in
                                  const void* row_info, const unsigned long long* scatter_bases8,
                                  unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
                                  const float* row_scale, void* status, void* stream);
+// The same on CTA pairs with swapped operands (weight rows on the M side of the MMA, a group's tokens on the N side).
+int slime_grouped_gemm_bf16_swapped(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                                    int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                                    const void* row_info, const unsigned long long* scatter_bases8,
+                                    unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
+                                    const float* row_scale, void* status, void* stream);
 // The same on CTA pairs with 256 x 512 tiles (two accumulator blocks that share the A tile).
 int slime_grouped_gemm_bf16_wide(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
                                  int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,

@@ -2,6 +2,7 @@
 // synthetic prefill stand-in), a grouped GEMM over device-side row groups (the
 // expert FFN), its SwiGLU-fused variant, and a variant whose epilogue scatters
 // weighted rows to arbitrary (possibly peer) addresses.
+#include "common/gemm_tc2s.cuh"
 #include "common/gemm_tc2w.cuh"
 #include "common/host_utils.h"
 #include "slime_cuda.h"
@@ -199,6 +200,27 @@ int launch_pair_grouped(const void* A, const void* B, const Args& args, long lon
         configured = true;
     }
     kern<<<2 * (sm_count() / 2), kThreads, S::kTotal, stream>>>(tmA, tmB, args);
+    SLIME_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+// CTA pairs with swapped operands: weight rows on the M side, a group's tokens (any multiple of 16 up to 256) on the N side.
+template<int EPI>
+int launch_pair_swapped(const void* A, const void* B, const Args& args, long long lda, long long ldb, cudaStream_t stream)
+{
+    constexpr int kSwapStages = 6;
+    using S = SmemSwap<kSwapStages>;
+    CUtensorMap tmW, tmX;
+    const unsigned long long rowsB_total = static_cast<unsigned long long>(args.rowsB) * args.num_groups;
+    if (make_tmap_2d(&tmX, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.M_total, args.K, lda, kBM, kBK)) return -1;
+    if (make_tmap_2d(&tmW, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rowsB_total, args.K, ldb, EPI == kEpiSwiGLU ? kBM / 2 : kBM, kBK)) return -1;
+    auto kern = gemm_bf16_pair_swapped_kernel<kSwapStages, EPI>;
+    static bool configured = false;
+    if (!configured) {
+        SLIME_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+        configured = true;
+    }
+    kern<<<2 * (sm_count() / 2), kThreads, S::kTotal, stream>>>(tmW, tmX, args);
     SLIME_CUDA_OK(cudaGetLastError());
     return 0;
 }
@@ -427,6 +449,22 @@ int slime_grouped_gemm_bf16_pair(const void* A, const void* B, void* C, const in
     return rc;
 }
 
+// The same on CTA pairs with the operands swapped (weights on the M side of the MMA, a group's tokens on the N side in
+// steps of 16): no rows are computed for nothing and a group of up to 256 rows reads its weights once.
+int slime_grouped_gemm_bf16_swapped(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
+                                    int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
+                                    const void* row_info, const unsigned long long* scatter_bases8,
+                                    unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
+                                    const float* row_scale, void* status, void* stream)
+{
+    if (ldc % 4 != 0 || scatter_row_bytes % 8 != 0) return fail("swapped grouped gemm: rows of the output must be 8-byte aligned");
+    g_on_pairs   = 3;
+    const int rc = grouped_gemm_impl(A, B, C, group_offsets, num_groups, M_cap, N, K, lda, ldb, ldc, epilogue, row_info, scatter_bases8,
+                                     scatter_row_bytes, scatter_slots, row_scale, nullptr, 0, nullptr, status, stream);
+    g_on_pairs   = 0;
+    return rc;
+}
+
 // The same on CTA pairs with 256 x 512 tiles: a quarter less traffic from L2 into shared memory per FLOP, which is
 // what counts once the kernel runs against the power limit.
 int slime_grouped_gemm_bf16_wide(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
@@ -505,12 +543,14 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, const int* g
     switch (epilogue) {
         case kEpiStore:
             a.rowsB = N;
-            return g_on_pairs == 2 ? launch_pair_wide<kEpiStore>(A, B, a, lda, ldb, s)
+            return g_on_pairs == 3 ? launch_pair_swapped<kEpiStore>(A, B, a, lda, ldb, s)
+                   : g_on_pairs == 2 ? launch_pair_wide<kEpiStore>(A, B, a, lda, ldb, s)
                    : g_on_pairs ? launch_pair_grouped<kEpiStore>(A, B, a, lda, ldb, s) : launch<kEpiStore>(A, B, a, lda, ldb, s);
         case kEpiSwiGLU:
             if (N % 32 != 0) return fail("grouped gemm: SwiGLU needs N to be a multiple of 32");
             a.rowsB = 2 * N;
-            return g_on_pairs == 2 ? launch_pair_wide<kEpiSwiGLU>(A, B, a, lda, ldb, s)
+            return g_on_pairs == 3 ? launch_pair_swapped<kEpiSwiGLU>(A, B, a, lda, ldb, s)
+                   : g_on_pairs == 2 ? launch_pair_wide<kEpiSwiGLU>(A, B, a, lda, ldb, s)
                    : g_on_pairs ? launch_pair_grouped<kEpiSwiGLU>(A, B, a, lda, ldb, s) : launch<kEpiSwiGLU>(A, B, a, lda, ldb, s);
         case kEpiScatterRows:
             if (row_info == nullptr || scatter_bases8 == nullptr) return fail("grouped gemm: scatter epilogue needs row_info and bases");
@@ -521,7 +561,8 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, const int* g
             for (int i = 0; i < 8; ++i) a.scatter_base[i] = scatter_bases8[i];
             a.scatter_row_bytes = scatter_row_bytes;
             a.scatter_slots     = scatter_slots;
-            return g_on_pairs == 2 ? launch_pair_wide<kEpiScatterRows>(A, B, a, lda, ldb, s)
+            return g_on_pairs == 3 ? launch_pair_swapped<kEpiScatterRows>(A, B, a, lda, ldb, s)
+                   : g_on_pairs == 2 ? launch_pair_wide<kEpiScatterRows>(A, B, a, lda, ldb, s)
                    : g_on_pairs ? launch_pair_grouped<kEpiScatterRows>(A, B, a, lda, ldb, s)
                                 : launch<kEpiScatterRows>(A, B, a, lda, ldb, s);
         default:

@@ -55,6 +55,7 @@ _SIGNATURES = {
 }
 _SIGNATURES["slime_grouped_gemm_bf16_pair"] = _SIGNATURES["slime_grouped_gemm_bf16"]
 _SIGNATURES["slime_grouped_gemm_bf16_wide"] = _SIGNATURES["slime_grouped_gemm_bf16"]
+_SIGNATURES["slime_grouped_gemm_bf16_swapped"] = _SIGNATURES["slime_grouped_gemm_bf16"]
 _SIGNATURES["slime_gemm_bf16_wide"] = _SIGNATURES["slime_gemm_bf16_pair"]
 _SIGNATURES["slime_grouped_gemm_bf16_tile"] = [*_SIGNATURES["slime_grouped_gemm_bf16"][:-2], c_int, c_void_p, c_void_p]
 

@@ -204,7 +204,7 @@ class ExpertParallelMoE:
         if self.fuse_dequant:
             return {"streamed": False, "reason": "the fused-dequant GEMM has no streamed form"}
         times = {}
-        kinds = {"single": False, "pair": True, "wide": "wide"}
+        kinds = {"single": False, "pair": True, "wide": "wide", "swap": "swap"}
         for form in (*kinds, True):
             if form is True:
                 best = min(kinds, key=lambda k: times[k])
@@ -232,7 +232,7 @@ class ExpertParallelMoE:
         self.streamed = times[True] < times[False]
         return {"streamed": self.streamed, "pair_gemm": self.pair_gemm, "serial_ms": round(times[False], 4),
                 "serial_single_cta_ms": round(times["single"], 4), "serial_cta_pair_ms": round(times["pair"], 4),
-                "serial_cta_pair_wide_ms": round(times["wide"], 4),
+                "serial_cta_pair_wide_ms": round(times["wide"], 4), "serial_cta_pair_swapped_ms": round(times["swap"], 4),
                 "streamed_ms": round(times[True], 4)}
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

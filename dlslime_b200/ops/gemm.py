@@ -97,7 +97,9 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
     ``pair`` runs the kernel on CTA pairs (256-row tiles, a third less traffic between L2 and the SMs): the faster form
     for groups of several hundred rows and more, the slower one for small groups (the last tile of a group computes
     up to 255 unused rows instead of up to 127). ``pair="wide"``: CTA pairs with 256 x 512 tiles, another quarter less
-    traffic per FLOP, which is what raises the clock under the power limit. ``tile_n`` (single CTAs only): tile width 128,
+    traffic per FLOP, which is what raises the clock under the power limit. ``pair="swap"``: CTA pairs with the operands
+    swapped (weight rows on the M side of the MMA, the tokens of a group on the N side in steps of 16): nothing is computed
+    for rows that do not exist, and a group of up to 256 rows passes over its weights once. ``tile_n`` (single CTAs only): tile width 128,
     192 or 224 instead of 256, see :func:`pick_grouped_tile_n`.
     """
     require_cuda(a, b, group_offsets)
@@ -115,7 +117,7 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
                   epilogue, ptr(row_info), scatter_bases, scatter_row_bytes, scatter_slots, ptr(row_scale), int(tile_n),
                   default_status().dev_ptr, stream_ptr())
         return out
-    entry = "slime_grouped_gemm_bf16_wide" if pair == "wide" else "slime_grouped_gemm_bf16_pair" if pair else "slime_grouped_gemm_bf16"
+    entry = "slime_grouped_gemm_bf16_swapped" if pair == "swap" else "slime_grouped_gemm_bf16_wide" if pair == "wide" else "slime_grouped_gemm_bf16_pair" if pair else "slime_grouped_gemm_bf16"
     _lib.call(entry, ptr(a), ptr(b), ptr(out),
               ptr(group_offsets), g, m_cap, n, k, a.stride(0), k, ldc, epilogue, ptr(row_info), scatter_bases, scatter_row_bytes, scatter_slots, ptr(row_scale),
               default_status().dev_ptr, stream_ptr())

@@ -30,7 +30,7 @@ def test_gemm_bf16(m, n, k):
     _check(out, ref, k)
 
 
-@pytest.mark.parametrize("pair", [False, True, "wide"])
+@pytest.mark.parametrize("pair", [False, True, "wide", "swap"])
 def test_grouped_gemm_store_and_swiglu(pair):
     from dlslime_b200.ops import gemm
     from dlslime_b200.ops._common import default_status
@@ -108,7 +108,7 @@ def test_grouped_gemm_narrow_tiles(tile_n):
         start += sz
 
 
-@pytest.mark.parametrize("pair", [False, True, "wide"])
+@pytest.mark.parametrize("pair", [False, True, "wide", "swap"])
 def test_grouped_gemm_scatter_rows(pair):
     from dlslime_b200.ops import gemm
     from dlslime_b200.ops._common import default_status
