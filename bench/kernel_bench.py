@@ -171,6 +171,14 @@ def cmd_grouped(a):
         wbytes = (w13.numel() + w2.numel()) * 2
         extra["picked_tile_n"] = {"gate_up": t1, "down": t2, "gate_up_ms": round(n1, 4), "down_ms": round(n2, 4),
                                   "weights_tbs": round(wbytes / (n1 + n2) / 1e9, 2), "weights_tbs_tile_256": round(wbytes / (b1 + b2) / 1e9, 2)}
+    if a.prefetch:  # weight prefetch into L2, for the weight-streaming shapes
+        extra["w_prefetch"] = {}
+        wbytes = (w13.numel() + w2.numel()) * 2
+        for d in (4, 8, 16, 32):
+            n1, _ = timeit(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, w_prefetch=d), a.iters)
+            n2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, w_prefetch=d), a.iters)
+            extra["w_prefetch"][d] = {"gate_up_ms": round(n1, 4), "down_ms": round(n2, 4), "weights_tbs": round(wbytes / (n1 + n2) / 1e9, 2)}
+        extra["w_prefetch"][0] = {"gate_up_ms": round(b1, 4), "down_ms": round(b2, 4), "weights_tbs": round(wbytes / (b1 + b2) / 1e9, 2)}
     if a.sustained:
         extra["sustained_gate_up"] = {
             "single": sustained(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU), f1),
@@ -234,6 +242,7 @@ if __name__ == "__main__":
     ap.add_argument("--experts", type=int, default=32)
     ap.add_argument("--rows", type=int, default=1024)
     ap.add_argument("--sustained", action="store_true", help="gemm, grouped: also loop each kernel for seconds and sample clock and power")
+    ap.add_argument("--prefetch", action="store_true", help="grouped: also time the single-CTA kernels with the weight prefetch into L2")
     ap.add_argument("--ragged", action="store_true", help="grouped: multinomial group sizes instead of equal ones")
     ap.add_argument("--rows-q", type=int, default=32768)
     ap.add_argument("--iters", type=int, default=10)

@@ -76,6 +76,13 @@ struct Args {
     // optional trace (u64 [2 * num_groups + gridDim.x], device memory): CTA 0's producer records, per group, when it
     // began to wait for the group and when the group was ready (globaltimer ns); behind that, every CTA's start time
     unsigned long long*       group_trace;
+    // weight-streaming launches (few rows per group): the producer asks L2 for the B boxes this many K blocks ahead of
+    // its loads, into the CTA's next tile too, so that more bytes are in flight from HBM than the shared-memory ring
+    // holds (0 = off; static tile order only). Measured on the weight-streaming shapes it LOSES at every distance (256
+    // experts x ~128 rows: 5.31 TB/s of weights without, 4.68 / 4.03 / 3.43 / 3.11 TB/s at 4 / 8 / 16 / 32 blocks; 32 x 32
+    // rows: 5.52 against 5.02 and less): 148 CTAs with four 48 KB stages already keep HBM busy, and the extra requests
+    // only disturb the order in which it is read. Off everywhere; kept as an option of the launcher.
+    int                       w_prefetch;
     // A operand as e4m3 with 1x128 scales (kernels instantiated with A8): the tile is expanded to bf16 in shared memory
     const float*              a_scale;         // [M_total, K / 128]
     KernelStatus*             status;
@@ -489,6 +496,10 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 args.group_ready == nullptr ? 0ull : (args.group_ready_epoch ? *reinterpret_cast<const volatile unsigned long long*>(args.group_ready_epoch) : args.group_ready_target);
             TileFeed feed(args, tile_ring, tr_full, tr_empty);
             bool     ended = false;
+            // the tile after the current one, for the weight prefetch (static order: every gridDim-th tile)
+            const int  pf_dist = (args.tile_counter == nullptr && args.w_prefetch > 0) ? (args.w_prefetch < kblocks ? args.w_prefetch : kblocks) : 0;
+            TileWalker peek(args, kBNOut);
+            TileCoord  tn;
             // behind the per-group pairs, the trace holds one start time per CTA
             if (args.group_trace != nullptr) args.group_trace[2 * args.num_groups + blockIdx.x] = globaltimer_ns();
             while (ok) {
@@ -542,7 +553,34 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     yb0 = tc.group * args.rowsB + tc.nt * BN;
                     yb1 = yb0 + BN / 2;
                 }
+                int  nb0 = 0, nb1 = 0;
+                bool have_next = false;
+                if (pf_dist) {
+                    have_next = peek.at(lt + static_cast<int>(gridDim.x), tn);
+                    if (have_next) {
+                        if (EPI == kEpiSwiGLU) {
+                            nb0 = tn.group * args.rowsB + tn.nt * (BN / 2);
+                            nb1 = nb0 + args.N;
+                        }
+                        else {
+                            nb0 = tn.group * args.rowsB + tn.nt * BN;
+                            nb1 = nb0 + BN / 2;
+                        }
+                        have_next = nb0 != yb0;  // the same weight rows again (another row tile of the group): L2 has them
+                    }
+                }
                 for (int kb = 0; kb < kblocks; ++kb) {
+                    if (pf_dist) {
+                        const int pk = kb + pf_dist;
+                        if (pk < kblocks) {
+                            tma_prefetch_l2_2d(&tmB, pk * kBK, yb0);
+                            tma_prefetch_l2_2d(&tmB, pk * kBK, yb1);
+                        }
+                        else if (have_next) {
+                            tma_prefetch_l2_2d(&tmB, (pk - kblocks) * kBK, nb0);
+                            tma_prefetch_l2_2d(&tmB, (pk - kblocks) * kBK, nb1);
+                        }
+                    }
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, st, 1, stage, lim)) {
                         ok = false;
                         break;

@@ -70,7 +70,8 @@ int launch_bn(const void* A, const void* B, const void* A_local, int rows_local,
     return 0;
 }
 
-thread_local int g_tile_n = 0;  // set around one grouped launch on single CTAs: tile width 128 / 192 / 224 (0 = 256)
+thread_local int g_tile_n     = 0;  // set around one grouped launch on single CTAs: tile width 128 / 192 / 224 (0 = 256)
+thread_local int g_w_prefetch = 0;  // and the distance of its weight prefetch in K blocks (0 = none)
 
 template<int EPI>
 int launch(const void* A, const void* B, const Args& args, long long lda, long long ldb, cudaStream_t stream)
@@ -419,19 +420,23 @@ int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* gr
                              scatter_row_bytes, scatter_slots, row_scale, nullptr, 0, nullptr, status, stream);
 }
 
-// The same on single CTAs with a tile width of 128, 192 or 224 columns instead of 256 (SwiGLU: half of it in output
-// columns), for launches whose tile count would otherwise leave most of the last wave empty.
+// The same on single CTAs with options: a tile width of 128, 192 or 224 columns instead of 256 (SwiGLU: half of it in
+// output columns), and a weight prefetch into L2 w_prefetch K blocks ahead of the loads (for launches with few rows per
+// group, which stream their weights from HBM).
 int slime_grouped_gemm_bf16_tile(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
                                  int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
                                  const void* row_info, const unsigned long long* scatter_bases8,
                                  unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
-                                 const float* row_scale, int tile_n, void* status, void* stream)
+                                 const float* row_scale, int tile_n, int w_prefetch, void* status, void* stream)
 {
     if (tile_n != 0 && tile_n != 128 && tile_n != 192 && tile_n != 224 && tile_n != 256) return fail("grouped gemm: tile width %d is not offered", tile_n);
+    if (w_prefetch < 0 || w_prefetch > 64) return fail("grouped gemm: weight prefetch distance %d not in [0, 64]", w_prefetch);
     g_tile_n     = tile_n == 256 ? 0 : tile_n;
+    g_w_prefetch = w_prefetch;
     const int rc = grouped_gemm_impl(A, B, C, group_offsets, num_groups, M_cap, N, K, lda, ldb, ldc, epilogue, row_info, scatter_bases8,
                                      scatter_row_bytes, scatter_slots, row_scale, nullptr, 0, nullptr, status, stream);
     g_tile_n     = 0;
+    g_w_prefetch = 0;
     return rc;
 }
 
@@ -531,6 +536,7 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, const int* g
     a.group_ready_epoch  = group_ready_epoch;
     a.group_trace        = g_group_trace;
     a.tile_counter       = g_tile_counter;
+    a.w_prefetch         = g_w_prefetch;
     a.M_total       = M_cap;
     a.N             = N;
     a.K             = K;
