@@ -197,9 +197,12 @@ __global__ void __launch_bounds__(256) ep_route_kernel(EpConfig cfg, const float
             const unsigned int       cnt  = atomicExch(&send_count[e], 0u);
             const unsigned long long word = (epoch << 32) | cnt;
             s_cnt[e]                      = cnt;
+            // The word carries its own step tag and publishes nothing but itself, so a relaxed store is enough. With release
+            // semantics every one of the (up to eight) stores of a thread waited for the one before it to be performed
+            // at its peer, which made this kernel take 40-50 us on 8 GPUs against 15 us on one.
             for (int p = 0; p < cfg.world; ++p) {
                 unsigned long long* dst = at<unsigned long long>(cfg, p, cfg.off_counts) + cfg.rank * E + e;
-                st_release_sys(dst, word);
+                st_relaxed_sys(dst, word);
             }
         }
         if (push_off != nullptr) {
