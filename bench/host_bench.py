@@ -200,11 +200,13 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("cmd", choices=["io", "sendrecv", "rpc", "cache", "torch"])
     ap.add_argument("--transport", default="tcp", choices=["tcp", "rdma"])
-    ap.add_argument("--sizes", default="4096,65536,1048576,16777216")
+    ap.add_argument("--sizes", default=None, help="default: 4096,65536,1048576,16777216 (rpc: 64,4096,65536,1048576, its slots hold 2 MiB)")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--concurrency", type=int, default=1, help="io: operations kept in flight per iteration")
     ap.add_argument("--qp", type=int, default=2)
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--length", type=int, default=16 << 20)
     a = ap.parse_args()
+    if a.sizes is None:
+        a.sizes = "64,4096,65536,1048576" if a.cmd == "rpc" else "4096,65536,1048576,16777216"
     {"io": cmd_io, "sendrecv": cmd_sendrecv, "rpc": cmd_rpc, "cache": cmd_cache, "torch": cmd_torch}[a.cmd](a)
