@@ -208,7 +208,19 @@ class NanoCtrlRegistration:
 
 
 class CacheServer:
-    """Everything a cache process needs: PeerAgent, service, HTTP server and NanoCtrl registration."""
+    """Everything a cache process needs: PeerAgent, service, HTTP server and NanoCtrl registration.
+
+    Called the way the reference's ``dlslime.cache.CacheServer`` is called (nothing but ``slab_size`` / ``memory_size``,
+    by keyword or as the two positional numbers) it returns the slab directory itself, which is what that name means
+    there (``dlslime/cache/__init__.py:23`` in the reference); the directory is also ``dlslime_b200.cache.CacheDirectory``.
+    """
+
+    def __new__(cls, ctrl=None, *args, **kw):
+        process_keys = {"host", "port", "scope", "alias", "device", "metadata_only"}
+        if (ctrl is None or isinstance(ctrl, int)) and not (process_keys & kw.keys()):
+            numbers = ([ctrl] if isinstance(ctrl, int) else []) + list(args)
+            return _cache.CacheServer(*numbers, **kw)
+        return super().__new__(cls)
 
     def __init__(self, ctrl: str | None = None, *, host: str = "127.0.0.1", port: int = 0, slab_size: int = DEFAULT_SLAB_SIZE,
                  memory_size: int = DEFAULT_MEMORY_SIZE, scope: str | None = None, alias: str | None = None,

@@ -23,6 +23,11 @@ def assignment_from_json(d: dict[str, Any]) -> Assignment:
                       int(d["source_offset"]), int(d["length"]))
 
 
+def assignment_to_tuple(a: Assignment) -> tuple[int, int, int, int, int]:
+    """``(mr_key, remote_mr_key, target_offset, source_offset, length)``, the order the endpoints take."""
+    return tuple(int(getattr(a, k)) for k in ("mr_key", "remote_mr_key", "target_offset", "source_offset", "length"))
+
+
 def manifest_to_json(m) -> dict[str, Any]:
     return {"peer_agent_id": m.peer_agent_id, "version": int(m.version), "total_bytes": int(m.total_bytes()),
             "slab_ids": [int(s) for s in m.slab_ids], "assignments": [assignment_to_json(a) for a in m.assignments]}

@@ -64,3 +64,16 @@ def test_stats_delete_clear_and_empty_peer():
     s.clear()
     assert s.stats().num_assignment_entries == 0
     assert s.store_assignments("a", [Assignment(1, 2, 0, 0, 64)]).version == 1
+
+
+def test_package_level_names_match_the_reference():
+    """``dlslime.cache`` in the reference exports the directory as ``CacheServer`` and a few helpers: the same calls work
+    on this package (``dlslime/cache/__init__.py:22-45`` in the reference)."""
+    import dlslime_b200.cache as pkg
+
+    d = pkg.CacheServer(slab_size=128 * K, memory_size=512 * K)
+    assert isinstance(d, cache.CacheServer) and d.num_slabs() == 4
+    assert isinstance(pkg.CacheServer(), cache.CacheServer) and isinstance(pkg.CacheServer(128 * K, 256 * K), cache.CacheServer)
+    assert pkg.ccache is cache and pkg.CacheDirectory is cache.CacheServer
+    assert pkg.assignment_to_tuple(Assignment(1, 2, 3, 4, 5)) == (1, 2, 3, 4, 5)
+    assert pkg.resolve_host_for_registration("10.0.0.1") == "10.0.0.1" and pkg.resolve_host_for_registration("0.0.0.0")
