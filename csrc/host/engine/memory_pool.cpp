@@ -37,9 +37,22 @@ int32_t LocalMemoryPool::register_memory_region(uintptr_t addr, uint64_t length,
         if (name && by_name_.find(*name) == by_name_.end()) by_name_[*name] = handle;
         if (r.addr == addr && r.length >= length) return handle;  // idempotent
         // same name or same pointer, but moved or grown: register again under the same handle
-        if (r.addr != addr)  // worth a line: two owners using one name in one registry would look exactly like this
+        if (r.addr != addr) {  // worth a line: two owners using one name in one registry would look exactly like this
             SLIME_LOG_WARN("memory region '", r.name, "' moves from ", reinterpret_cast<void*>(r.addr), " to ",
                            reinterpret_cast<void*>(addr), " under handle ", handle);
+            // An automatic name says where the region starts, so it does not survive the move (the region moves under
+            // one of its other names): left in place it would collide with the automatic name of whatever is registered
+            // at the old address next.
+            char was[40];
+            snprintf(was, sizeof(was), "auto_0x%llx", static_cast<unsigned long long>(r.addr));
+            if (name && *name != was) {
+                auto stale = by_name_.find(was);
+                if (stale != by_name_.end() && stale->second == handle) {
+                    by_name_.erase(stale);
+                    if (r.name == was) r.name = *name;
+                }
+            }
+        }
         if (on_unregister) on_unregister(r);
         obs::record_mr_grow(r.system, r.length, length);
         by_ptr_.erase(r.addr);

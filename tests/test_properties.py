@@ -302,7 +302,8 @@ pool_ops = st.lists(st.one_of(
 @given(pool_ops)
 def test_memory_pool_handles_are_stable_and_regions_only_grow(program):
     """A name identifies its region (registering it again returns the same handle, a larger length grows the region); a
-    second name for a pointer that is registered already becomes an alias of that region; unregistering a name removes the region only with its last name, unregistering the handle removes it with all names; handles of live regions are distinct."""
+    second name for a pointer that is registered already becomes an alias of that region; a region that moves under one of
+    its names loses the automatic name of its old address; unregistering a name removes the region only with its last name, unregistering the handle removes it with all names; handles of live regions are distinct."""
     from dlslime_b200 import _slime_c
 
     pool = _slime_c.MemoryPool()
@@ -323,6 +324,10 @@ def test_memory_pool_handles_are_stable_and_regions_only_grow(program):
                     regions[h][1] = length
             elif key in names:  # the name wins: same handle, moved and / or grown
                 assert h == names[key]
+                if regions[h][0] != addr:  # an automatic name says where the region started: it does not survive a move
+                    stale = f"auto_{regions[h][0]:#x}"
+                    if stale != key and names.get(stale) == h:
+                        del names[stale]
                 if regions[h][0] != addr or regions[h][1] < length:
                     regions[h] = [addr, length]
             elif by_ptr is not None:  # a new name for a registered pointer: alias
