@@ -8,6 +8,16 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
+try:  # property tests: the same examples on every run unless exploring is asked for (HYPOTHESIS_PROFILE=explore)
+    from hypothesis import settings as _hyp_settings
+
+    _hyp_settings.register_profile("repeatable", derandomize=True, database=None)
+    _hyp_settings.register_profile("explore")
+    _hyp_settings.load_profile(os.environ.get("HYPOTHESIS_PROFILE", "repeatable"))
+except ImportError:
+    pass
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (runs only on a GPU box)")
     config.addinivalue_line("markers", "multigpu: needs at least two GPUs on one node")
