@@ -171,6 +171,12 @@ def cmd_grouped(a):
         wbytes = (w13.numel() + w2.numel()) * 2
         extra["picked_tile_n"] = {"gate_up": t1, "down": t2, "gate_up_ms": round(n1, 4), "down_ms": round(n2, 4),
                                   "weights_tbs": round(wbytes / (n1 + n2) / 1e9, 2), "weights_tbs_tile_256": round(wbytes / (b1 + b2) / 1e9, 2)}
+    if rows <= 48:  # groups of a few dozen rows: row tiles of 64 and a fifth pipeline stage
+        m1, _ = timeit(lambda: gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, tile_m=64), a.iters)
+        m2, _ = timeit(lambda: gemm.grouped_gemm_bf16(h, w2, offs, out=y, tile_m=64), a.iters)
+        wbytes = (w13.numel() + w2.numel()) * 2
+        extra["tile_m_64"] = {"gate_up_ms": round(m1, 4), "down_ms": round(m2, 4), "weights_tbs": round(wbytes / (m1 + m2) / 1e9, 2),
+                              "weights_tbs_tile_m_128": round(wbytes / (b1 + b2) / 1e9, 2)}
     if a.prefetch:  # weight prefetch into L2, for the weight-streaming shapes
         extra["w_prefetch"] = {}
         wbytes = (w13.numel() + w2.numel()) * 2

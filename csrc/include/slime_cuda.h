@@ -90,12 +90,12 @@ int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* gr
                             unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
                             const float* row_scale, void* status, void* stream);
 // The same on single CTAs with tiles of tile_n = 128, 192, 224 or 256 columns (0 = 256) and the weight boxes asked into
-// L2 w_prefetch K blocks (of 64) ahead of the loads (0 = no prefetch).
+// L2 w_prefetch K blocks (of 64) ahead of the loads (0 = no prefetch); tile_m = 64: row tiles of 64 and a five-stage ring.
 int slime_grouped_gemm_bf16_tile(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
                                  int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
                                  const void* row_info, const unsigned long long* scatter_bases8,
                                  unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
-                                 const float* row_scale, int tile_n, int w_prefetch, void* status, void* stream);
+                                 const float* row_scale, int tile_n, int w_prefetch, int tile_m, void* status, void* stream);
 // The same on CTA pairs (clusters of two CTAs, 256-row tiles): faster where groups hold several hundred rows or more.
 int slime_grouped_gemm_bf16_pair(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
                                  int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,

@@ -94,9 +94,11 @@ constexpr int kAgChunkBytes = 4096;  // staging buffer of the in-kernel all-gath
 constexpr int kAgMaxBufs    = 6;
 constexpr int kSmemLimit    = 227 * 1024;
 
-template<int BN, int STAGES, bool AG = false, bool A8 = false>
+// AROWS: rows of A that a stage holds (128, or 64 for launches whose groups are small: the MMA still reads 128 rows, the
+// upper 64 from whatever follows in the stage, and their results are never stored)
+template<int BN, int STAGES, bool AG = false, bool A8 = false, int AROWS = kBM>
 struct Smem {
-    static constexpr int kABytes     = kBM * kBK * 2;
+    static constexpr int kABytes     = AROWS * kBK * 2;
     static constexpr int kBBytes     = BN * kBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kRawBytes   = A8 ? kBM * kBK : 0;  // e4m3 A tile of a stage as it arrives, before expansion
@@ -125,8 +127,9 @@ struct TileWalker {
     int         g;          // current group
     int         cum;        // tiles before group g
     int         g_begin, g_end, g_mtiles;
+    int         tile_rows;  // rows of a tile: 128, or 64 in the short-A instantiations
 
-    __device__ TileWalker(const Args& args, int bn_out): a(args)
+    __device__ TileWalker(const Args& args, int bn_out, int rows_per_tile = kBM): a(args), tile_rows(rows_per_tile)
     {
         ntiles_n = (a.N + bn_out - 1) / bn_out;
         t        = blockIdx.x;
@@ -143,7 +146,7 @@ struct TileWalker {
             g_end    = a.group_offsets ? a.group_offsets[g + 1] : a.M_total;
             if (g_end > a.M_total) g_end = a.M_total;
             if (g_begin > g_end) g_begin = g_end;
-            g_mtiles = (g_end - g_begin + kBM - 1) / kBM;
+            g_mtiles = (g_end - g_begin + tile_rows - 1) / tile_rows;
         }
     }
     __device__ bool next(TileCoord& c)
@@ -178,7 +181,7 @@ struct TileWalker {
                     nt = local / g_mtiles;
                 }
                 c.group   = g;
-                c.row0    = g_begin + mt * kBM;
+                c.row0    = g_begin + mt * tile_rows;
                 c.row_end = g_end;
                 c.nt      = nt;
                 return true;
@@ -417,13 +420,14 @@ constexpr int kCvtThreads = 128;  // A8 kernels: four more warps expand the e4m3
 // but the raw tile costs a pipeline stage (3 instead of 4) and the expansion sits between the load and the MMA: in the
 // weight-streaming regime (256 experts x 128 rows on one GPU) the kernel was measured 38 % slower than the 4-stage one,
 // more than the separate pass costs, so callers keep the two-pass path by default.
-template<int BN, int STAGES, int EPI, bool AG = false, bool A8 = false>
+template<int BN, int STAGES, int EPI, bool AG = false, bool A8 = false, int AROWS = kBM>
 __global__ void __launch_bounds__(kThreads + (AG ? kAgThreads : 0) + (A8 ? kCvtThreads : 0), 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmAL, const Args args)
 {
     static_assert(!(AG && A8), "the all-gather form takes bf16 activations");
-    using S = Smem<BN, STAGES, AG, A8>;
+    static_assert(AROWS == kBM || (AROWS == 64 && !AG && !A8), "short A tiles: 64 rows, grouped bf16 launches only");
+    using S = Smem<BN, STAGES, AG, A8, AROWS>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -486,7 +490,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            TileWalker walk(args, kBNOut);
+            TileWalker walk(args, kBNOut, AROWS);
             TileCoord  tc;
             int        stage = 0;
             uint32_t   phase = 0;
@@ -498,7 +502,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             bool     ended = false;
             // the tile after the current one, for the weight prefetch (static order: every gridDim-th tile)
             const int  pf_dist = (args.tile_counter == nullptr && args.w_prefetch > 0) ? (args.w_prefetch < kblocks ? args.w_prefetch : kblocks) : 0;
-            TileWalker peek(args, kBNOut);
+            TileWalker peek(args, kBNOut, AROWS);
             TileCoord  tn;
             // behind the per-group pairs, the trace holds one start time per CTA
             if (args.group_trace != nullptr) args.group_trace[2 * args.num_groups + blockIdx.x] = globaltimer_ns();
@@ -613,7 +617,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
-            TileWalker walk(args, kBNOut);
+            TileWalker walk(args, kBNOut, AROWS);
             TileCoord  tc;
             int        stage = 0;
             uint32_t   phase = 0;
@@ -665,7 +669,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     else if (A8 && warp >= 6) {
         // ------------------------------ e4m3 -> bf16 expansion of the A tile ------
         const int  r = threadIdx.x - kThreads;  // tile row of this thread
-        TileWalker walk(args, kBNOut);
+        TileWalker walk(args, kBNOut, AROWS);
         TileCoord  tc;
         int        stage = 0;
         uint32_t   phase = 0;
@@ -710,7 +714,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     else {
         // ------------------------------ epilogue ----------------------------------
         const int  quad = warp & 3;  // TMEM lane quadrant this warp may access
-        TileWalker walk(args, kBNOut);
+        TileWalker walk(args, kBNOut, AROWS);
         TileCoord  tc;
         int        acc = 0;
         uint32_t   acc_phase = 0;
@@ -726,7 +730,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
             tc_fence_after_sync();
             const int      row   = tc.row0 + quad * 32 + lane;
-            const bool     valid = row < tc.row_end;
+            const bool     valid = row < tc.row_end && quad * 32 + lane < AROWS;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kAccStride;
             const int      col0  = tc.nt * kBNOut;
 

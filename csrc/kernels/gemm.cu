@@ -34,14 +34,14 @@ int pick_bn(int M, int N)
     return best;
 }
 
-template<int BN, int EPI, bool AG>
+template<int BN, int EPI, bool AG, int AROWS = kBM, int STAGES = kStages>
 int launch_bn(const void* A, const void* B, const void* A_local, int rows_local, const Args& args, long long lda, long long ldb,
               int threads, cudaStream_t stream)
 {
-    using S = Smem<BN, kStages, AG>;
+    using S = Smem<BN, STAGES, AG, false, AROWS>;
     CUtensorMap tmA, tmB, tmAL;
     const unsigned long long rowsB_total = static_cast<unsigned long long>(args.rowsB) * args.num_groups;
-    if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.M_total, args.K, lda, kBM, kBK)) return -1;
+    if (make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.M_total, args.K, lda, AROWS, kBK)) return -1;
     if (make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rowsB_total, args.K, ldb, BN / 2, kBK)) return -1;
     if (A_local) {
         if (make_tmap_2d(&tmAL, A_local, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_local, args.K, args.K, kBM, kBK)) return -1;
@@ -49,13 +49,13 @@ int launch_bn(const void* A, const void* B, const void* A_local, int rows_local,
     else {
         tmAL = tmA;
     }
-    auto kern = gemm_bf16_tc_kernel<BN, kStages, EPI, AG>;
+    auto kern = gemm_bf16_tc_kernel<BN, STAGES, EPI, AG, false, AROWS>;
     static bool configured = false;
     if (!configured) {
         SLIME_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
         configured = true;
     }
-    const long tiles = static_cast<long>((args.M_total + kBM - 1) / kBM) * ((args.N + BN - 1) / BN);
+    const long tiles = static_cast<long>((args.M_total + AROWS - 1) / AROWS) * ((args.N + BN - 1) / BN);
     int        grid  = sm_count();
     // a fused all-gather kernel keeps the full grid (its extra warps push whatever the tile count is);
     // grouped launches do not know their tile count on the host
@@ -72,12 +72,15 @@ int launch_bn(const void* A, const void* B, const void* A_local, int rows_local,
 
 thread_local int g_tile_n     = 0;  // set around one grouped launch on single CTAs: tile width 128 / 192 / 224 (0 = 256)
 thread_local int g_w_prefetch = 0;  // and the distance of its weight prefetch in K blocks (0 = none)
+thread_local int g_tile_m     = 0;  // 64: row tiles of 64 with a five-stage ring (groups of a few dozen rows)
 
 template<int EPI>
 int launch(const void* A, const void* B, const Args& args, long long lda, long long ldb, cudaStream_t stream)
 {
     // A grouped launch with few tiles (decode-size steps on many ranks: 32 experts x 16 tile columns = 3.46 waves of 148)
     // is quantised by the wave count; the caller, who knows the expected number of row tiles, may ask for a narrower tile.
+    if (args.group_ready == nullptr && g_tile_m == 64 && g_tile_n == 0)
+        return launch_bn<kBN, EPI, false, 64, 5>(A, B, nullptr, 0, args, lda, ldb, kThreads, stream);
     if (args.group_ready == nullptr) {
         switch (g_tile_n) {
             case 128: return launch_bn<128, EPI, false>(A, B, nullptr, 0, args, lda, ldb, kThreads, stream);
@@ -421,14 +424,18 @@ int slime_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* gr
 }
 
 // The same on single CTAs with options: a tile width of 128, 192 or 224 columns instead of 256 (SwiGLU: half of it in
-// output columns), and a weight prefetch into L2 w_prefetch K blocks ahead of the loads (for launches with few rows per
-// group, which stream their weights from HBM).
+// output columns), a weight prefetch into L2 w_prefetch K blocks ahead of the loads (for launches with few rows per
+// group, which stream their weights from HBM), and row tiles of 64 (tile_m = 64): the A part of a stage shrinks from 16
+// to 8 KB, which makes room for a fifth stage, i.e. 160 instead of 128 KB of weight tiles in flight per SM.
 int slime_grouped_gemm_bf16_tile(const void* A, const void* B, void* C, const int* group_offsets, int num_groups,
                                  int M_cap, int N, int K, long long lda, long long ldb, long long ldc, int epilogue,
                                  const void* row_info, const unsigned long long* scatter_bases8,
                                  unsigned long long scatter_row_bytes, unsigned long long scatter_slots,
-                                 const float* row_scale, int tile_n, int w_prefetch, void* status, void* stream)
+                                 const float* row_scale, int tile_n, int w_prefetch, int tile_m, void* status, void* stream)
 {
+    if (tile_m != 0 && tile_m != 64 && tile_m != 128) return fail("grouped gemm: row tiles of %d are not offered", tile_m);
+    if (tile_m == 64 && tile_n != 0 && tile_n != 256) return fail("grouped gemm: row tiles of 64 come with 256-wide tiles only");
+    g_tile_m = tile_m == 64 ? 64 : 0;
     if (tile_n != 0 && tile_n != 128 && tile_n != 192 && tile_n != 224 && tile_n != 256) return fail("grouped gemm: tile width %d is not offered", tile_n);
     if (w_prefetch < 0 || w_prefetch > 64) return fail("grouped gemm: weight prefetch distance %d not in [0, 64]", w_prefetch);
     g_tile_n     = tile_n == 256 ? 0 : tile_n;
@@ -437,6 +444,7 @@ int slime_grouped_gemm_bf16_tile(const void* A, const void* B, void* C, const in
                                      scatter_row_bytes, scatter_slots, row_scale, nullptr, 0, nullptr, status, stream);
     g_tile_n     = 0;
     g_w_prefetch = 0;
+    g_tile_m     = 0;
     return rc;
 }
 

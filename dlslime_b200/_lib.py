@@ -57,7 +57,7 @@ _SIGNATURES["slime_grouped_gemm_bf16_pair"] = _SIGNATURES["slime_grouped_gemm_bf
 _SIGNATURES["slime_grouped_gemm_bf16_wide"] = _SIGNATURES["slime_grouped_gemm_bf16"]
 _SIGNATURES["slime_grouped_gemm_bf16_swapped"] = _SIGNATURES["slime_grouped_gemm_bf16"]
 _SIGNATURES["slime_gemm_bf16_wide"] = _SIGNATURES["slime_gemm_bf16_pair"]
-_SIGNATURES["slime_grouped_gemm_bf16_tile"] = [*_SIGNATURES["slime_grouped_gemm_bf16"][:-2], c_int, c_int, c_void_p, c_void_p]
+_SIGNATURES["slime_grouped_gemm_bf16_tile"] = [*_SIGNATURES["slime_grouped_gemm_bf16"][:-2], c_int, c_int, c_int, c_void_p, c_void_p]
 
 
 class SlimeCudaError(RuntimeError):

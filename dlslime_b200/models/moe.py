@@ -98,6 +98,11 @@ class ExpertParallelMoE:
         # from HBM, the CTAs do not wait for one another between waves, and a short last wave still fills the memory
         # system (5.66 TB/s of weights with 256-wide tiles, 5.53 with the widths that fill the waves).
         self.tile_n_gate_up = self.tile_n_down = int(os.environ.get("SLIME_EP_TILE_N", "0"))
+        # row tiles of 64 where a local expert is expected to see a few dozen rows per step (decode steps): the A part of
+        # a pipeline stage halves, the ring gets a fifth stage and more weight bytes are in flight (SLIME_EP_TILE_M=0|64)
+        expected = max_tokens * cfg.topk * self.world / max(1, cfg.num_experts)
+        forced_m = os.environ.get("SLIME_EP_TILE_M")
+        self.tile_m = (64 if expected + 3 * expected ** 0.5 <= 64 else 0) if forced_m is None else int(forced_m)
         cap = self.buf.recv_cap
         self.xd = torch.empty((cap, cfg.hidden), dtype=torch.bfloat16, device=dev)
         self.h = torch.empty((cap, cfg.intermediate), dtype=torch.bfloat16, device=dev)
@@ -127,14 +132,14 @@ class ExpertParallelMoE:
                                    epilogue=gemm.EPI_SWIGLU)
             return
         gemm.grouped_gemm_bf16(self.xd, self.w_gate_up, self.buf.group_offsets, out=self.h, epilogue=gemm.EPI_SWIGLU,
-                               pair=self.pair_gemm, tile_n=self.tile_n_gate_up)
+                               pair=self.pair_gemm, tile_n=self.tile_n_gate_up, tile_m=self.tile_m)
 
     def step_down(self):
         c = self.cfg
         gemm.grouped_gemm_bf16(self.h, self.w_down, self.buf.group_offsets, epilogue=gemm.EPI_SCATTER_ROWS,
                                row_info=self.buf.recv_info, scatter_bases=self._bases,
                                scatter_row_bytes=c.hidden * 2, scatter_slots=self.max_tokens * c.topk, pair=self.pair_gemm,
-                               tile_n=self.tile_n_down)
+                               tile_n=self.tile_n_down, tile_m=self.tile_m)
 
     def step_experts(self, T, epoch):
         self.step_recv(T, epoch)

@@ -83,7 +83,7 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
                       epilogue: int = EPI_STORE, row_info: torch.Tensor | None = None, scatter_bases=None,
                       scatter_row_bytes: int = 0, scatter_slots: int = 0,
                       row_scale: torch.Tensor | None = None, pair: bool | str = False, tile_n: int = 0,
-                      w_prefetch: int = 0) -> torch.Tensor | None:
+                      w_prefetch: int = 0, tile_m: int = 0) -> torch.Tensor | None:
     """Grouped GEMM over consecutive row groups of ``a``.
 
     ``a`` is ``[M_cap, K]``; ``group_offsets`` is an int32 device tensor of
@@ -103,7 +103,9 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
     for rows that do not exist, and a group of up to 256 rows passes over its weights once. ``tile_n`` (single CTAs only): tile width 128,
     192 or 224 instead of 256, see :func:`pick_grouped_tile_n`. ``w_prefetch`` (single CTAs only): the producer asks L2 for
     the weight boxes this many 64-deep K blocks ahead of its loads, meant for launches that stream weights from HBM (few rows per
-    group); measured slower than no prefetch at every distance on this part, so nothing sets it.
+    group); measured slower than no prefetch at every distance on this part, so nothing sets it. ``tile_m=64`` (single CTAs, 256-wide
+    tiles): row tiles of 64 instead of 128, for groups of a few dozen rows (a decode step): the A part of a pipeline stage
+    halves and the ring gets a fifth stage, so more weight bytes are in flight per SM.
     """
     require_cuda(a, b, group_offsets)
     assert a.dtype == b.dtype == torch.bfloat16 and group_offsets.dtype == torch.int32
@@ -115,9 +117,9 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Ten
     if epilogue != EPI_SCATTER_ROWS and out is None:
         out = torch.empty((m_cap, n), dtype=torch.bfloat16, device=a.device)
     ldc = out.stride(0) if out is not None else n
-    if not pair and (tile_n not in (0, 256) or w_prefetch):
+    if not pair and (tile_n not in (0, 256) or w_prefetch or tile_m == 64):
         _lib.call("slime_grouped_gemm_bf16_tile", ptr(a), ptr(b), ptr(out), ptr(group_offsets), g, m_cap, n, k, a.stride(0), k, ldc,
-                  epilogue, ptr(row_info), scatter_bases, scatter_row_bytes, scatter_slots, ptr(row_scale), int(tile_n), int(w_prefetch),
+                  epilogue, ptr(row_info), scatter_bases, scatter_row_bytes, scatter_slots, ptr(row_scale), int(tile_n), int(w_prefetch), int(tile_m),
                   default_status().dev_ptr, stream_ptr())
         return out
     entry = "slime_grouped_gemm_bf16_swapped" if pair == "swap" else "slime_grouped_gemm_bf16_wide" if pair == "wide" else "slime_grouped_gemm_bf16_pair" if pair else "slime_grouped_gemm_bf16"

@@ -70,17 +70,17 @@ def test_grouped_gemm_store_and_swiglu(pair):
         start += sz
 
 
-@pytest.mark.parametrize("tile_n,w_prefetch", [(128, 0), (192, 3), (224, 0), (0, 4), (0, 40)])
-def test_grouped_gemm_narrow_tiles(tile_n, w_prefetch):
-    """The single-CTA grouped GEMM with tile widths other than 256 and with the weight prefetch into L2 (a distance
-    shorter and longer than the K loop of 6 blocks): store, SwiGLU (an output width that the half tile does not divide)
-    and scatter epilogues against the fp32 product."""
+@pytest.mark.parametrize("tile_n,w_prefetch,tile_m", [(128, 0, 0), (192, 3, 0), (224, 0, 0), (0, 4, 0), (0, 40, 0), (0, 0, 64)])
+def test_grouped_gemm_narrow_tiles(tile_n, w_prefetch, tile_m):
+    """The single-CTA grouped GEMM with tile widths other than 256, with the weight prefetch into L2 (a distance
+    shorter and longer than the K loop of 6 blocks) and with row tiles of 64: store, SwiGLU (an output width that the
+    half tile does not divide) and scatter epilogues against the fp32 product."""
     import ctypes
 
     from dlslime_b200.ops import gemm
     from dlslime_b200.ops._common import default_status
 
-    torch.manual_seed(tile_n + w_prefetch)
+    torch.manual_seed(tile_n + w_prefetch + tile_m)
     sizes = [3, 0, 130, 257, 64]
     g, k, n = len(sizes), 384, 448
     total = sum(sizes)
@@ -88,14 +88,14 @@ def test_grouped_gemm_narrow_tiles(tile_n, w_prefetch):
     a = torch.randn(total, k, device="cuda", dtype=torch.bfloat16)
     w = (torch.randn(g, n, k, device="cuda") * 0.05).to(torch.bfloat16)
     w2 = (torch.randn(g, 2 * n, k, device="cuda") * 0.05).to(torch.bfloat16)
-    out = gemm.grouped_gemm_bf16(a, w, offs, tile_n=tile_n, w_prefetch=w_prefetch)
-    h = gemm.grouped_gemm_bf16(a, w2, offs, epilogue=gemm.EPI_SWIGLU, tile_n=tile_n, w_prefetch=w_prefetch)
+    out = gemm.grouped_gemm_bf16(a, w, offs, tile_n=tile_n, w_prefetch=w_prefetch, tile_m=tile_m)
+    h = gemm.grouped_gemm_bf16(a, w2, offs, epilogue=gemm.EPI_SWIGLU, tile_n=tile_n, w_prefetch=w_prefetch, tile_m=tile_m)
     dst = torch.zeros(total, n, device="cuda", dtype=torch.bfloat16)
     perm = torch.randperm(total, device="cuda")
     bases = (ctypes.c_ulonglong * 8)()
     bases[0] = dst.data_ptr()
     gemm.grouped_gemm_bf16(a, w, offs, epilogue=gemm.EPI_SCATTER_ROWS, row_info=perm.to(torch.int64), scatter_bases=bases,
-                           scatter_row_bytes=n * 2, scatter_slots=total, tile_n=tile_n, w_prefetch=w_prefetch)
+                           scatter_row_bytes=n * 2, scatter_slots=total, tile_n=tile_n, w_prefetch=w_prefetch, tile_m=tile_m)
     torch.cuda.synchronize()
     default_status().check()
     start = 0
