@@ -12,10 +12,10 @@
 //     ("tfull") in both CTAs at once; the epilogue warps of both CTAs drain their own TMEM and arrive
 //     on the leader's "tempty" barrier (the peer's arrivals are remote).
 //
-// One group only (plain GEMM and all-gather -> GEMM); the grouped expert GEMM stays on the single-CTA
-// kernel, whose 128-row tiles waste less on ragged groups. Same Args, same bounded waits, same
-// status page as gemm_tc.cuh; the all-gather roles (gating on arrival counters, shard-major tile order,
-// the push warp) carry over.
+// This file: one group (plain GEMM and all-gather -> GEMM). The grouped forms on pairs are gemm_tc2g.cuh
+// (256 x 256 tiles per group), gemm_tc2w.cuh (256 x 512 tiles) and gemm_tc2s.cuh (operands swapped). Same Args,
+// same bounded waits, same status page as gemm_tc.cuh; the all-gather roles (gating on arrival counters,
+// shard-major tile order, the push warp) carry over.
 #pragma once
 
 #include "gemm_tc.cuh"
