@@ -182,7 +182,7 @@ std::shared_ptr<ReadWriteFuture> TcpEndpoint::submit_one_sided(OpCode opcode, co
     st->link_id = obs_link_;
     obs::record_submit(obs_link_, obs::op_index(opcode), assign.size(), bytes);
     auto fut = std::make_shared<ReadWriteFuture>(st);
-    if (!connected_.load() || stopping_.load()) {
+    if (!connected_.load() || stopping_.load() || broken_.load()) {
         complete(st, FAILED);
         return fut;
     }
@@ -192,12 +192,46 @@ std::shared_ptr<ReadWriteFuture> TcpEndpoint::submit_one_sided(OpCode opcode, co
     op.imm    = imm;
     op.state  = st;
     op.id     = next_id_.fetch_add(1);
+    // a read posts only headers; a write is posted by the caller only when it is small enough not to hold the caller up
+    if (!try_post_inline(op, opcode == OpCode::READ ? 0 : bytes)) enqueue(std::move(op));
+    return fut;
+}
+
+void TcpEndpoint::enqueue(Op&& op)
+{
     {
         std::lock_guard<std::mutex> g(submit_mu_);
         submit_q_.push_back(std::move(op));
     }
     submit_cv_.notify_one();
-    return fut;
+}
+
+bool TcpEndpoint::try_post_inline(Op& op, uint64_t bytes)
+{
+    constexpr uint64_t kInlineBytes = 256 * 1024;
+    if (bytes > kInlineBytes || !op.state->signal->is_gpu_ready()) return false;
+    if (op.opcode == OpCode::READ && op.assign.empty()) return false;  // completed by the sender loop without a post
+    {
+        std::lock_guard<std::mutex> g(submit_mu_);
+        if (posting_ || !submit_q_.empty() || stopping_.load()) return false;
+        posting_ = true;  // from here on every other operation queues up behind this one
+    }
+    {
+        std::lock_guard<std::mutex> g(inflight_mu_);
+        inflight_[op.id] = op;
+    }
+    const bool ok = post_op(op);
+    {
+        std::lock_guard<std::mutex> g(submit_mu_);
+        posting_ = false;
+    }
+    submit_cv_.notify_one();  // the sender thread may have been waiting for its turn
+    if (!ok) {
+        obs::record_post_failure(obs_link_, obs::op_index(op.opcode));
+        broken_.store(true);
+        fail_everything(FAILED);
+    }
+    return true;
 }
 
 std::shared_ptr<ReadWriteFuture> TcpEndpoint::read(const std::vector<assign_tuple_t>& assign, void* stream)
@@ -244,7 +278,7 @@ std::shared_ptr<SendFuture> TcpEndpoint::send(const chunk_tuple_t& chunk, void* 
     auto fut = std::make_shared<SendFuture>(st);
     if (stream != nullptr && !engine_env().bypass_device_signal) st->signal->bind_stream(stream);
     st->signal->record_gpu_ready();
-    if (!connected_.load() || stopping_.load()) {
+    if (!connected_.load() || stopping_.load() || broken_.load()) {
         complete(st, FAILED);
         return fut;
     }
@@ -253,11 +287,7 @@ std::shared_ptr<SendFuture> TcpEndpoint::send(const chunk_tuple_t& chunk, void* 
     op.chunk  = chunk;
     op.state  = st;
     op.id     = next_id_.fetch_add(1);
-    {
-        std::lock_guard<std::mutex> g(submit_mu_);
-        submit_q_.push_back(std::move(op));
-    }
-    submit_cv_.notify_one();
+    if (!try_post_inline(op, std::get<2>(chunk))) enqueue(std::move(op));
     return fut;
 }
 
@@ -371,11 +401,23 @@ void TcpEndpoint::sender_loop()
         Op op;
         {
             std::unique_lock<std::mutex> g(submit_mu_);
-            submit_cv_.wait(g, [&] { return stopping_.load() || !submit_q_.empty(); });
+            submit_cv_.wait(g, [&] { return stopping_.load() || (!submit_q_.empty() && !posting_); });
             if (stopping_.load()) return;
             op = std::move(submit_q_.front());
             submit_q_.pop_front();
+            posting_ = true;
         }
+        struct Turn {  // hands the turn back however this iteration ends
+            TcpEndpoint* e;
+            ~Turn()
+            {
+                {
+                    std::lock_guard<std::mutex> g(e->submit_mu_);
+                    e->posting_ = false;
+                }
+                e->submit_cv_.notify_one();
+            }
+        } turn{this};
         // head of line: operations leave in submission order, so a buffer that is not ready yet holds back what follows
         while (!op.state->signal->is_gpu_ready() && !stopping_.load()) std::this_thread::sleep_for(std::chrono::microseconds(20));
         if (stopping_.load()) {
@@ -392,6 +434,7 @@ void TcpEndpoint::sender_loop()
         }
         if (!post_op(op)) {
             obs::record_post_failure(obs_link_, obs::op_index(op.opcode));
+            broken_.store(true);
             fail_everything(FAILED);
             return;
         }

@@ -83,6 +83,10 @@ private:
     void acceptor_loop();
     void server_loop(int fd);
     bool post_op(Op& op);
+    // Posts `op` on the calling thread when nothing is queued or being posted (small operations: no hand-over to the
+    // sender thread, one wake-up less per operation). False = not taken, queue it.
+    bool try_post_inline(Op& op, uint64_t bytes);
+    void enqueue(Op&& op);
     void complete(const std::shared_ptr<EndpointOpState>& st, int32_t status);
     void fail_everything(int32_t status);
     void deliver_imm(int32_t imm);
@@ -99,6 +103,8 @@ private:
     std::mutex              submit_mu_;
     std::condition_variable submit_cv_;
     std::deque<Op>          submit_q_;
+    bool                    posting_ = false;  // under submit_mu_: some thread is inside post_op (operations leave in order)
+    std::atomic<bool>       broken_{false};    // a post failed: the link is gone, later operations fail at once
 
     std::mutex                       inflight_mu_;
     std::unordered_map<uint64_t, Op> inflight_;  // awaiting an acknowledgement or read data
