@@ -87,13 +87,22 @@ void RpcSession::post_committed(uint32_t tag, uint64_t request_id, uint32_t targ
     memcpy(reinterpret_cast<void*>(send_ptr_), &h, sizeof(h));
     std::vector<assign_tuple_t> assign{assign_tuple_t(static_cast<uintptr_t>(send_h_), static_cast<uintptr_t>(remote_recv_h_),
                                                       static_cast<uint64_t>(target_slot) * slot_size_, 0, h.total_len)};
-    auto fut = ep_->write_with_imm(assign, static_cast<int32_t>(target_slot));
-    // the single send buffer may be reused as soon as the write completed
+    // The single send buffer may be reused as soon as this write has completed. Nobody waits for that here: the caller
+    // goes on to wait for the reply (which cannot arrive before the request has), and whoever stages the next message
+    // settles this write first (settle_last_post). That takes the write's acknowledgement off the path of a call.
+    last_post_ = ep_->write_with_imm(assign, static_cast<int32_t>(target_slot));
+}
+
+void RpcSession::settle_last_post()
+{
+    if (!last_post_) return;
+    auto fut = std::move(last_post_);
+    last_post_.reset();
     // bounded like every other host wait: a peer that stops draining must not hold send_mu_ for ever
     static const int64_t post_ms = get_env<int64_t>("SLIME_RPC_POST_TIMEOUT_MS", 30000);
     const int32_t st = fut->wait(post_ms > 0 ? post_ms : 30000);
-    if (st == TIME_OUT) throw std::runtime_error("rpc session: write did not complete within " + std::to_string(post_ms) + " ms (status 402)");
-    if (st != SUCCESS) throw std::runtime_error("rpc session: write failed with status " + std::to_string(st));
+    if (st == TIME_OUT) throw std::runtime_error("rpc session: the previous write did not complete within " + std::to_string(post_ms) + " ms (status 402)");
+    if (st != SUCCESS) throw std::runtime_error("rpc session: the previous write failed with status " + std::to_string(st));
 }
 
 std::shared_ptr<ClientFuture> RpcSession::call(uint32_t tag, const void* payload, size_t nbytes)
@@ -117,6 +126,7 @@ std::shared_ptr<ClientFuture> RpcSession::call_inplace(uint32_t tag, const Write
     }
     try {
         std::lock_guard<std::mutex> g(send_mu_);
+        settle_last_post();
         const size_t n = writer(reinterpret_cast<char*>(send_ptr_) + HEADER_SIZE, payload_capacity());
         if (n > payload_capacity()) throw std::length_error("rpc writer produced more bytes than the slot holds");
         post_committed(tag & ~FLAG_MASK, rid, slot, n);
@@ -248,6 +258,7 @@ void RpcSession::post_reply_inplace(uint32_t tag, uint64_t request_id, uint32_t 
     if (closed_.load()) throw std::runtime_error("rpc session is closed");
     if (client_slot_id >= slot_count_) throw std::out_of_range("rpc reply names a slot outside the mailbox");
     std::lock_guard<std::mutex> g(send_mu_);
+    settle_last_post();
     const size_t n = writer(reinterpret_cast<char*>(send_ptr_) + HEADER_SIZE, payload_capacity());
     if (n > payload_capacity()) throw std::length_error("rpc writer produced more bytes than the slot holds");
     post_committed(tag | REPLY_BIT, request_id, client_slot_id, n);

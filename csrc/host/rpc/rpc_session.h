@@ -114,6 +114,7 @@ private:
     uint32_t acquire_slot();
     void     release_slot(uint32_t slot);
     void     post_committed(uint32_t tag, uint64_t request_id, uint32_t target_slot, size_t payload_bytes);
+    void     settle_last_post();  // caller holds send_mu_: the write that last used the send buffer has completed
     void     recv_loop();
     bool     handle_arrival(uint32_t slot);  // false = malformed
     void     fail_all_pending(const std::string& why);
@@ -125,6 +126,7 @@ private:
     const bool      has_pump_;
 
     std::mutex send_mu_;  // one send buffer: header + payload are staged there, then written out
+    std::shared_ptr<ReadWriteFuture> last_post_;  // under send_mu_: the write that still reads the send buffer
     std::mutex slot_mu_;
     std::condition_variable slot_cv_;
     std::deque<uint32_t>    free_slots_;
