@@ -8,6 +8,7 @@
 #include <netinet/tcp.h>
 #include <poll.h>
 #include <sys/socket.h>
+#include <sys/uio.h>
 #include <sys/types.h>
 #include <unistd.h>
 
@@ -53,6 +54,28 @@ bool send_all(int fd, const void* buf, size_t n)
         n -= static_cast<size_t>(w);
     }
     return true;
+}
+
+// Header and payload in one system call (one segment on the wire for small payloads instead of two).
+bool send_hdr_and_payload(int fd, const void* hdr, size_t hdr_len, const void* payload, size_t n)
+{
+    if (n == 0) return send_all(fd, hdr, hdr_len);
+    iovec  iov[2] = {{const_cast<void*>(hdr), hdr_len}, {const_cast<void*>(payload), n}};
+    msghdr m{};
+    m.msg_iov    = iov;
+    m.msg_iovlen = 2;
+    ssize_t w;
+    do {
+        w = ::sendmsg(fd, &m, MSG_NOSIGNAL);
+    } while (w < 0 && errno == EINTR);
+    if (w <= 0) return false;
+    size_t done = static_cast<size_t>(w);
+    if (done < hdr_len) {  // rare: finish the header, then the payload
+        if (!send_all(fd, static_cast<const char*>(hdr) + done, hdr_len - done)) return false;
+        done = hdr_len;
+    }
+    const size_t sent = done - hdr_len;
+    return sent >= n || send_all(fd, static_cast<const char*>(payload) + sent, n - sent);
 }
 
 bool recv_all(int fd, void* buf, size_t n)
@@ -231,6 +254,9 @@ bool TcpEndpoint::try_post_inline(Op& op, uint64_t bytes)
         broken_.store(true);
         fail_everything(FAILED);
     }
+    else if (broken_.load()) {
+        fail_everything(FAILED);  // the link died while this operation was on its way: nobody will answer it
+    }
     return true;
 }
 
@@ -334,8 +360,7 @@ bool TcpEndpoint::post_op(Op& op)
         h.flags  = F_LAST;
         h.id     = op.id;
         h.length = std::get<2>(op.chunk);
-        if (!send_all(out_fd_, &h, sizeof(h))) return false;
-        return send_all(out_fd_, reinterpret_cast<const void*>(std::get<0>(op.chunk) + std::get<1>(op.chunk)), h.length);
+        return send_hdr_and_payload(out_fd_, &h, sizeof(h), reinterpret_cast<const void*>(std::get<0>(op.chunk) + std::get<1>(op.chunk)), h.length);
     }
     // Every piece is checked before the first byte leaves: a batch with a piece that names an unknown region or runs
     // past one fails as a whole, moves nothing, and leaves nothing in flight for the peer to answer.
@@ -377,8 +402,7 @@ bool TcpEndpoint::post_op(Op& op)
                 h.flags |= F_IMM;
                 h.imm = op.imm;
             }
-            if (!send_all(out_fd_, &h, sizeof(h))) return false;
-            if (!send_all(out_fd_, reinterpret_cast<const void*>(local.addr + std::get<3>(a)), h.length)) return false;
+            if (!send_hdr_and_payload(out_fd_, &h, sizeof(h), reinterpret_cast<const void*>(local.addr + std::get<3>(a)), h.length)) return false;
         }
         posted += h.length;
     }
@@ -435,6 +459,10 @@ void TcpEndpoint::sender_loop()
         if (!post_op(op)) {
             obs::record_post_failure(obs_link_, obs::op_index(op.opcode));
             broken_.store(true);
+            fail_everything(FAILED);
+            return;
+        }
+        if (broken_.load()) {  // the link died while this operation was on its way: nobody will answer it
             fail_everything(FAILED);
             return;
         }
@@ -499,7 +527,10 @@ void TcpEndpoint::receiver_loop()
             }
         }
     }
-    if (!stopping_.load()) fail_everything(FAILED);
+    if (!stopping_.load()) {
+        broken_.store(true);  // the peer is gone: whatever is submitted from now on fails at once
+        fail_everything(FAILED);
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -566,8 +597,7 @@ void TcpEndpoint::server_loop(int fd)
             rsp.imm    = h.imm;
             rsp.status = ok ? SUCCESS : FAILED;
             rsp.length = ok ? h.length : 0;
-            if (!send_all(fd, &rsp, sizeof(rsp))) break;
-            if (ok && !send_all(fd, reinterpret_cast<const void*>(r.addr + h.offset), h.length)) break;
+            if (!send_hdr_and_payload(fd, &rsp, sizeof(rsp), reinterpret_cast<const void*>(r.addr + h.offset), ok ? h.length : 0)) break;
         }
         else if (h.kind == REQ_SEND) {
             // The length comes from the peer: a corrupt or hostile header must neither pin gigabytes of host memory
