@@ -172,3 +172,28 @@ def test_oversized_message_closes_the_connection_instead_of_the_process():
     env = dict(os.environ, PYTHONPATH=repo, SLIME_TCP_MAX_MESSAGE_BYTES="1024")
     r = subprocess.run([sys.executable, "-c", body], env=env, capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "alive" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+def test_operations_of_one_thread_leave_in_submission_order_whatever_their_size(pair):
+    """Small operations are posted by the submitting thread when nothing is queued, large ones by the sender thread. A
+    stream of alternating 1 MiB and 8-byte writes with immediates, submitted without waiting, must still reach the peer in
+    submission order: the immediates arrive as 0, 1, 2, ... and the word that every small write targets ends up holding
+    the last small write's value."""
+    a, b, ba, bb = pair
+    k = 64
+    word = 3 << 20  # offset of the 8-byte word in both buffers
+    futs = []
+    for i in range(k):
+        if i % 2 == 0:
+            futs.append(a.write_with_imm([(0, 0, 0, 0, 1 << 20)], i))
+        else:
+            ctypes.memmove(ctypes.addressof(ba) + (1 << 21) + 8 * i, i.to_bytes(8, "little"), 8)  # a distinct source per write
+            futs.append(a.write_with_imm([(0, 0, word, (1 << 21) + 8 * i, 8)], i))
+    assert all(f.wait(20) == 0 for f in futs)
+    got = []
+    for _ in range(k):
+        r = b.imm_recv()
+        assert r.wait(10) == 0
+        got.append(r.imm_data())
+    assert got == list(range(k))
+    assert int.from_bytes(bb.raw[word:word + 8], "little") == k - 1
