@@ -5,6 +5,7 @@
     python bench/profile_case.py gemm_pair   # the same product on CTA pairs (cta_group::2), 3 launches
     python bench/profile_case.py gemm_wide   # 8192^3 on CTA pairs with 256 x 512 tiles (operands larger than L2), 2 launches
     python bench/profile_case.py grouped_pair  # grouped SwiGLU gate/up + down GEMM on CTA pairs, 8 experts x 1024 rows, 2 launches each
+    python bench/profile_case.py grouped_decode  # gate/up GEMM of a decode step on 8 ranks (32 experts x 32 rows): 128-row tiles, then 64-row tiles with five stages
     python bench/profile_case.py gemm_fp8    # the same shape in block-scaled fp8 (e4m3), 3 launches
     python bench/profile_case.py grouped     # grouped SwiGLU gate/up + down GEMM, 8 experts x 512 rows, 2 launches each
     python bench/profile_case.py grouped_stream  # the same GEMMs with 16 experts x 128 rows: weight streaming, HBM-bound
@@ -71,6 +72,20 @@ def grouped_pair_case():
     for _ in range(2):
         gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, pair=True)
         gemm.grouped_gemm_bf16(h, w2, offs, out=y, pair=True)
+
+
+def grouped_decode_case():
+    """Weight streaming with a few dozen rows per expert: the same launch with four 48 KB stages and with five 40 KB stages."""
+    from dlslime_b200.ops import gemm
+
+    g, rows, k, inter = 32, 32, 7168, 2048
+    offs = torch.arange(0, g + 1, dtype=torch.int32, device="cuda") * rows
+    x = torch.randn(g * rows, k, device="cuda").to(torch.bfloat16)
+    w13 = (torch.randn(g, 2 * inter, k, device="cuda") * 0.02).to(torch.bfloat16)
+    h = torch.empty(g * rows, inter, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):
+        gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU)
+        gemm.grouped_gemm_bf16(x, w13, offs, out=h, epilogue=gemm.EPI_SWIGLU, tile_m=64)
 
 
 def gemm_fp8_case():
@@ -251,6 +266,6 @@ def moe_stream_case():
 if __name__ == "__main__":
     {"ag_gemm_fused": ag_gemm_fused_case, "ag_gemm_fp8_fused": ag_gemm_fp8_fused_case, "moe_stream": moe_stream_case,
      "alltoall": alltoall_case, "kv": kv_case, "allgather": allgather_case, "gemm": gemm_case, "gemm_pair": gemm_pair_case, "gemm_wide": gemm_wide_case,
-     "grouped_pair": grouped_pair_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "grouped_stream": grouped_stream_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
+     "grouped_pair": grouped_pair_case, "grouped_decode": grouped_decode_case, "gemm_fp8": gemm_fp8_case, "grouped": grouped_case, "grouped_stream": grouped_stream_case, "moe_step": moe_case, "quant": quant_case, "copy": copy_case}[sys.argv[1]]()
     torch.cuda.synchronize()
     print("done", sys.argv[1])
